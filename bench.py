@@ -1,0 +1,440 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on synthetic data of the named shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c5|c4] [--impl reference]
+
+One JSON line on stdout (rank 0).  A step is one pass of the hot path over one batch:
+
+  c3 (default)  batched GQA decode, 256 ragged sequences (L ~ U[512, 4096]), 9 q / 3 kv heads,
+                D = 64, bf16 KV cache.  Metric: KV GB/s (HBM roofline).  With N GPUs every rank
+                holds its own 256 sequences (weak scaling, no collective on the data path).
+  c5            long-context decode, 8 x 131072 rows, 32 q / 8 kv heads, D = 128, bf16; the KV
+                sequence is sharded over the ranks and the (o, m, l) partials are gathered with
+                NCCL and merged (strong scaling).
+  c4            causal prefill 4 x 8192, 32 q / 8 kv heads, D = 128, bf16 (tensor roofline); KV
+                heads are split over the ranks, no collective (strong scaling).
+
+`value` is timed with CUDA events on the launching stream with inputs resident in HBM;
+`e2e` is the same metric through the host-facing call: every step copies that step's
+activations from pinned host memory, runs RoPE + cache append + attention, and copies the
+result back.  `--impl reference` times the CPU restatement of the reference's attention
+(the reference has no CPU forward of its own) on the host cores and, when the reference's
+kernels were compiled into oracle/_ref, also its own GPU launch sequence on the same batch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEEDS = {"c3": 20253, "c4": 20254, "c5": 20255}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, taken from the
+# ncu summaries under profiles/ (None until a capture exists for that workload)
+NCU_TRAFFIC_BYTES = {"c3": None, "c5": None, "c4": None}
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm": float(p["hbm_gbs"]), "bf16": float(p["bf16_tflops"]),
+                "bf16_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz, self.stop_flag = [], set(), None, False
+        self.index, self.thread, self.ok = index, None, False
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception as e:  # pragma: no cover
+            log(f"clock sampler: NVML unavailable ({e})")
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+                 "hw_thermal_slowdown": 0x40, "hw_power_brake": 0x80}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.ok:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop_flag = True
+        if self.thread:
+            self.thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+class Dist:
+    def __init__(self, n_gpus):
+        import torch
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != n_gpus:
+            if self.world == 1 and n_gpus > 1:
+                raise SystemExit(f"--gpus {n_gpus} needs a launch with torch.distributed.run --nproc-per-node {n_gpus}")
+        torch.cuda.set_device(self.local)
+        self.torch = torch
+        if self.world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.dist = dist
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max(self, x):
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum(self, x):
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def close(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def timed_steps(torch, step, steps, warmup, flush=None, dist=None):
+    """W untimed warm-up steps, then exactly K steps, each bracketed by CUDA events on the
+    current stream with an L2 flush outside the bracket.  Returns the per-step ms list."""
+    for _ in range(warmup):
+        if flush is not None:
+            flush.zero_()
+        step()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    if dist is not None:
+        dist.barrier()
+    else:
+        torch.cuda.synchronize()
+    for a, b in ev:
+        if flush is not None:
+            flush.zero_()
+        a.record()
+        step()
+        b.record()
+    if dist is not None:
+        dist.barrier()
+    else:
+        torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in ev]
+
+
+# ------------------------------------------------------------------------------- c3 / c5
+def decode_workload(name, rank, world, device="cuda"):
+    """Shapes and seeded synthetic data of the two decode configurations, built on `device`."""
+    import torch
+    gen = torch.Generator(device=device)
+    if name == "c3":
+        B, Hq, Hkv, D, cap = 256, 9, 3, 64, 4096
+        gen.manual_seed(SEEDS[name] + 1000 * rank)
+        lens = np.random.Generator(np.random.Philox(key=SEEDS[name] + 1000 * rank)).integers(512, 4097, B).astype(np.int32)
+        rows = cap
+    else:
+        B, Hq, Hkv, D, L = 8, 32, 8, 128, 131072
+        gen.manual_seed(SEEDS[name] + 1000 * rank)
+        rows = L // world           # this rank's contiguous slice of every KV head
+        cap = rows
+        lens = np.full(B, rows, np.int32)
+    kc = torch.empty(B, Hkv, cap, D, dtype=torch.bfloat16, device=device)
+    vc = torch.empty_like(kc)
+    for t in (kc, vc):              # fill in slices: randn in fp32 then round, without a 2x fp32 copy
+        for b in range(B):
+            t[b] = torch.randn(Hkv, cap, D, generator=gen, device=device).bfloat16()
+    qgen = torch.Generator(device=device).manual_seed(SEEDS[name] + 7)   # q is the same on every rank of c5
+    q = torch.randn(B, Hq * D, generator=qgen if name == "c5" else gen, device=device).bfloat16()
+    kv_bytes = int(lens.astype(np.int64).sum()) * 2 * Hkv * D * 2
+    qo_bytes = B * Hq * D * (2 + 4)
+    return dict(B=B, Hq=Hq, Hkv=Hkv, D=D, cap=cap, lens=lens, kc=kc, vc=vc, q=q, rows=rows,
+                bytes=kv_bytes + qo_bytes, scale=1.0 / math.sqrt(D))
+
+
+def run_decode(args, dist, name):
+    import torch
+    from nimllm_b200 import attention as A
+    from nimllm_b200 import _lib
+    torch.manual_seed(0)
+    w = decode_workload(name, dist.rank, dist.world)
+    B, Hq, Hkv, D, cap = w["B"], w["Hq"], w["Hkv"], w["D"], w["cap"]
+    seq_len = torch.from_numpy(w["lens"]).cuda()
+    max_len = int(w["lens"].max())
+    geom = dict(n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=max_len, seq_len=seq_len,
+                seq_stride=Hkv * cap * D, head_stride=cap * D, scale=w["scale"], chunk_rows=args.chunk_rows)
+    out = torch.empty(B, Hq * D, dtype=torch.float32, device="cuda")
+    sharded = name == "c5" and dist.world > 1
+    if sharded:
+        W = D + 4
+        gathered = torch.empty(dist.world, B * Hq, W, dtype=torch.float32, device="cuda")
+
+    def step():
+        if not sharded:
+            A.decode_batch(w["q"], w["kc"], w["vc"], out=out, **geom)
+        else:
+            _, rec = A.decode_batch(w["q"], w["kc"], w["vc"], out=out, partials=True, **geom)
+            dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
+            A.combine(gathered, D)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    sampler = ClockSampler(dist.local)
+    with sampler:
+        ms = timed_steps(torch, step, args.steps, args.warmup, flush, dist)
+    t_local = sum(ms) / 1e3
+    t_max = dist.max(t_local)
+    total_bytes = dist.sum(float(w["bytes"])) if not sharded else float(w["bytes"]) * dist.world
+    value = total_bytes / t_max * args.steps / 1e9
+
+    # ---- end to end through the host-facing call: H2D activations, RoPE + append + decode, D2H
+    E, Ekv = Hq * D, Hkv * D
+    hq = torch.randn(B, E).pin_memory(); hk = torch.randn(B, Ekv).pin_memory(); hv = torch.randn(B, Ekv).pin_memory()
+    hout = torch.empty(B, E).pin_memory()
+    dq = torch.empty(B, E, device="cuda"); dk = torch.empty(B, Ekv, device="cuda"); dv = torch.empty(B, Ekv, device="cuda")
+    # the new token overwrites the last attended row, so the batch keeps its lengths from step to
+    # step; in c5 that is global row 131071, which only the last KV-sequence shard stores
+    if name == "c5":
+        cos, sin = A.rope_tables(131072, D, 500000.0)
+        seq_pos = torch.full((B,), 131071, dtype=torch.int32, device="cuda")
+        row0 = dist.rank * w["rows"]
+    else:
+        cos, sin = A.rope_tables(max_len + 1, D, 10000.0)
+        seq_pos = (seq_len - 1).to(torch.int32)
+        row0 = 0
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
+        A.rope_append(dq.view(B, 1, E), dk.view(B, 1, Ekv), dv.view(B, 1, Ekv), cos, sin, n_head=Hq, n_kv_head=Hkv,
+                      head_dim=D, seq_pos=seq_pos, k_cache=w["kc"], v_cache=w["vc"], seq_stride=Hkv * cap * D,
+                      head_stride=cap * D, cache_row0=row0, max_seq=cap)
+        if not sharded:
+            A.decode_batch(dq, w["kc"], w["vc"], out=out, **geom)
+            hout.copy_(out, non_blocking=True)
+        else:
+            _, rec = A.decode_batch(dq, w["kc"], w["vc"], out=out, partials=True, **geom)
+            dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
+            hout.copy_(A.combine(gathered, D).view(B, E), non_blocking=True)
+
+    e2e_ms = timed_steps(torch, e2e_step, args.steps, args.warmup, flush, dist)
+    e2e_t = dist.max(sum(e2e_ms) / 1e3)
+    e2e_value = total_bytes / e2e_t * args.steps / 1e9
+    # restore nothing: the overwritten rows stay valid bf16 data
+
+    pk = peaks()
+    launches_per_step = 1 + (1 if lib_needs_combine(_lib, B, Hq, Hkv, D, max_len, args.chunk_rows) else 0) + (1 if sharded else 0)
+    per_rank_ms = sum(ms) / len(ms)
+    achieved = float(w["bytes"]) / (per_rank_ms / 1e3) / 1e9
+    line = {
+        "metric": "decode_attn_kv_gbps", "value": round(value, 2), "unit": "GB/s", "n_gpus": dist.world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_max / args.steps * 1e3, 5),
+        "higher_is_better": True, "scaling": "strong" if name == "c5" else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": {"c3": "C3 batched GQA decode: 256 ragged sequences per GPU, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
+                                "c5": "C5 long-context decode: 8 x 131072 rows, 32q/8kv heads, D=128, bf16 KV, KV sequence sharded over the GPUs"}[name],
+                   "batch_per_gpu": B, "kv_rows_total": int(w["lens"].astype(np.int64).sum()),
+                   "parallelism": ("kv-sequence shards + NCCL all-gather of (o,m,l)" if sharded else
+                                   f"independent sequences x{dist.world}, no collective"),
+                   "l2": "256 MiB flush between timed steps; working set exceeds L2 as well",
+                   "tokens_per_s": round(B * (1 if name == "c5" else dist.world) / (t_max / args.steps), 1)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm"], 4), "traffic": NCU_TRAFFIC_BYTES[name],
+                     "peak_source": pk["source"], "algorithmic_bytes_per_step": int(w["bytes"]),
+                     "kernel": "decode_mma_kernel (+ combine_kernel) per step, CUDA events on the launching stream"},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": B * (E + 2 * Ekv) * 4,
+                "d2h_bytes_per_step": B * E * 4, "ms_per_step": round(e2e_t / args.steps * 1e3, 5)},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": sampler.summary(),
+    }
+    if dist.rank == 0 and dist.world == 1:
+        line["cpu_baseline"] = cpu_baseline_decode(w, reps=3)
+    return line
+
+
+def lib_needs_combine(_lib, B, Hq, Hkv, D, max_len, chunk_rows):
+    return _lib.lib().nimllm_attn_decode_workspace_bytes(B, Hq, Hkv, D, max_len, chunk_rows) > 0
+
+
+def cpu_baseline_decode(w, reps=3, max_seqs=None):
+    """The CPU restatement of the reference's per-head decode loop (oracle/attn_oracle.c,
+    fp32 arithmetic, OpenMP over sequence x head) on the same batch, all host threads."""
+    from oracle import oracle as O
+    import torch
+    B, Hq, Hkv, D, cap = w["B"], w["Hq"], w["Hkv"], w["D"], w["cap"]
+    n = B if max_seqs is None else min(B, max_seqs)
+    kb = w["kc"][:n].cpu().view(torch.int16).numpy().view(np.uint16).reshape(-1)
+    vb = w["vc"][:n].cpu().view(torch.int16).numpy().view(np.uint16).reshape(-1)
+    q = w["q"][:n].float().cpu().numpy()
+    off = np.arange(n, dtype=np.int64) * Hkv * cap * D
+    hs = np.full(n, cap * D, np.int64)
+    lens = w["lens"][:n]
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.decode_batch(q, kb, vb, off, hs, lens, Hq, Hkv, D, w["scale"])
+        best = min(best, time.perf_counter() - t0)
+    nbytes = int(lens.astype(np.int64).sum()) * 2 * Hkv * D * 2 + n * Hq * D * 6
+    return {"value": round(nbytes / best / 1e9, 3), "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"{n} of {B} sequences, 1 step, best of {reps}; {best * 1e3:.1f} ms",
+            "host_cpus": os.cpu_count()}
+
+
+def run_reference_decode(args, dist, name):
+    """Reference arm: the CPU restatement on the host cores (and, as extra information, the
+    reference's own GPU launch sequence from oracle/_ref on an fp32 copy of a sample)."""
+    import torch
+    from oracle import oracle as O
+    if name != "c3":
+        return {"impl": "reference", "unavailable": "reference arm is implemented for the c3 workload"}
+    w = decode_workload(name, 0, 1, "cuda" if torch.cuda.is_available() else "cpu")
+    B, Hq, Hkv, D, cap = w["B"], w["Hq"], w["Hkv"], w["D"], w["cap"]
+    kb = w["kc"].cpu().view(torch.int16).numpy().view(np.uint16).reshape(-1)
+    vb = w["vc"].cpu().view(torch.int16).numpy().view(np.uint16).reshape(-1)
+    q = w["q"].float().cpu().numpy()
+    off = np.arange(B, dtype=np.int64) * Hkv * cap * D
+    hs = np.full(B, cap * D, np.int64)
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        O.decode_batch(q, kb, vb, off, hs, w["lens"], Hq, Hkv, D, w["scale"])
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    t = sum(times)
+    value = w["bytes"] * args.steps / t / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_attn_kv_gbps", "value": round(value, 3), "unit": "GB/s",
+        "n_gpus": dist.world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(t / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C3 batched GQA decode: 256 ragged sequences, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
+                   "note": "the reference has no CPU forward; this is the C restatement of its attention loop "
+                           "(src/model.nim:822-840) with OpenMP over sequence x head; the numerator is the "
+                           "workload's algorithmic bytes (bf16 KV), so ratios of values are ratios of speed"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                         "sample": f"full batch of {B} sequences per step"},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    if O.ref_available() and torch.cuda.is_available():
+        try:
+            n = 32                                 # sample of sequences for the reference's GPU launch loop
+            kf = w["kc"][:n].float().contiguous(); vf = w["vc"][:n].float().contiguous()
+            qf = w["q"][:n].float().contiguous()
+            o = torch.zeros(n, Hq * D, device="cuda"); scr = torch.zeros(2 * cap, device="cuda")
+            R = O.ref_lib()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            best = float("inf")
+            for _ in range(3):
+                torch.cuda.synchronize(); a.record()
+                R.ref_decode_batch_dev(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), off[:n].copy(), hs[:n].copy(),
+                                       w["lens"][:n].copy(), o.data_ptr(), scr.data_ptr(), n, Hq, Hkv, D, cap)
+                b.record(); torch.cuda.synchronize()
+                best = min(best, a.elapsed_time(b))
+            nb = int(w["lens"][:n].astype(np.int64).sum()) * 2 * Hkv * D * 2 + n * Hq * D * 6
+            line["reference_gpu_path"] = {
+                "what": "the reference's compiled kernels + cublasSgemm_v2, 4 launches per query head "
+                        "(src/model.nim:822-840), fp32 KV, same B200",
+                "sample": f"{n} of {B} sequences", "ms": round(best, 3), "launches": n * Hq * 4,
+                "value": round(nb / (best / 1e3) / 1e9, 2), "unit": "GB/s (bf16-equivalent algorithmic bytes)"}
+        except Exception as e:  # pragma: no cover
+            line["reference_gpu_path"] = {"unavailable": str(e)[:200]}
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c5", "c4"])
+    ap.add_argument("--chunk-rows", type=int, default=0)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        if rank != 0:
+            return 0
+        class _Solo:
+            world, rank, local = args.gpus, 0, 0
+        if torch.cuda.is_available():
+            torch.cuda.set_device(0)
+        args.steps = min(args.steps, 20)       # each CPU step is a full batch: bound the run
+        args.warmup = min(args.warmup, 3)
+        line = run_reference_decode(args, _Solo, args.workload)
+        print(json.dumps(line), flush=True)
+        return 0
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention library has no CPU path")
+    from nimllm_b200 import _lib, build
+    if not os.path.exists(_lib.LIB_PATH) and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        build.build()
+    dist = Dist(args.gpus)
+    if args.workload in ("c3", "c5"):
+        line = run_decode(args, dist, args.workload)
+    else:
+        from nimllm_b200 import bench_prefill
+        line = bench_prefill.run(args, dist, peaks(), ClockSampler, timed_steps)
+    if dist.rank == 0:
+        print(json.dumps(line), flush=True)
+    dist.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,186 @@
+/* nimllm_attn.h -- C ABI of the B200 (sm_100a) grouped-query attention path for nimllm.
+ *
+ * This is the boundary the Nim host code binds with {.importc, cdecl.}, the way
+ * src/gpu.nim:219-328 binds src/kernels.cu today.  Conventions follow the
+ * reference: raw device pointers, runtime int shapes, no structs, the caller owns
+ * every buffer, nothing is allocated per call, no host synchronisation inside.
+ * Unlike the reference's void launchers every new entry point returns an int
+ * status (0 = ok) that Nim may `discard`; nimllm_attn_last_error() explains it.
+ * `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream
+ * the reference launches everything on (src/gpu.nim:166-175).
+ *
+ * Tensor layouts are the reference's: activations are row-major [tokens, heads*D]
+ * with heads as column blocks of width D (src/model.nim:487-497); a KV head of
+ * the cache is a dense row-major [rows, D] block with K stored AFTER RoPE and V
+ * raw (src/model.nim:797-815); query head h reads KV head h / (Hq/Hkv)
+ * (src/kernels.cu:447, src/model.nim:823).
+ */
+#ifndef NIMLLM_ATTN_H
+#define NIMLLM_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations / cache */
+#define NIMLLM_F32 0
+#define NIMLLM_BF16 1
+
+/* status codes */
+#define NIMLLM_OK 0
+#define NIMLLM_ERR_ARG 1         /* null pointer, bad shape */
+#define NIMLLM_ERR_UNSUPPORTED 2 /* head_dim / dtype / group size without a kernel */
+#define NIMLLM_ERR_WORKSPACE 3   /* caller-provided workspace too small */
+#define NIMLLM_ERR_CUDA 4        /* launch or runtime error; see last_error */
+
+/* Message for the calling thread's most recent non-zero status ("" if none). */
+const char *nimllm_attn_last_error(void);
+int nimllm_attn_version(void);
+
+/* ---- RoPE tables -----------------------------------------------------------
+ * Replaces the host loop of src/model.nim:153-163: cos/sin [max_pos, D/2] fp32,
+ * theta = float(pos) / powf(base, 2f/D), filled on the HOST (upload them the way
+ * initModel does).  base is a run-time value (the reference bakes ropeTheta in
+ * at compile time, src/model.nim:22). */
+int nimllm_rope_tables_host(float *cos_tab, float *sin_tab, int max_pos, int head_dim, float base);
+
+/* ---- KV cache: contiguous layout ---------------------------------------------
+ * Replaces KvCache / initKvCache / resetKvCache (src/model.nim:70-73,729-746).
+ * The reference makes 2*nLayer*nKvHead separate cudaMallocs of [blockSize, D]
+ * fp32.  Here K and V are ONE allocation each, [n_layer][n_seq][Hkv][max_seq][D]
+ * of `dtype`, zero-filled; a (layer, sequence, KV head) block is the same dense
+ * [max_seq, D] rows the reference's per-head buffer is.  The handle also keeps
+ * the host-side `pos` of the reference's KvCache.  create/destroy allocate and
+ * free and are set-up calls, not hot-path calls. */
+typedef struct nimllm_kvcache nimllm_kvcache;
+nimllm_kvcache *nimllm_kvcache_create(int n_layer, int n_seq, int n_kv_head, int max_seq,
+                                      int head_dim, int dtype);
+void nimllm_kvcache_destroy(nimllm_kvcache *kv);
+int nimllm_kvcache_reset(nimllm_kvcache *kv, void *stream); /* zero-fill, pos = 0 */
+void *nimllm_kvcache_k(const nimllm_kvcache *kv, int layer); /* [n_seq][Hkv][max_seq][D] */
+void *nimllm_kvcache_v(const nimllm_kvcache *kv, int layer);
+int nimllm_kvcache_pos(const nimllm_kvcache *kv);
+void nimllm_kvcache_set_pos(nimllm_kvcache *kv, int pos);
+int64_t nimllm_kvcache_seq_stride(const nimllm_kvcache *kv);  /* elements: Hkv*max_seq*D */
+int64_t nimllm_kvcache_head_stride(const nimllm_kvcache *kv); /* elements: max_seq*D */
+
+/* ---- fused RoPE + cast + cache append ------------------------------------------
+ * Replaces, in one launch, ropeFwd(q) and ropeFwd(kNew) (src/model.nim:796-797 via
+ * src/kernels.cu:399-423) and the per-KV-head append of src/model.nim:799-815
+ * (2*Hkv cudaMemcpy D2D for one token, gpu_extract_kv_head for several).
+ *
+ *   q      [B, n, Hq*D] act_dtype, rotated IN PLACE (NULL: skip)
+ *   k_new  [B, n, Hkv*D] act_dtype; rotated copy goes to the cache; it is also
+ *          written back in place when write_back_k != 0 (the reference always
+ *          rotates in place)
+ *   v_new  [B, n, Hkv*D] act_dtype, copied raw
+ *   rope_cos / rope_sin  full tables [>= max position + 1, D/2]; both NULL: no rotation
+ *   seq_pos  DEVICE int32 [B], absolute position of each sequence's first new
+ *          token, or NULL: every sequence starts at pos0 (the reference's kv.pos)
+ *   k_cache / v_cache  cache_dtype; sequence b's block starts at element
+ *          kv_off[b] (DEVICE int64 [B]) or, with kv_off NULL, at b*seq_stride;
+ *          KV head h follows at h*head_stride; cache row = position - cache_row0;
+ *          rows outside [0, max_seq) are not stored (a KV-sequence shard keeps only
+ *          its own rows).  Both NULL: rotate only.
+ */
+int nimllm_rope_append(void *q, int n_head, void *k_new, const void *v_new, int act_dtype,
+                       int write_back_k, const float *rope_cos, const float *rope_sin,
+                       const int32_t *seq_pos, int pos0, void *k_cache, void *v_cache,
+                       int cache_dtype, const int64_t *kv_off, int64_t seq_stride,
+                       int64_t head_stride, int cache_row0, int max_seq, int batch, int n,
+                       int n_kv_head, int head_dim, void *stream);
+
+/* ---- GQA decode -----------------------------------------------------------------
+ * Replaces the per-query-head loop of src/model.nim:822-840 (cublasSgemm_v2 [1,D]x
+ * [L,D]^T, gpu_scale, gpu_softmax_fwd, cublasSgemm_v2 [1,L]x[L,D]; 4 launches per
+ * query head) for a whole batch of sequences: each KV head is read once for all of
+ * its Hq/Hkv query heads, the KV sequence is split into chunks whose partial
+ * (max, sum, output) triples are merged by log-sum-exp.
+ *
+ *   q        [B, Hq*D] q_dtype, already rotated
+ *   seq_len  DEVICE int32 [B], rows to attend (the reference's pos + 1), or NULL:
+ *            every sequence attends max_len rows
+ *   max_len  host upper bound of seq_len (sizes the grid and the workspace)
+ *   out      [B, Hq*D] out_dtype (may be NULL when partials_out is given)
+ *   partials_out  optional fp32 [B*Hq, D+4] records {o[D] normalised, m, l, 0, 0}
+ *            with m = max of the scaled scores and l = sum exp(s - m): what a
+ *            KV-sequence shard hands to nimllm_attn_combine
+ *   chunk_rows  KV rows per split; 0 = choose
+ *   workspace   nimllm_attn_decode_workspace_bytes(...) bytes, 256-byte aligned
+ */
+size_t nimllm_attn_decode_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim,
+                                          int max_len, int chunk_rows);
+int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const void *v_cache,
+                       int cache_dtype, const int64_t *kv_off, int64_t seq_stride,
+                       int64_t head_stride, const int32_t *seq_len, int max_len, void *out,
+                       int out_dtype, float *partials_out, int batch, int n_head,
+                       int n_kv_head, int head_dim, float scale, int chunk_rows,
+                       void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- merge of (max, sum, output) partials ----------------------------------------
+ * No counterpart in the reference (it never splits a softmax row, src/kernels.cu:
+ * 267-303 sees the whole row).  parts [n_parts, rows, rec_stride] fp32 records
+ * {o[D], m, l, ...}; out [rows, D].  Used after gathering the shards of a
+ * KV-sequence-sharded decode. partials_out (optional) receives the merged records. */
+int nimllm_attn_combine(const float *parts, int n_parts, int rows, int head_dim, int rec_stride,
+                        void *out, int out_dtype, float *partials_out, void *stream);
+
+/* ---- causal prefill ----------------------------------------------------------------
+ * Replaces the attention block of forward(), src/model.nim:469-475,494-508: RoPE on
+ * q and k, then per query head gather / cublasSgemm_v2 QK^T / gpu_causal_mask /
+ * gpu_softmax_fwd / cublasSgemm_v2 PV / scatter (2 + 8*Hq launches, two S x S fp32
+ * matrices per head) -- as one flash-style kernel (plus one RoPE/append pre-pass).
+ *
+ *   q [B,S,Hq*D], k, v [B,S,Hkv*D], out [B,S,Hq*D], all `dtype`
+ *   rope tables as above (NULL: inputs are already rotated); token i of every
+ *   sequence sits at position pos0 + i
+ *   save_cache  the reference's forward(saveCache) flag (src/model.nim:454-457,534):
+ *            non-zero guarantees q and k hold their post-RoPE values on return, as
+ *            backward() expects (src/model.nim:656-685).  k is rotated in place in
+ *            either case; with 0 the contents of q afterwards are unspecified.
+ *   k_cache / v_cache (optional) receive rows pos0..pos0+S-1, as in rope_append
+ *   lse      optional fp32 [B, Hq, S]: log-sum-exp of the scaled scores per row
+ *   dtype F32 runs on the CUDA cores in fp32 (the <= 1e-4 parity path); BF16 runs
+ *   QK^T and PV on the tcgen05 tensor cores with fp32 accumulation.
+ */
+size_t nimllm_attn_prefill_workspace_bytes(int batch, int seq_len, int n_head, int n_kv_head,
+                                           int head_dim, int dtype);
+int nimllm_attn_prefill(void *q, void *k, const void *v, int dtype, const float *rope_cos,
+                        const float *rope_sin, int pos0, void *out, int batch, int seq_len,
+                        int n_head, int n_kv_head, int head_dim, float scale, int save_cache,
+                        void *k_cache, void *v_cache, int cache_dtype, const int64_t *kv_off,
+                        int64_t seq_stride, int64_t head_stride, int max_seq, float *lse,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- the reference's own attention-path launchers, same names and arguments -------
+ * Kept so that callers that still use the unfused sequence (backward(), the test
+ * programs) link against this library alone.  All launch on the legacy default
+ * stream and return void like the originals. */
+/* src/kernels.cu:417-423 */
+void gpu_rope_fwd(float *data, const float *cos_tab, const float *sin_tab, int seq_len,
+                  int n_embd, int n_head, int head_dim);
+/* src/kernels.cu:376-381 */
+void gpu_extract_head(const float *src, float *dst, int h, int seq_len, int n_embd, int head_dim);
+/* src/kernels.cu:383-388 */
+void gpu_insert_head(const float *src, float *dst, int h, int seq_len, int n_embd, int head_dim);
+/* src/kernels.cu:463-469 */
+void gpu_extract_kv_head(const float *src, float *dst, int qHead, int kvRepeat, int seq_len,
+                         int n_kv_dim, int head_dim);
+/* src/kernels.cu:260-263 */
+void gpu_causal_mask(float *scores, float scale, int seq_len);
+/* src/kernels.cu:159-161 */
+void gpu_scale(const float *x, float s, float *y, int n);
+/* src/kernels.cu:336-339 */
+void gpu_softmax_fwd(const float *x, float *y, int rows, int cols);
+/* src/kernels.cu:750-755 (bound in src/gpu.nim:309-311, no caller): single-head fused
+ * attention on dense [S, hd] fp32 buffers */
+void gpu_flash_attn_fwd(const float *Q, const float *K, const float *V, float *O, int S, int hd,
+                        float scale, int causal);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NIMLLM_ATTN_H */

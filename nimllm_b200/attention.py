@@ -1,0 +1,172 @@
+"""Host layer over the C ABI, named after the reference's procedures.
+
+  reference (src/model.nim, src/gpu.nim)          here
+  ------------------------------------------     ---------------------------------
+  initModel's RoPE table loop (:153-163)          rope_tables()
+  KvCache / initKvCache / resetKvCache (:70-73,   KvCache (one device allocation per K and V,
+    :729-746)                                       [layer][seq][kv head][row][D])
+  forward()'s attention block (:494-508)          attn_forward()
+  forwardCached()'s attention block (:788-840)    attn_forward_cached()
+  (no counterpart: batch 1 only)                  decode_batch(), combine()
+
+torch is used for device memory and streams only; every computation goes through
+libnimllm_attn.so and raises if that library is missing or reports an error."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import BF16, F32, check, lib
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise _lib.NimllmAttnError(f"unsupported dtype {t.dtype}: float32 and bfloat16 are built") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise _lib.NimllmAttnError("device tensor expected (there is no CPU path)")
+    if not t.is_contiguous():
+        raise _lib.NimllmAttnError("contiguous tensor expected")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class _Arena:
+    """Caller-owned scratch, the role trackedCreate's arena plays in the reference
+    (src/autograd.nim:37-51): grown outside the hot loop, reused by every call."""
+
+    def __init__(self):
+        self.buf = {}
+
+    def get(self, nbytes: int, device) -> Optional[torch.Tensor]:
+        if nbytes == 0:
+            return None
+        key = torch.device(device).index or 0
+        cur = self.buf.get(key)
+        if cur is None or cur.numel() < nbytes:
+            cur = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            self.buf[key] = cur
+        return cur
+
+
+_arena = _Arena()
+
+
+def rope_tables(max_pos: int, head_dim: int, base: float, device="cuda"):
+    """cos/sin tables [max_pos, D/2] fp32, computed on the host as initModel does."""
+    cos = np.empty((max_pos, head_dim // 2), np.float32)
+    sin = np.empty_like(cos)
+    check(lib().nimllm_rope_tables_host(cos.ctypes.data, sin.ctypes.data, max_pos, head_dim, float(base)))
+    return torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device)
+
+
+class KvCache:
+    """K and V as [n_layer, n_seq, Hkv, max_seq, D] device tensors plus the host `pos`."""
+
+    def __init__(self, n_layer, n_seq, n_kv_head, max_seq, head_dim, dtype=torch.float32, device="cuda"):
+        shape = (n_layer, n_seq, n_kv_head, max_seq, head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.pos = 0
+        self.n_layer, self.n_seq, self.n_kv_head, self.max_seq, self.head_dim = shape
+        self.seq_stride = n_kv_head * max_seq * head_dim
+        self.head_stride = max_seq * head_dim
+
+    def reset(self):
+        self.k.zero_()
+        self.v.zero_()
+        self.pos = 0
+
+
+def rope_append(q, k_new, v_new, cos, sin, *, n_head, n_kv_head, head_dim, pos0=0, seq_pos=None,
+                k_cache=None, v_cache=None, kv_off=None, seq_stride=0, head_stride=0, cache_row0=0,
+                max_seq=0, write_back_k=True):
+    """Fused RoPE(q), RoPE(k_new) + cast + scatter of k_new / v_new into the cache."""
+    B, n = k_new.shape[0], k_new.shape[1]
+    check(lib().nimllm_rope_append(
+        _ptr(q), n_head, _ptr(k_new), _ptr(v_new), _code(k_new), int(write_back_k), _ptr(cos), _ptr(sin),
+        _ptr(seq_pos), pos0, _ptr(k_cache), _ptr(v_cache), _code(k_cache) if k_cache is not None else F32,
+        _ptr(kv_off), seq_stride, head_stride, cache_row0, max_seq, B, n, n_kv_head, head_dim, _stream()))
+
+
+def decode_batch(q, k_cache, v_cache, *, n_head, n_kv_head, head_dim, max_len, seq_len=None, kv_off=None,
+                 seq_stride=0, head_stride=0, scale=None, chunk_rows=0, out=None, out_dtype=torch.float32,
+                 partials=False):
+    """GQA decode of a batch of independent sequences. Returns out [B, Hq*D] (and the
+    (o, m, l) records [B*Hq, D+4] when partials=True)."""
+    B = q.shape[0]
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    if out is None:
+        out = torch.empty((B, n_head * head_dim), dtype=out_dtype, device=q.device)
+    rec = torch.empty((B * n_head, head_dim + 4), dtype=torch.float32, device=q.device) if partials else None
+    need = lib().nimllm_attn_decode_workspace_bytes(B, n_head, n_kv_head, head_dim, max_len, chunk_rows)
+    ws = _arena.get(need, q.device)
+    check(lib().nimllm_attn_decode(
+        _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(kv_off), seq_stride, head_stride,
+        _ptr(seq_len), max_len, _ptr(out), _code(out), _ptr(rec), B, n_head, n_kv_head, head_dim, scale,
+        chunk_rows, _ptr(ws), need, _stream()))
+    return (out, rec) if partials else out
+
+
+def combine(parts, head_dim, out_dtype=torch.float32, partials=False):
+    """Merge (o, m, l) records [n_parts, rows, D+4] -> out [rows, D]."""
+    n_parts, rows, W = parts.shape
+    out = torch.empty((rows, head_dim), dtype=out_dtype, device=parts.device)
+    rec = torch.empty((rows, W), dtype=torch.float32, device=parts.device) if partials else None
+    check(lib().nimllm_attn_combine(_ptr(parts), n_parts, rows, head_dim, W, _ptr(out), _code(out), _ptr(rec),
+                                    _stream()))
+    return (out, rec) if partials else out
+
+
+def attn_forward(q, k, v, cos, sin, *, n_head, n_kv_head, head_dim, pos0=0, save_cache=True, kv: KvCache = None,
+                 layer=0, scale=None, lse=None):
+    """forward()'s attention block: RoPE(q, k) then causal GQA attention.
+    q [B,S,Hq*D] (or [S,Hq*D]), k, v [B,S,Hkv*D]. q and k are rotated in place like the
+    reference's ropeFwd does; with kv given, rows pos0.. of the cache are filled."""
+    squeeze = q.dim() == 2
+    if squeeze:
+        q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+    B, S = q.shape[0], q.shape[1]
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    out = torch.empty_like(q)
+    need = lib().nimllm_attn_prefill_workspace_bytes(B, S, n_head, n_kv_head, head_dim, _code(q))
+    ws = _arena.get(need, q.device)
+    kc = kv.k[layer] if kv is not None else None
+    vc = kv.v[layer] if kv is not None else None
+    check(lib().nimllm_attn_prefill(
+        _ptr(q), _ptr(k), _ptr(v), _code(q), _ptr(cos), _ptr(sin), pos0, _ptr(out), B, S, n_head, n_kv_head,
+        head_dim, scale, int(save_cache), _ptr(kc), _ptr(vc), _code(kc) if kc is not None else F32, None,
+        kv.seq_stride if kv is not None else 0, kv.head_stride if kv is not None else 0,
+        kv.max_seq if kv is not None else 0, _ptr(lse), _ptr(ws), need, _stream()))
+    return out[0] if squeeze else out
+
+
+def attn_forward_cached(kv: KvCache, layer, q, k_new, v_new, cos, sin, *, n_head, scale=None, chunk_rows=0):
+    """forwardCached()'s attention block for one new token per sequence (newTokens == 1):
+    RoPE(q, k_new) at row kv.pos, append, attend rows 0..kv.pos.  q [n_seq, Hq*D],
+    k_new / v_new [n_seq, Hkv*D].  The caller advances kv.pos after the last layer, as
+    the reference does (src/model.nim:890)."""
+    B = q.shape[0]
+    D, Hkv = kv.head_dim, kv.n_kv_head
+    kc, vc = kv.k[layer], kv.v[layer]
+    rope_append(q.view(B, 1, -1), k_new.view(B, 1, -1), v_new.view(B, 1, -1), cos, sin, n_head=n_head,
+                n_kv_head=Hkv, head_dim=D, pos0=kv.pos, k_cache=kc, v_cache=vc, seq_stride=kv.seq_stride,
+                head_stride=kv.head_stride, max_seq=kv.max_seq)
+    return decode_batch(q, kc, vc, n_head=n_head, n_kv_head=Hkv, head_dim=D, max_len=kv.pos + 1,
+                        seq_stride=kv.seq_stride, head_stride=kv.head_stride, scale=scale,
+                        chunk_rows=chunk_rows, out_dtype=torch.float32)

@@ -1,0 +1,599 @@
+// decode.cu -- GQA decode attention over a KV cache (HBM-bound).
+//
+// Replaces the per-query-head loop of src/model.nim:822-840 (per head: cublasSgemm_v2
+// [1,D]x[L,D]^T, gpu_scale, gpu_softmax_fwd, cublasSgemm_v2 [1,L]x[L,D]).  One CTA owns
+// one (sequence, KV head, chunk of KV rows) and serves ALL query heads of that KV head,
+// so every cached K and V row is fetched from HBM once (the reference re-reads it once
+// per query head).  Chunks produce (max, sum, output) partials that are merged by
+// log-sum-exp -- in this file for the chunks of one GPU, and through the same combine
+// kernel for KV-sequence shards gathered from other GPUs.
+//
+// Two kernels:
+//   decode_mma_kernel      bf16 cache.  The G (<= 8) query heads are the rows of a 16-row
+//                          A operand of mma.sync.m16n8k16; K rows are the B operand of
+//                          Q K^T and V rows the B operand of P V.  Each lane fetches its
+//                          fragments straight from global memory with 16-byte loads: the
+//                          contraction index of Q K^T and the output column of P V may be
+//                          permuted freely, and the permutations below are chosen so that
+//                          a lane's 16 contiguous bytes are exactly what its fragments
+//                          need (K) or need after one byte-permute (V).
+//   decode_generic_kernel  fp32 or bf16 cache, fp32 FMA on the CUDA cores: the <= 1e-4
+//                          parity path for the reference's fp32 cache, and the fallback
+//                          for group sizes the mma kernel does not take.
+#include "common.cuh"
+
+namespace nimllm {
+
+namespace {
+
+constexpr int kWarps = 4;
+
+struct DecodeParams {
+    const void *q;
+    const void *k, *v;
+    const int64_t *kv_off;
+    int64_t seq_stride, head_stride;
+    const int32_t *seq_len;
+    void *out;
+    float *partials_out;
+    float *ws;
+    int q_dtype, out_dtype;
+    int max_len, chunk_rows;
+    int B, Hq, Hkv, G;
+    float scale_log2e;
+};
+
+__device__ __forceinline__ int seq_rows(const DecodeParams &p, int b) {
+    int L = p.seq_len ? p.seq_len[b] : p.max_len;
+    return L < 0 ? 0 : (L > p.max_len ? p.max_len : L);
+}
+
+// Final write of one (sequence, query head, column): either the finished output (single
+// chunk) or a partial record for the combine kernel.
+__device__ __forceinline__ void emit(const DecodeParams &p, int D, int b, int hq, int chunk,
+                                     int n_chunks, int d, float o, float l, float m2) {
+    const int W = rec_stride(D);
+    const float val = l > 0.f ? o / l : 0.f;
+    const int64_t row = (int64_t)b * p.Hq + hq;
+    if (n_chunks <= 1) {
+        if (p.out) store_from_f32(p.out, p.out_dtype, row * D + d, val);
+        if (p.partials_out) {
+            float *rec = p.partials_out + row * W;
+            rec[d] = val;
+            if (d == 0) { rec[D] = m2 * kLn2; rec[D + 1] = l; rec[D + 2] = 0.f; rec[D + 3] = 0.f; }
+        }
+    } else {
+        float *rec = p.ws + ((int64_t)chunk * p.B * p.Hq + row) * W;
+        rec[d] = val;
+        if (d == 0) { rec[D] = m2 * kLn2; rec[D + 1] = l; rec[D + 2] = 0.f; rec[D + 3] = 0.f; }
+    }
+}
+
+// Merge of the per-warp states left in shared memory; NH heads, D columns.
+template <int D>
+__device__ __forceinline__ void merge_warps_and_emit(const DecodeParams &p, const float *sm_m,
+                                                     const float *sm_l, const float *sm_o,
+                                                     int nh_stride, int nh, int b, int hq0,
+                                                     int chunk, int n_chunks) {
+    for (int idx = threadIdx.x; idx < nh * D; idx += kWarps * 32) {
+        int g = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, sm_m[w * nh_stride + g]);
+        float safe = (M == -INFINITY) ? 0.f : M;
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            float c = ex2(sm_m[w * nh_stride + g] - safe);
+            l += sm_l[w * nh_stride + g] * c;
+            o += sm_o[((size_t)w * nh_stride + g) * D + d] * c;
+        }
+        emit(p, D, b, hq0 + g, chunk, n_chunks, d, o, l, M);
+    }
+}
+
+// ------------------------------------------------------------------ generic kernel
+// Lane groups of LPR lanes own one KV row at a time (16 bytes per lane); every group
+// keeps its own online-softmax state for the GT query heads and the states are merged
+// at the end (lane groups by shuffles, warps through shared memory).
+template <typename T, int D, int GT>
+__global__ void __launch_bounds__(kWarps * 32) decode_generic_kernel(DecodeParams p) {
+    constexpr int VEC = Elem<T>::kVec;
+    constexpr int LPR = D / VEC;        // lanes per row
+    constexpr int RPW = 32 / LPR;       // rows per warp step
+    constexpr int NWK = kWarps * RPW;   // row workers per CTA
+    constexpr int U = 4;                // rows in flight per worker
+    static_assert(LPR <= 32 && LPR >= 1, "head_dim too large for one warp");
+
+    __shared__ float sm_m[kWarps * GT], sm_l[kWarps * GT];
+    __shared__ float sm_o[kWarps * GT * D];
+
+    const int b = blockIdx.z, chunk = blockIdx.x;
+    const int groups = (p.G + GT - 1) / GT;
+    const int kvh = blockIdx.y / groups, grp = blockIdx.y % groups;
+    const int L = seq_rows(p, b);
+    const int n_chunks = L <= p.chunk_rows ? 1 : (L + p.chunk_rows - 1) / p.chunk_rows;
+    if (chunk >= n_chunks) return;
+    const int r0 = chunk * p.chunk_rows;
+    const int r1 = min(L, r0 + p.chunk_rows);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lir = lane % LPR, rw = lane / LPR;
+    const int wid = warp * RPW + rw;
+    const int g0 = grp * GT;
+    const int ng = min(GT, p.G - g0);
+    const int hq0 = kvh * p.G + g0;
+    const int E = p.Hq * D;
+
+    float qr[GT][VEC];
+#pragma unroll
+    for (int g = 0; g < GT; g++)
+#pragma unroll
+        for (int i = 0; i < VEC; i++)
+            qr[g][i] = g < ng ? load_as_f32(p.q, p.q_dtype, (int64_t)b * E + (int64_t)(hq0 + g) * D + lir * VEC + i) *
+                                    p.scale_log2e
+                              : 0.f;
+
+    float m[GT], l[GT], acc[GT][VEC];
+#pragma unroll
+    for (int g = 0; g < GT; g++) {
+        m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; i++) acc[g][i] = 0.f;
+    }
+
+    const int64_t base = (p.kv_off ? p.kv_off[b] : (int64_t)b * p.seq_stride) + (int64_t)kvh * p.head_stride + lir * VEC;
+    const T *kb = reinterpret_cast<const T *>(p.k) + base;
+    const T *vb = reinterpret_cast<const T *>(p.v) + base;
+
+    for (int rb = r0 + wid; rb < r1; rb += NWK * U) {
+        uint4 kx[U], vx[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            int row = min(rb + u * NWK, r1 - 1);
+            kx[u] = ldg_stream(kb + (int64_t)row * D);
+            vx[u] = ldg_stream(vb + (int64_t)row * D);
+        }
+        float s[U][GT];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float kf[VEC];
+            Elem<T>::unpack(kx[u], kf);
+#pragma unroll
+            for (int g = 0; g < GT; g++) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < VEC; i++) a = fmaf(qr[g][i], kf[i], a);
+                s[u][g] = a;
+            }
+        }
+#pragma unroll
+        for (int off = LPR / 2; off > 0; off >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+                for (int g = 0; g < GT; g++) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], off);
+        float pr[U][GT];
+#pragma unroll
+        for (int g = 0; g < GT; g++) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if (rb + u * NWK >= r1) s[u][g] = -INFINITY;
+                mx = fmaxf(mx, s[u][g]);
+            }
+            float m_new = fmaxf(m[g], mx);
+            float safe = (m_new == -INFINITY) ? 0.f : m_new;
+            float corr = ex2(m[g] - safe);
+            float sum = 0.f;
+#pragma unroll
+            for (int u = 0; u < U; u++) { pr[u][g] = ex2(s[u][g] - safe); sum += pr[u][g]; }
+            l[g] = l[g] * corr + sum;
+            m[g] = m_new;
+#pragma unroll
+            for (int i = 0; i < VEC; i++) acc[g][i] *= corr;
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float vf[VEC];
+            Elem<T>::unpack(vx[u], vf);
+#pragma unroll
+            for (int g = 0; g < GT; g++)
+#pragma unroll
+                for (int i = 0; i < VEC; i++) acc[g][i] = fmaf(pr[u][g], vf[i], acc[g][i]);
+        }
+    }
+
+    // merge the RPW lane groups of this warp
+#pragma unroll
+    for (int off = LPR; off < 32; off <<= 1) {
+#pragma unroll
+        for (int g = 0; g < GT; g++) {
+            float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
+            float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
+            float m_new = fmaxf(m[g], mo);
+            float safe = (m_new == -INFINITY) ? 0.f : m_new;
+            float ca = ex2(m[g] - safe), cb = ex2(mo - safe);
+            l[g] = l[g] * ca + lo * cb;
+            m[g] = m_new;
+#pragma unroll
+            for (int i = 0; i < VEC; i++) {
+                float ao = __shfl_xor_sync(0xffffffffu, acc[g][i], off);
+                acc[g][i] = acc[g][i] * ca + ao * cb;
+            }
+        }
+    }
+    if (rw == 0) {
+#pragma unroll
+        for (int g = 0; g < GT; g++) {
+            if (lir == 0) { sm_m[warp * GT + g] = m[g]; sm_l[warp * GT + g] = l[g]; }
+#pragma unroll
+            for (int i = 0; i < VEC; i++) sm_o[(warp * GT + g) * D + lir * VEC + i] = acc[g][i];
+        }
+    }
+    __syncthreads();
+    merge_warps_and_emit<D>(p, sm_m, sm_l, sm_o, GT, ng, b, hq0, chunk, n_chunks);
+}
+
+// ---------------------------------------------------------------------- mma kernel
+__device__ __forceinline__ void mma_bf16_16816(float &d0, float &d1, uint32_t a0, uint32_t a2,
+                                               uint32_t b0, uint32_t b1) {
+    // rows 8..15 of A are zero padding (a1 = a3 = 0); their outputs are discarded
+    float d2, d3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%10,%10};"
+        : "+f"(d0), "+f"(d1), "=f"(d2), "=f"(d3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+template <int D> struct KvFrag {
+    uint32_t k[2][D / 32][4];  // [row tile][32-column chunk][16 bytes]
+    uint32_t v[4][D / 64][4];  // [row 2t, 2t+1, 2t+8, 2t+9][64-column half][16 bytes]
+};
+
+// Lane (g = lane/4, t = lane%4) of a warp working on the 16 rows starting at rb.
+//  K: rows rb+g and rb+8+g, columns c*32 + t*8 .. +7     (B operand of Q K^T, n = g)
+//  V: rows rb+2t, +2t+1, +2t+8, +2t+9, columns h*64 + g*8 .. +7  (B operand of P V)
+// Rows past the end of the chunk are clamped (their probabilities are forced to 0).
+template <int D>
+__device__ __forceinline__ void load_frag(KvFrag<D> &f, const __nv_bfloat16 *kb,
+                                          const __nv_bfloat16 *vb, int rb, int r_last, int g, int t) {
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+        int row = min(rb + nt * 8 + g, r_last);
+#pragma unroll
+        for (int c = 0; c < D / 32; c++) {
+            uint4 x = ldg_stream(kb + (int64_t)row * D + c * 32 + t * 8);
+            f.k[nt][c][0] = x.x; f.k[nt][c][1] = x.y; f.k[nt][c][2] = x.z; f.k[nt][c][3] = x.w;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int row = min(rb + 2 * t + (i & 1) + (i >> 1) * 8, r_last);
+#pragma unroll
+        for (int h = 0; h < D / 64; h++) {
+            uint4 x = ldg_stream(vb + (int64_t)row * D + h * 64 + g * 8);
+            f.v[i][h][0] = x.x; f.v[i][h][1] = x.y; f.v[i][h][2] = x.z; f.v[i][h][3] = x.w;
+        }
+    }
+}
+
+template <int D>
+__device__ __forceinline__ void consume_frag(const KvFrag<D> &f, const uint32_t (*qreg)[4],
+                                             float (*o)[2], float &m, float &l, int rb, int r1,
+                                             int t, float scale_log2e) {
+    // scores: head g (row of A), KV rows rb + nt*8 + 2t + {0,1}
+    float s[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int c = 0; c < D / 32; c++)
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+                mma_bf16_16816(s[nt][0], s[nt][1], qreg[c][2 * j], qreg[c][2 * j + 1],
+                               f.k[nt][c][2 * j], f.k[nt][c][2 * j + 1]);
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            int row = rb + nt * 8 + 2 * t + e;
+            s[nt][e] = row < r1 ? s[nt][e] * scale_log2e : -INFINITY;
+            mx = fmaxf(mx, s[nt][e]);
+        }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    float m_new = fmaxf(m, mx);
+    float safe = (m_new == -INFINITY) ? 0.f : m_new;
+    float corr = ex2(m - safe);
+    float p00 = ex2(s[0][0] - safe), p01 = ex2(s[0][1] - safe);
+    float p10 = ex2(s[1][0] - safe), p11 = ex2(s[1][1] - safe);
+    l = l * corr + (p00 + p01) + (p10 + p11);
+    m = m_new;
+    const uint32_t pa0 = pack_bf16(p00, p01);  // k slots 2t, 2t+1   <-> rows rb+2t, rb+2t+1
+    const uint32_t pa2 = pack_bf16(p10, p11);  // k slots 2t+8, 2t+9 <-> rows rb+8+2t, rb+9+2t
+#pragma unroll
+    for (int h = 0; h < D / 64; h++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+            uint32_t b0 = prmt(f.v[0][h][j >> 1], f.v[1][h][j >> 1], sel);
+            uint32_t b1 = prmt(f.v[2][h][j >> 1], f.v[3][h][j >> 1], sel);
+            float *acc = o[h * 8 + j];
+            acc[0] *= corr;
+            acc[1] *= corr;
+            mma_bf16_16816(acc[0], acc[1], pa0, pa2, b0, b1);
+        }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kWarps * 32) decode_mma_kernel(DecodeParams p) {
+    constexpr int NH = 8;  // head rows kept (G <= 8)
+    __shared__ float sm_m[kWarps * NH], sm_l[kWarps * NH];
+    __shared__ float sm_o[kWarps * NH * D];
+
+    const int b = blockIdx.z, chunk = blockIdx.x, kvh = blockIdx.y;
+    const int L = seq_rows(p, b);
+    const int n_chunks = L <= p.chunk_rows ? 1 : (L + p.chunk_rows - 1) / p.chunk_rows;
+    if (chunk >= n_chunks) return;
+    const int r0 = chunk * p.chunk_rows;
+    const int r1 = min(L, r0 + p.chunk_rows);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int E = p.Hq * D;
+    const int hq0 = kvh * p.G;
+
+    // A operand: Q[head g][c*32 + t*8 .. +7] as bf16 pairs (zero for padding heads)
+    uint32_t qreg[D / 32][4];
+#pragma unroll
+    for (int c = 0; c < D / 32; c++) {
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            x[i] = g < p.G ? load_as_f32(p.q, p.q_dtype, (int64_t)b * E + (int64_t)(hq0 + g) * D + c * 32 + t * 8 + i)
+                           : 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) qreg[c][i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+    }
+
+    float o[D / 8][2];
+#pragma unroll
+    for (int i = 0; i < D / 8; i++) { o[i][0] = 0.f; o[i][1] = 0.f; }
+    float m = -INFINITY, l = 0.f;
+
+    const int64_t base = (p.kv_off ? p.kv_off[b] : (int64_t)b * p.seq_stride) + (int64_t)kvh * p.head_stride;
+    const __nv_bfloat16 *kb = reinterpret_cast<const __nv_bfloat16 *>(p.k) + base;
+    const __nv_bfloat16 *vb = reinterpret_cast<const __nv_bfloat16 *>(p.v) + base;
+
+    constexpr int STEP = kWarps * 16;
+    int rb = r0 + warp * 16;
+    KvFrag<D> fa, fb;
+    if (rb < r1) load_frag<D>(fa, kb, vb, rb, r1 - 1, g, t);
+    while (rb < r1) {
+        if (rb + STEP < r1) load_frag<D>(fb, kb, vb, rb + STEP, r1 - 1, g, t);
+        consume_frag<D>(fa, qreg, o, m, l, rb, r1, t, p.scale_log2e);
+        rb += STEP;
+        if (rb >= r1) break;
+        if (rb + STEP < r1) load_frag<D>(fa, kb, vb, rb + STEP, r1 - 1, g, t);
+        consume_frag<D>(fb, qreg, o, m, l, rb, r1, t, p.scale_log2e);
+        rb += STEP;
+    }
+
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (t == 0) { sm_m[warp * NH + g] = m; sm_l[warp * NH + g] = l; }
+    // accumulator tile h*8+j, element e  <->  column h*64 + (2t+e)*8 + j
+#pragma unroll
+    for (int h = 0; h < D / 64; h++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++)
+                sm_o[(warp * NH + g) * D + h * 64 + (2 * t + e) * 8 + j] = o[h * 8 + j][e];
+    __syncthreads();
+    merge_warps_and_emit<D>(p, sm_m, sm_l, sm_o, NH, p.G, b, hq0, chunk, n_chunks);
+}
+
+// ------------------------------------------------------------------ combine kernel
+// One warp per output row (sequence, query head).  parts[(part * rows + row) * W].
+// With seq_len given, the number of parts of a row is the number of chunks of its
+// sequence and rows with a single chunk are skipped (the decode kernel already wrote
+// them); without it every row merges n_parts records.
+struct CombineParams {
+    const float *parts;
+    const int32_t *seq_len;
+    void *out;
+    float *partials_out;
+    int out_dtype;
+    int n_parts, rows, D, W, Hq, chunk_rows, max_len;
+};
+
+__global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= p.rows) return;
+    int n = p.n_parts;
+    if (p.seq_len) {
+        int L = p.seq_len[row / p.Hq];
+        L = L < 0 ? 0 : (L > p.max_len ? p.max_len : L);
+        n = (L + p.chunk_rows - 1) / p.chunk_rows;
+        if (n <= 1) return;
+    }
+    const int64_t pstride = (int64_t)p.rows * p.W;
+    const float *rec = p.parts + (int64_t)row * p.W;
+    float M = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+        float li = rec[i * pstride + p.D + 1];
+        float mi = rec[i * pstride + p.D];
+        if (li > 0.f) M = fmaxf(M, mi);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float safe = (M == -INFINITY) ? 0.f : M;
+    float acc[8];  // D <= 256
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    float wsum = 0.f;
+    for (int i = 0; i < n; i++) {
+        const float *r = rec + i * pstride;
+        float li = r[p.D + 1];
+        float w = li > 0.f ? li * ex2((r[p.D] - safe) * kLog2e) : 0.f;
+        wsum += w;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            int d = lane + 32 * j;
+            if (d < p.D) acc[j] = fmaf(w, r[d], acc[j]);
+        }
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        int d = lane + 32 * j;
+        if (d < p.D) {
+            float val = acc[j] * inv;
+            if (p.out) store_from_f32(p.out, p.out_dtype, (int64_t)row * p.D + d, val);
+            if (p.partials_out) p.partials_out[(int64_t)row * p.W + d] = val;
+        }
+    }
+    if (p.partials_out && lane == 0) {
+        float *o = p.partials_out + (int64_t)row * p.W;
+        o[p.D] = M; o[p.D + 1] = wsum; o[p.D + 2] = 0.f; o[p.D + 3] = 0.f;
+    }
+}
+
+int g_force_kernel = 0;  // 0 auto, 1 generic, 2 mma (testing hook)
+
+int auto_chunk_rows(int B, int Hkv, int max_len) {
+    int64_t total = (int64_t)B * Hkv * max_len;
+    int64_t target = (int64_t)sm_count() * 32;
+    int64_t c = (total + target - 1) / target;
+    c = (c + 63) / 64 * 64;
+    if (c < 128) c = 128;
+    if (c > 8192) c = 8192;
+    return (int)c;
+}
+
+template <typename T, int D>
+void launch_generic(const DecodeParams &p, dim3 grid_base, cudaStream_t st) {
+    // GT query heads per CTA; groups > 1 only for G > 4
+    int G = p.G;
+    if (G == 1) { decode_generic_kernel<T, D, 1><<<grid_base, kWarps * 32, 0, st>>>(p); }
+    else if (G == 2) { decode_generic_kernel<T, D, 2><<<grid_base, kWarps * 32, 0, st>>>(p); }
+    else if (G == 3) { decode_generic_kernel<T, D, 3><<<grid_base, kWarps * 32, 0, st>>>(p); }
+    else {
+        dim3 grid = grid_base;
+        grid.y *= (G + 3) / 4;
+        decode_generic_kernel<T, D, 4><<<grid, kWarps * 32, 0, st>>>(p);
+    }
+}
+
+}  // namespace
+
+}  // namespace nimllm
+
+using namespace nimllm;
+
+extern "C" {
+
+void nimllm_attn_debug_force_decode_kernel(int which) { g_force_kernel = which; }
+
+size_t nimllm_attn_decode_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim,
+                                          int max_len, int chunk_rows) {
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || max_len <= 0) return 0;
+    if (chunk_rows <= 0) chunk_rows = auto_chunk_rows(batch, n_kv_head, max_len);
+    int max_chunks = (max_len + chunk_rows - 1) / chunk_rows;
+    if (max_chunks <= 1) return 0;
+    return (size_t)max_chunks * batch * n_head * rec_stride(head_dim) * sizeof(float);
+}
+
+int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const void *v_cache,
+                       int cache_dtype, const int64_t *kv_off, int64_t seq_stride,
+                       int64_t head_stride, const int32_t *seq_len, int max_len, void *out,
+                       int out_dtype, float *partials_out, int batch, int n_head,
+                       int n_kv_head, int head_dim, float scale, int chunk_rows,
+                       void *workspace, size_t workspace_bytes, void *stream) {
+    if (!q || !k_cache || !v_cache || (!out && !partials_out))
+        return fail(NIMLLM_ERR_ARG, "attn_decode: null q / cache / output pointer");
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head != 0 || max_len <= 0)
+        return fail(NIMLLM_ERR_ARG, "attn_decode: bad shape B=%d Hq=%d Hkv=%d max_len=%d", batch,
+                    n_head, n_kv_head, max_len);
+    if (!dtype_ok(q_dtype) || !dtype_ok(cache_dtype) || !dtype_ok(out_dtype))
+        return fail(NIMLLM_ERR_ARG, "attn_decode: unknown dtype");
+    if (head_dim != 64 && head_dim != 128)
+        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: head_dim %d (64 and 128 are built)", head_dim);
+    if (chunk_rows < 0 || (chunk_rows > 0 && chunk_rows % 64 != 0))
+        return fail(NIMLLM_ERR_ARG, "attn_decode: chunk_rows must be a multiple of 64");
+    if (batch > 65535) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: batch %d > 65535", batch);
+    if (chunk_rows == 0) chunk_rows = auto_chunk_rows(batch, n_kv_head, max_len);
+    const int max_chunks = (max_len + chunk_rows - 1) / chunk_rows;
+    const size_t need = nimllm_attn_decode_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(NIMLLM_ERR_WORKSPACE, "attn_decode: workspace %zu bytes, need %zu", workspace_bytes, need);
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
+        return fail(NIMLLM_ERR_ARG, "attn_decode: cache pointers must be 16-byte aligned");
+
+    DecodeParams p;
+    p.q = q; p.k = k_cache; p.v = v_cache; p.kv_off = kv_off;
+    p.seq_stride = seq_stride; p.head_stride = head_stride; p.seq_len = seq_len;
+    p.out = out; p.partials_out = partials_out; p.ws = (float *)workspace;
+    p.q_dtype = q_dtype; p.out_dtype = out_dtype; p.max_len = max_len; p.chunk_rows = chunk_rows;
+    p.B = batch; p.Hq = n_head; p.Hkv = n_kv_head; p.G = n_head / n_kv_head;
+    p.scale_log2e = scale * kLog2e;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    dim3 grid(max_chunks, n_kv_head, batch);
+    const bool mma_ok = cache_dtype == NIMLLM_BF16 && p.G <= 8;
+    if (g_force_kernel == 2 && !mma_ok)
+        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: mma kernel needs a bf16 cache and Hq/Hkv <= 8");
+    const bool use_mma = mma_ok && g_force_kernel != 1;
+    if (use_mma) {
+        if (head_dim == 64) decode_mma_kernel<64><<<grid, kWarps * 32, 0, st>>>(p);
+        else decode_mma_kernel<128><<<grid, kWarps * 32, 0, st>>>(p);
+    } else if (cache_dtype == NIMLLM_BF16) {
+        if (head_dim == 64) launch_generic<__nv_bfloat16, 64>(p, grid, st);
+        else launch_generic<__nv_bfloat16, 128>(p, grid, st);
+    } else {
+        if (head_dim == 64) launch_generic<float, 64>(p, grid, st);
+        else launch_generic<float, 128>(p, grid, st);
+    }
+    NIMLLM_CHECK_LAUNCH("attn_decode");
+
+    if (max_chunks > 1) {
+        CombineParams c;
+        c.parts = (const float *)workspace; c.seq_len = seq_len; c.out = out;
+        c.partials_out = partials_out; c.out_dtype = out_dtype;
+        c.n_parts = max_chunks; c.rows = batch * n_head; c.D = head_dim;
+        c.W = rec_stride(head_dim); c.Hq = n_head; c.chunk_rows = chunk_rows; c.max_len = max_len;
+        combine_kernel<<<(c.rows + 3) / 4, 128, 0, st>>>(c);
+        NIMLLM_CHECK_LAUNCH("attn_decode combine");
+    }
+    return NIMLLM_OK;
+}
+
+int nimllm_attn_combine(const float *parts, int n_parts, int rows, int head_dim, int rec_stride_,
+                        void *out, int out_dtype, float *partials_out, void *stream) {
+    if (!parts || (!out && !partials_out)) return fail(NIMLLM_ERR_ARG, "attn_combine: null pointer");
+    if (n_parts <= 0 || rows <= 0 || head_dim <= 0 || head_dim > 256 || rec_stride_ < head_dim + 2)
+        return fail(NIMLLM_ERR_ARG, "attn_combine: bad shape n_parts=%d rows=%d D=%d stride=%d", n_parts,
+                    rows, head_dim, rec_stride_);
+    if (out && !dtype_ok(out_dtype)) return fail(NIMLLM_ERR_ARG, "attn_combine: unknown dtype");
+    if (partials_out && rec_stride_ != rec_stride(head_dim))
+        return fail(NIMLLM_ERR_ARG, "attn_combine: partials_out needs rec_stride == head_dim + 4");
+    CombineParams c;
+    c.parts = parts; c.seq_len = nullptr; c.out = out; c.partials_out = partials_out;
+    c.out_dtype = out_dtype; c.n_parts = n_parts; c.rows = rows; c.D = head_dim; c.W = rec_stride_;
+    c.Hq = 1; c.chunk_rows = 1; c.max_len = 0;
+    combine_kernel<<<(rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(c);
+    NIMLLM_CHECK_LAUNCH("attn_combine");
+    return NIMLLM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+// legacy_abi.cu -- the reference's unfused attention-path launchers, under their own
+// names and argument lists (src/kernels.cu, bound in src/gpu.nim:227-248,274-276,309-311),
+// so that code which still walks the unfused sequence (backward(), the test programs)
+// links against this library alone.  Same semantics: void return, legacy default stream,
+// fp32.  The kernels are new: vector accesses where the shapes allow, warp-shuffle
+// reductions in the softmax, and the fused fp32 flash kernel behind gpu_flash_attn_fwd.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace nimllm {
+namespace {
+
+// src/kernels.cu:399-415 k_rope with sign = +1: pairs (f, f + D/2), table row = token row.
+__global__ void legacy_rope_kernel(float *data, const float *cos_tab, const float *sin_tab,
+                                   int seq_len, int n_embd, int n_head, int head_dim) {
+    const int half = head_dim / 2;
+    const int64_t total = (int64_t)seq_len * n_head * half;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        int f = (int)(idx % half);
+        int64_t r = idx / half;
+        int h = (int)(r % n_head);
+        int64_t pos = r / n_head;
+        float *x = data + pos * n_embd + (int64_t)h * head_dim;
+        float c = cos_tab[pos * half + f], s = sin_tab[pos * half + f];
+        float x0 = x[f], x1 = x[f + half];
+        x[f] = x0 * c - x1 * s;
+        x[f + half] = x0 * s + x1 * c;
+    }
+}
+
+// src/kernels.cu:349-365: dense [S, D] <-> column block col0.. of [S, width]
+template <bool kGather>
+__global__ void legacy_head_copy_kernel(const float *src, float *dst, int col0, int seq_len,
+                                        int width, int head_dim) {
+    const int64_t total = (int64_t)seq_len * head_dim;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        int64_t pos = idx / head_dim;
+        int j = (int)(idx % head_dim);
+        if (kGather) dst[idx] = src[pos * width + col0 + j];
+        else dst[pos * width + col0 + j] = src[idx];
+    }
+}
+
+// src/kernels.cu:248-258
+__global__ void legacy_causal_mask_kernel(float *scores, float scale, int seq_len) {
+    const int64_t total = (int64_t)seq_len * seq_len;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        int row = (int)(idx / seq_len), col = (int)(idx % seq_len);
+        if (col > row) scores[idx] = -1e9f;
+        else scores[idx] *= scale;
+    }
+}
+
+// src/kernels.cu:145-149
+__global__ void legacy_scale_kernel(const float *x, float s, float *y, int n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = x[i] * s;
+}
+
+// src/kernels.cu:267-303: row softmax, max-subtracted, expf, times reciprocal of the sum.
+// One CTA per row; reductions by warp shuffles plus one shared-memory hop.
+__global__ void __launch_bounds__(256) legacy_softmax_kernel(const float *x, float *y, int rows,
+                                                             int cols) {
+    __shared__ float red[8];
+    const int row = blockIdx.x;
+    if (row >= rows) return;
+    const float *xi = x + (int64_t)row * cols;
+    float *yi = y + (int64_t)row * cols;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+
+    float mx = -FLT_MAX;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) mx = fmaxf(mx, xi[j]);
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < nw; w++) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+        float e = expf(xi[j] - mx);
+        yi[j] = e;
+        sum += e;
+    }
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    sum = 0.f;
+    for (int w = 0; w < nw; w++) sum += red[w];
+    const float inv = 1.0f / sum;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) yi[j] *= inv;
+}
+
+inline int grid_for(int64_t n) {
+    int64_t blocks = (n + 255) / 256;
+    int64_t cap = (int64_t)sm_count() * 16;
+    return (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+
+}  // namespace
+}  // namespace nimllm
+
+using namespace nimllm;
+
+extern "C" {
+
+void gpu_rope_fwd(float *data, const float *cos_tab, const float *sin_tab, int seq_len,
+                  int n_embd, int n_head, int head_dim) {
+    int64_t n = (int64_t)seq_len * n_head * (head_dim / 2);
+    if (n <= 0) return;
+    legacy_rope_kernel<<<grid_for(n), 256>>>(data, cos_tab, sin_tab, seq_len, n_embd, n_head, head_dim);
+}
+
+void gpu_extract_head(const float *src, float *dst, int h, int seq_len, int n_embd, int head_dim) {
+    int64_t n = (int64_t)seq_len * head_dim;
+    if (n <= 0) return;
+    legacy_head_copy_kernel<true><<<grid_for(n), 256>>>(src, dst, h * head_dim, seq_len, n_embd, head_dim);
+}
+
+void gpu_insert_head(const float *src, float *dst, int h, int seq_len, int n_embd, int head_dim) {
+    int64_t n = (int64_t)seq_len * head_dim;
+    if (n <= 0) return;
+    legacy_head_copy_kernel<false><<<grid_for(n), 256>>>(src, dst, h * head_dim, seq_len, n_embd, head_dim);
+}
+
+void gpu_extract_kv_head(const float *src, float *dst, int qHead, int kvRepeat, int seq_len,
+                         int n_kv_dim, int head_dim) {
+    int64_t n = (int64_t)seq_len * head_dim;
+    if (n <= 0 || kvRepeat <= 0) return;
+    legacy_head_copy_kernel<true><<<grid_for(n), 256>>>(src, dst, (qHead / kvRepeat) * head_dim, seq_len,
+                                                         n_kv_dim, head_dim);
+}
+
+void gpu_causal_mask(float *scores, float scale, int seq_len) {
+    int64_t n = (int64_t)seq_len * seq_len;
+    if (n <= 0) return;
+    legacy_causal_mask_kernel<<<grid_for(n), 256>>>(scores, scale, seq_len);
+}
+
+void gpu_scale(const float *x, float s, float *y, int n) {
+    if (n <= 0) return;
+    legacy_scale_kernel<<<grid_for(n), 256>>>(x, s, y, n);
+}
+
+void gpu_softmax_fwd(const float *x, float *y, int rows, int cols) {
+    if (rows <= 0 || cols <= 0) return;
+    int threads = cols >= 256 ? 256 : (cols <= 32 ? 32 : ((cols + 31) / 32) * 32);
+    legacy_softmax_kernel<<<rows, threads>>>(x, y, rows, cols);
+}
+
+void gpu_flash_attn_fwd(const float *Q, const float *K, const float *V, float *O, int S, int hd,
+                        float scale, int causal) {
+    if (S <= 0) return;
+    launch_prefill_f32(Q, K, V, O, nullptr, 1, S, 1, 1, hd, scale, causal, 0);
+}
+
+}  // extern "C"

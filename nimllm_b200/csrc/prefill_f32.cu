@@ -1,0 +1,155 @@
+// prefill_f32.cu -- causal GQA attention in fp32 on the CUDA cores.
+//
+// The <= 1e-4 parity path for the reference's fp32 forward() attention block
+// (src/model.nim:498-508: per query head gather, cublasSgemm_v2 QK^T, gpu_causal_mask,
+// gpu_softmax_fwd, cublasSgemm_v2 PV, scatter).  TF32 tensor-core products cannot hold
+// 1e-4, so this path multiplies and accumulates in fp32.  It is flash-style: no S x S
+// matrix is written; K/V tiles of 32 rows are staged in shared memory and an online
+// softmax keeps (max, sum, output) per query row.  Heads are read and written in place in
+// the reference's [tokens, heads*D] layout, which removes the gather / scatter kernels
+// (src/kernels.cu:349-365,439-449).  Also backs the reference's unused single-head entry
+// gpu_flash_attn_fwd (src/kernels.cu:703-755).
+#include "common.cuh"
+
+namespace nimllm {
+
+namespace {
+
+constexpr int BM = 16;  // query rows per CTA (4 per warp)
+constexpr int BN = 32;  // key rows per tile (one per lane)
+
+template <int D>
+__global__ void __launch_bounds__(128) prefill_f32_kernel(const float *__restrict__ q,
+                                                          const float *__restrict__ k,
+                                                          const float *__restrict__ v,
+                                                          float *__restrict__ out,
+                                                          float *__restrict__ lse, int S, int Hq,
+                                                          int Hkv, float scale_log2e, int causal) {
+    constexpr int RPW = BM / 4;  // rows per warp
+    constexpr int DPL = D / 32;  // output columns per lane
+    __shared__ __align__(16) float Qs[BM][D];
+    __shared__ float Ks[BN][D + 1];
+    __shared__ __align__(16) float Vs[BN][D];
+    __shared__ __align__(16) float Ps[4][BN][RPW];
+
+    const int tile_m = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / (Hq / Hkv);
+    const int E = Hq * D, Ekv = Hkv * D;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = tile_m * BM;
+    const float *qb = q + (int64_t)b * S * E + (int64_t)h * D;
+    const float *kb = k + (int64_t)b * S * Ekv + (int64_t)kvh * D;
+    const float *vb = v + (int64_t)b * S * Ekv + (int64_t)kvh * D;
+
+    for (int i = threadIdx.x; i < BM * D / 4; i += 128) {
+        int r = i / (D / 4), c = (i % (D / 4)) * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < S) x = *reinterpret_cast<const float4 *>(qb + (int64_t)(row0 + r) * E + c);
+        *reinterpret_cast<float4 *>(&Qs[r][c]) = x;
+    }
+
+    float m[RPW], l[RPW], o[RPW][DPL];
+#pragma unroll
+    for (int r = 0; r < RPW; r++) {
+        m[r] = -INFINITY; l[r] = 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; d++) o[r][d] = 0.f;
+    }
+
+    const int last_row = min(row0 + BM, S) - 1;
+    const int kv_end = causal ? last_row + 1 : S;  // keys [0, kv_end)
+    for (int j0 = 0; j0 < kv_end; j0 += BN) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < BN * D / 4; i += 128) {
+            int r = i / (D / 4), c = (i % (D / 4)) * 4;
+            float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), vx = kx;
+            if (j0 + r < S) {
+                kx = *reinterpret_cast<const float4 *>(kb + (int64_t)(j0 + r) * Ekv + c);
+                vx = *reinterpret_cast<const float4 *>(vb + (int64_t)(j0 + r) * Ekv + c);
+            }
+            Ks[r][c] = kx.x; Ks[r][c + 1] = kx.y; Ks[r][c + 2] = kx.z; Ks[r][c + 3] = kx.w;
+            *reinterpret_cast<float4 *>(&Vs[r][c]) = vx;
+        }
+        __syncthreads();
+
+        // scores of this lane's key against the warp's RPW query rows
+        float s[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; r++) s[r] = 0.f;
+#pragma unroll 4
+        for (int d = 0; d < D; d += 4) {
+            float k0 = Ks[lane][d], k1 = Ks[lane][d + 1], k2 = Ks[lane][d + 2], k3 = Ks[lane][d + 3];
+#pragma unroll
+            for (int r = 0; r < RPW; r++) {
+                float4 qv = *reinterpret_cast<const float4 *>(&Qs[warp * RPW + r][d]);
+                s[r] = fmaf(qv.x, k0, s[r]); s[r] = fmaf(qv.y, k1, s[r]);
+                s[r] = fmaf(qv.z, k2, s[r]); s[r] = fmaf(qv.w, k3, s[r]);
+            }
+        }
+        const int key = j0 + lane;
+        float p[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; r++) {
+            const int qi = row0 + warp * RPW + r;
+            const bool valid = key < S && (!causal || key <= qi);
+            float sv = valid ? s[r] * scale_log2e : -INFINITY;
+            float mx = sv;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            float m_new = fmaxf(m[r], mx);
+            float safe = (m_new == -INFINITY) ? 0.f : m_new;
+            float corr = ex2(m[r] - safe);
+            p[r] = ex2(sv - safe);
+            float sum = p[r];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            l[r] = l[r] * corr + sum;
+            m[r] = m_new;
+#pragma unroll
+            for (int d = 0; d < DPL; d++) o[r][d] *= corr;
+        }
+        __syncwarp();
+        if (RPW == 4) *reinterpret_cast<float4 *>(&Ps[warp][lane][0]) = make_float4(p[0], p[1], p[2], p[3]);
+        __syncwarp();
+#pragma unroll 8
+        for (int j = 0; j < BN; j++) {
+            float4 pj = *reinterpret_cast<const float4 *>(&Ps[warp][j][0]);
+#pragma unroll
+            for (int d = 0; d < DPL; d++) {
+                float vv = Vs[j][lane + 32 * d];
+                o[0][d] = fmaf(pj.x, vv, o[0][d]); o[1][d] = fmaf(pj.y, vv, o[1][d]);
+                o[2][d] = fmaf(pj.z, vv, o[2][d]); o[3][d] = fmaf(pj.w, vv, o[3][d]);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < RPW; r++) {
+        const int qi = row0 + warp * RPW + r;
+        if (qi >= S) continue;
+        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; d++)
+            out[((int64_t)b * S + qi) * E + (int64_t)h * D + lane + 32 * d] = o[r][d] * inv;
+        if (lse && lane == 0)
+            lse[((int64_t)b * Hq + h) * S + qi] = l[r] > 0.f ? (m[r] + log2f(l[r])) * kLn2 : -INFINITY;
+    }
+}
+
+}  // namespace
+
+int launch_prefill_f32(const float *q, const float *k, const float *v, float *out, float *lse,
+                       int B, int S, int Hq, int Hkv, int D, float scale, int causal,
+                       cudaStream_t st) {
+    static_assert(BM == 16, "Ps stores 4 rows per warp as one float4");
+    dim3 grid((S + BM - 1) / BM, Hq, B);
+    const float sl = scale * kLog2e;
+    if (D == 32) prefill_f32_kernel<32><<<grid, 128, 0, st>>>(q, k, v, out, lse, S, Hq, Hkv, sl, causal);
+    else if (D == 64) prefill_f32_kernel<64><<<grid, 128, 0, st>>>(q, k, v, out, lse, S, Hq, Hkv, sl, causal);
+    else if (D == 128) prefill_f32_kernel<128><<<grid, 128, 0, st>>>(q, k, v, out, lse, S, Hq, Hkv, sl, causal);
+    else return fail(NIMLLM_ERR_UNSUPPORTED, "prefill fp32: head_dim %d (32, 64, 128 are built)", D);
+    NIMLLM_CHECK_LAUNCH("attn_prefill fp32");
+    return NIMLLM_OK;
+}
+
+}  // namespace nimllm

@@ -1,0 +1,41 @@
+"""Shared helpers of the test suite: seeded synthetic inputs and the error definitions.
+
+Error definitions (stated once, used by every parity test):
+  rel_err(a, b)  = max|a - b| / max|b|                       (per tensor)
+  elem_err(a, b) = max( |a - b| / max(|b|, rms(b)) )         (per element, floored at rms)
+Bounds: fp32 paths <= 1e-4 against the reference fp32 arithmetic; bf16 paths <= 2e-2
+against float64 ground truth computed on the same bf16-rounded inputs.
+"""
+import numpy as np
+
+TOL_F32 = 1e-4
+TOL_BF16 = 2e-2
+
+# seeds of the synthetic configurations: 20250 + configuration number (1-based)
+SEED_C1, SEED_C2, SEED_C3, SEED_C4, SEED_C5 = 20251, 20252, 20253, 20254, 20255
+
+
+def rng(seed, stream=0):
+    return np.random.Generator(np.random.Philox(key=seed, counter=[stream, 0, 0, 0]))
+
+
+def normal(seed, stream, shape, scale=1.0):
+    return (rng(seed, stream).standard_normal(shape, dtype=np.float32) * np.float32(scale)).astype(np.float32)
+
+
+def rel_err(a, b):
+    a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def elem_err(a, b):
+    a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
+    rms = float(np.sqrt(np.mean(b * b)))
+    return float((np.abs(a - b) / np.maximum(np.abs(b), max(rms, 1e-30))).max())
+
+
+def assert_close(a, b, tol, what=""):
+    r, e = rel_err(a, b), elem_err(a, b)
+    assert np.isfinite(np.asarray(a, np.float64)).all(), f"{what}: non-finite values"
+    assert r <= tol and e <= tol, f"{what}: rel_err {r:.3e}, elem_err {e:.3e} > {tol:.1e}"
+    return r, e
