@@ -20,6 +20,8 @@
 //   decode_generic_kernel  fp32 or bf16 cache, fp32 FMA on the CUDA cores: the <= 1e-4
 //                          parity path for the reference's fp32 cache, and the fallback
 //                          for group sizes the mma kernel does not take.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace nimllm {
@@ -36,7 +38,7 @@ struct DecodeParams {
     const int32_t *seq_len;
     void *out;
     float *partials_out;
-    float *ws;
+    float *ws;               // partial records of split sequences
     int q_dtype, out_dtype;
     int max_len, chunk_rows;
     int B, Hq, Hkv, G;
@@ -69,7 +71,9 @@ __device__ __forceinline__ void emit(const DecodeParams &p, int D, int b, int hq
     }
 }
 
-// Merge of the per-warp states left in shared memory; NH heads, D columns.
+// Merge of the per-warp states left in shared memory (NH heads, D columns).  (Letting the
+// last-arriving CTA of a split sequence merge the chunks in-kernel was measured slower than
+// the separate combine launch: its serial tail costs more than the launch it saves.)
 template <int D>
 __device__ __forceinline__ void merge_warps_and_emit(const DecodeParams &p, const float *sm_m,
                                                      const float *sm_l, const float *sm_o,
@@ -119,7 +123,6 @@ __global__ void __launch_bounds__(kWarps * 32) decode_generic_kernel(DecodeParam
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int lir = lane % LPR, rw = lane / LPR;
-    const int wid = warp * RPW + rw;
     const int g0 = grp * GT;
     const int ng = min(GT, p.G - g0);
     const int hq0 = kvh * p.G + g0;
@@ -146,11 +149,13 @@ __global__ void __launch_bounds__(kWarps * 32) decode_generic_kernel(DecodeParam
     const T *kb = reinterpret_cast<const T *>(p.k) + base;
     const T *vb = reinterpret_cast<const T *>(p.v) + base;
 
-    for (int rb = r0 + wid; rb < r1; rb += NWK * U) {
+    // rb is warp-uniform (the shuffles below need the whole warp in the loop); lane group rw
+    // of warp w owns rows rb + rw + u*NWK
+    for (int rb = r0 + warp * RPW; rb < r1; rb += NWK * U) {
         uint4 kx[U], vx[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            int row = min(rb + u * NWK, r1 - 1);
+            int row = min(rb + rw + u * NWK, r1 - 1);
             kx[u] = ldg_stream(kb + (int64_t)row * D);
             vx[u] = ldg_stream(vb + (int64_t)row * D);
         }
@@ -179,7 +184,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_generic_kernel(DecodeParam
             float mx = -INFINITY;
 #pragma unroll
             for (int u = 0; u < U; u++) {
-                if (rb + u * NWK >= r1) s[u][g] = -INFINITY;
+                if (rb + rw + u * NWK >= r1) s[u][g] = -INFINITY;
                 mx = fmaxf(mx, s[u][g]);
             }
             float m_new = fmaxf(m[g], mx);
@@ -333,8 +338,10 @@ __device__ __forceinline__ void consume_frag(const KvFrag<D> &f, const uint32_t 
         }
 }
 
-template <int D>
-__global__ void __launch_bounds__(kWarps * 32) decode_mma_kernel(DecodeParams p) {
+// MINB = resident CTAs per SM the register budget is held to (3 at D = 64, 2 at D = 128;
+// forcing 4 at D = 64 spilled and measured no faster).
+template <int D, int MINB>
+__global__ void __launch_bounds__(kWarps * 32, MINB) decode_mma_kernel(DecodeParams p) {
     constexpr int NH = 8;  // head rows kept (G <= 8)
     __shared__ float sm_m[kWarps * NH], sm_l[kWarps * NH];
     __shared__ float sm_o[kWarps * NH * D];
@@ -471,13 +478,16 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
 
 int g_force_kernel = 0;  // 0 auto, 1 generic, 2 mma (testing hook)
 
+
 int auto_chunk_rows(int B, int Hkv, int max_len) {
     int64_t total = (int64_t)B * Hkv * max_len;
-    int64_t target = (int64_t)sm_count() * 32;
+    // measured on B200: long chunks win (fewer CTA start-ups and partial records) until the
+    // grid drops below a few waves of the ~3 resident CTAs per SM
+    int64_t target = (int64_t)sm_count() * 8;
     int64_t c = (total + target - 1) / target;
     c = (c + 63) / 64 * 64;
-    if (c < 128) c = 128;
-    if (c > 8192) c = 8192;
+    if (c < 256) c = 256;
+    if (c > 4096) c = 4096;
     return (int)c;
 }
 
@@ -539,11 +549,14 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
         return fail(NIMLLM_ERR_WORKSPACE, "attn_decode: workspace %zu bytes, need %zu", workspace_bytes, need);
     if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
         return fail(NIMLLM_ERR_ARG, "attn_decode: cache pointers must be 16-byte aligned");
+    if (need > 0 && ((uintptr_t)workspace & 15))
+        return fail(NIMLLM_ERR_ARG, "attn_decode: workspace must be 16-byte aligned");
 
     DecodeParams p;
     p.q = q; p.k = k_cache; p.v = v_cache; p.kv_off = kv_off;
     p.seq_stride = seq_stride; p.head_stride = head_stride; p.seq_len = seq_len;
-    p.out = out; p.partials_out = partials_out; p.ws = (float *)workspace;
+    p.out = out; p.partials_out = partials_out;
+    p.ws = (float *)workspace;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype; p.max_len = max_len; p.chunk_rows = chunk_rows;
     p.B = batch; p.Hq = n_head; p.Hkv = n_kv_head; p.G = n_head / n_kv_head;
     p.scale_log2e = scale * kLog2e;
@@ -555,8 +568,8 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
         return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: mma kernel needs a bf16 cache and Hq/Hkv <= 8");
     const bool use_mma = mma_ok && g_force_kernel != 1;
     if (use_mma) {
-        if (head_dim == 64) decode_mma_kernel<64><<<grid, kWarps * 32, 0, st>>>(p);
-        else decode_mma_kernel<128><<<grid, kWarps * 32, 0, st>>>(p);
+        if (head_dim == 64) decode_mma_kernel<64, 3><<<grid, kWarps * 32, 0, st>>>(p);
+        else decode_mma_kernel<128, 2><<<grid, kWarps * 32, 0, st>>>(p);
     } else if (cache_dtype == NIMLLM_BF16) {
         if (head_dim == 64) launch_generic<__nv_bfloat16, 64>(p, grid, st);
         else launch_generic<__nv_bfloat16, 128>(p, grid, st);
@@ -568,7 +581,7 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
 
     if (max_chunks > 1) {
         CombineParams c;
-        c.parts = (const float *)workspace; c.seq_len = seq_len; c.out = out;
+        c.parts = p.ws; c.seq_len = seq_len; c.out = out;
         c.partials_out = partials_out; c.out_dtype = out_dtype;
         c.n_parts = max_chunks; c.rows = batch * n_head; c.D = head_dim;
         c.W = rec_stride(head_dim); c.Hq = n_head; c.chunk_rows = chunk_rows; c.max_len = max_len;

@@ -20,15 +20,18 @@ def bf16_bits(t):
 
 
 def ragged_cache(seed, lens, Hkv, D, dtype, normal, pad_rows=0):
-    """Packed ragged KV: sequence b is a [Hkv, cap_b, D] block, blocks laid end to end.
-    Returns numpy fp32 arrays (already rounded to dtype), offsets and head strides."""
+    """KV for a ragged batch: sequence b owns a [Hkv, cap, D] block (cap = longest sequence +
+    pad_rows, so the head stride is uniform) that starts at an arbitrary 8-element-aligned
+    offset kv_off[b]; the gaps between blocks differ so that kv_off is exercised.
+    Returns fp32 arrays already rounded to dtype, the offsets and per-sequence head strides."""
     B = len(lens)
-    off = np.zeros(B, np.int64); hs = np.zeros(B, np.int64)
+    cap = max(int(max(lens)) + pad_rows, 1)
+    off = np.zeros(B, np.int64)
     total = 0
     for b in range(B):
-        cap = max(int(lens[b]) + pad_rows, 1)
-        off[b] = total; hs[b] = cap * D
-        total += Hkv * cap * D
+        off[b] = total
+        total += Hkv * cap * D + 8 * ((b * 5) % 7)
+    hs = np.full(B, cap * D, np.int64)
     k = normal(seed, 10, (total,)); v = normal(seed, 11, (total,))
     if dtype == torch.bfloat16:
         k = O.from_bf16(O.to_bf16(k)); v = O.from_bf16(O.to_bf16(v))

@@ -27,7 +27,8 @@ def _run(seed, lens, Hq, Hkv, D, kv_dtype, chunk_rows, force=0, q_dtype=torch.fl
     _lib.lib().nimllm_attn_debug_force_decode_kernel(force)
     out, rec = A.decode_batch(dev(q, q_dtype), dev(k, kv_dtype), dev(v, kv_dtype), n_head=Hq, n_kv_head=Hkv,
                               head_dim=D, max_len=int(max(max(lens), 1)), seq_len=dev(np.asarray(lens, np.int32)),
-                              kv_off=dev(off), scale=scale, chunk_rows=chunk_rows, partials=True)
+                              kv_off=dev(off), head_stride=int(hs[0]), scale=scale, chunk_rows=chunk_rows,
+                              partials=True)
     torch.cuda.synchronize()
     ref32 = O.decode_batch(q, k, v, off, hs, np.asarray(lens, np.int32), Hq, Hkv, D, scale)
     ref64, m, l = O.decode_batch(q, k, v, off, hs, np.asarray(lens, np.int32), Hq, Hkv, D, scale, acc64=True,
@@ -68,7 +69,8 @@ def test_mma_kernel_is_tight_when_p_is_exact():
     q = normal(103, 12, (6, Hq * D))
     _lib.lib().nimllm_attn_debug_force_decode_kernel(2)
     out = A.decode_batch(dev(q), dev(k, torch.bfloat16), dev(v, torch.bfloat16), n_head=Hq, n_kv_head=Hkv,
-                         head_dim=D, max_len=1, seq_len=dev(np.asarray(lens, np.int32)), kv_off=dev(off))
+                         head_dim=D, max_len=1, seq_len=dev(np.asarray(lens, np.int32)), kv_off=dev(off),
+                         head_stride=int(hs[0]))
     out = host(out).reshape(6, Hq, D)
     for b in range(6):
         for h in range(Hq):
@@ -83,6 +85,7 @@ def test_zero_length_and_missing_seq_len():
         assert not out[0].any() and not out[2].any()
         assert_close(out, ref64, TOL_BF16 if dt == torch.bfloat16 else TOL_F32, "zero-length rows")
     # seq_len = NULL: every sequence attends max_len rows of a uniform cache
+    _lib.lib().nimllm_attn_debug_force_decode_kernel(0)
     B, L = 3, 77
     kv = normal(105, 0, (2, B, Hkv, 80, D))
     q = normal(105, 1, (B, Hq * D))
@@ -114,13 +117,15 @@ def test_split_invariance_and_determinism_c3_shape():
     again = host(A.decode_batch(q, kc, vc, chunk_rows=0, **args))
     np.testing.assert_array_equal(outs[0], again)
     for chunk in (256, 1024, 4096):
-        assert_close(outs[chunk], outs[0], 2e-3, f"chunk {chunk} vs auto")
+        # the bf16 rounding of P depends on the running maximum, hence on the split
+        assert_close(outs[chunk], outs[0], TOL_BF16, f"chunk {chunk} vs auto")
     sample = [0, 17, 255, int(np.argmax(lens)), int(np.argmin(lens))]
     kb, vb = bf16_bits(kc[sample]).reshape(-1), bf16_bits(vc[sample]).reshape(-1)
     soff = np.arange(len(sample), dtype=np.int64) * Hkv * cap * D
     ref = O.decode_batch(host(q[sample]), kb, vb, soff, np.full(len(sample), cap * D, np.int64), lens[sample],
                          Hq, Hkv, D, 0.125, acc64=True)
-    assert_close(outs[0][sample], ref, TOL_BF16, "C3 sample vs fp64")
+    for chunk in outs:
+        assert_close(outs[chunk][sample], ref, TOL_BF16, f"C3 sample vs fp64, chunk {chunk}")
 
 
 def test_kv_sequence_shards_combine_to_unsharded_c5_shape():

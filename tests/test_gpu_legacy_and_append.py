@@ -17,8 +17,8 @@ def test_legacy_launchers_match_oracle():
     E, Ekv = Hq * D, Hkv * D
     x = normal(400, 0, (S, E))
     cos, sin = O.rope_tables(S, D, 10000.0)
-    d = dev(x)
-    L.gpu_rope_fwd(d.data_ptr(), dev(cos).data_ptr(), dev(sin).data_ptr(), S, E, Hq, D)
+    d, dcos, dsin = dev(x), dev(cos), dev(sin)      # named: a temporary would be freed before the launch
+    L.gpu_rope_fwd(d.data_ptr(), dcos.data_ptr(), dsin.data_ptr(), S, E, Hq, D)
     ref = O.rope_fwd(x.copy(), cos, sin, Hq, D)
     assert_close(host(d), ref, 1e-6, "gpu_rope_fwd")
 
@@ -44,10 +44,12 @@ def test_legacy_launchers_match_oracle():
     for cols in (1, 31, 32, 33, 300, 1025):
         xs = normal(401, cols, (3, cols), 2.0)
         ys = torch.zeros(3, cols, device="cuda")
-        L.gpu_softmax_fwd(dev(xs).data_ptr(), ys.data_ptr(), 3, cols)
+        dxs = dev(xs)
+        L.gpu_softmax_fwd(dxs.data_ptr(), ys.data_ptr(), 3, cols)
         assert_close(host(ys), O.softmax_fwd(xs), 1e-6, f"softmax cols={cols}")
     z = torch.zeros(S * S, device="cuda")
-    L.gpu_scale(dev(sc).data_ptr(), 0.3, z.data_ptr(), S * S)
+    dsc2 = dev(sc)
+    L.gpu_scale(dsc2.data_ptr(), 0.3, z.data_ptr(), S * S)
     np.testing.assert_array_equal(host(z), (sc * np.float32(0.3)).reshape(-1))
     torch.cuda.synchronize()
 
@@ -58,8 +60,8 @@ def test_gpu_flash_attn_fwd_single_head(causal):
     S, D = 45, 64
     q = normal(402, 0, (S, D)); k = normal(402, 1, (S, D)); v = normal(402, 2, (S, D))
     o = torch.zeros(S, D, device="cuda")
-    _lib.lib().gpu_flash_attn_fwd(dev(q).data_ptr(), dev(k).data_ptr(), dev(v).data_ptr(), o.data_ptr(), S, D,
-                                  0.125, causal)
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    _lib.lib().gpu_flash_attn_fwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), o.data_ptr(), S, D, 0.125, causal)
     torch.cuda.synchronize()
     if causal:
         ref = O.prefill_f64(q[None], k[None], v[None], 1, 1, D, 0.125)[0]
@@ -133,7 +135,8 @@ def test_kvcache_handle_api():
     assert L.nimllm_kvcache_k(h, 2) is None
     # append through the ABI into layer 1, then read the block back with a plain copy
     k = normal(405, 0, (3, 1, 128)); v = normal(405, 1, (3, 1, 128))
-    _lib.check(L.nimllm_rope_append(None, 0, dev(k).data_ptr(), dev(v).data_ptr(), _lib.F32, 0, None, None, None, 5,
+    dk, dv = dev(k), dev(v)
+    _lib.check(L.nimllm_rope_append(None, 0, dk.data_ptr(), dv.data_ptr(), _lib.F32, 0, None, None, None, 5,
                                     k1, L.nimllm_kvcache_v(h, 1), _lib.F32, None, L.nimllm_kvcache_seq_stride(h),
                                     L.nimllm_kvcache_head_stride(h), 0, 16, 3, 1, 2, 64, None))
     L.nimllm_kvcache_set_pos(h, 6)
