@@ -51,6 +51,7 @@ PROTOTYPES = {
 # testing hooks exported by the library but not part of include/nimllm_attn.h
 _EXTRA = {
     "nimllm_attn_debug_force_decode_kernel": (None, [i32]),
+    "nimllm_attn_debug_prefill_dump": (None, [vp]),
 }
 
 

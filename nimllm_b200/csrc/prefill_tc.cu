@@ -1,9 +1,600 @@
-// prefill_tc.cu -- placeholder until the tcgen05 kernel lands.
+// prefill_tc.cu -- causal GQA prefill attention on the Blackwell tensor cores (bf16, D = 128).
+//
+// Replaces, for bf16 activations, the per-query-head loop of forward() in the reference
+// (src/model.nim:498-508: gather, cublasSgemm_v2 QK^T, gpu_causal_mask, gpu_softmax_fwd,
+// cublasSgemm_v2 PV, scatter -- two S x S matrices through HBM per head) with one
+// flash-style kernel: no score matrix leaves the SM.
+//
+// One CTA owns 256 consecutive query rows of one (sequence, query head) as two 128-row
+// tiles and walks the KV sequence in 128-row tiles up to the causal diagonal.
+//
+//   warp 8      TMA producer: Q tiles once, then K_j / V_j tiles into a 2-stage shared-memory
+//               ring (cp.async.bulk.tensor, 128-byte swizzle, mbarrier transaction counts).
+//   warp 9      MMA issuer (one lane): S_w = Q_w K_j^T and O_w += P_w V_j as tcgen05.mma
+//               (cta_group::1, kind::f16, M = N = 128, fp32 accumulators in TMEM).  S and O of
+//               both query tiles take the 512 TMEM columns: S0 S1 O0 O1, 128 columns each.
+//   warps 0-3 / 4-7   softmax group of query tile 0 / 1: one thread per query row (= one TMEM
+//               lane): tcgen05.ld the row of S, running max / sum, P = exp2(S*c - m) rounded
+//               to bf16 and stored back over S (tcgen05.st), which the PV MMA reads as its A
+//               operand straight from TMEM.  O is rescaled only when a row maximum grows by
+//               more than 2^8 (the exact softmax is restored by the final division by the
+//               running sum), then normalised, rounded and written in the epilogue.
+//
+// While one group computes its softmax the tensor pipe works on the other tile's S and PV.
+// RoPE: K arrives already rotated (the pre-pass that also fills the KV cache rotates it, as
+// the reference stores K after RoPE); Q is rotated by the pre-pass when the caller keeps it
+// (save_cache), otherwise by this kernel's prologue while staging Q in shared memory.
+//
+// Every wait on an mbarrier is bounded: after ~2 s without progress the CTA raises an abort
+// flag, all roles leave their loops, TMEM is released and a status word is set.
+#include <cuda.h>
+
 #include "common.cuh"
+
 namespace nimllm {
-size_t prefill_tc_workspace_bytes(int, int, int, int, int) { return 0; }
-int launch_prefill_tc(void *, const void *, const void *, void *, float *, const float *, const float *, int, int,
-                      int, int, int, int, int, float, void *, size_t, cudaStream_t) {
-    return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill: bf16 tensor-core kernel not built");
+
+namespace {
+
+constexpr int kD = 128;            // head_dim
+constexpr int kBM = 128;           // query rows per tile (= TMEM lanes)
+constexpr int kBN = 128;           // KV rows per tile
+constexpr int kStages = 2;
+constexpr int kTileBytes = kBN * kD * 2;     // 32 KiB: one [128 x 128] bf16 tile = two swizzled 64-column boxes
+constexpr int kBoxBytes = kTileBytes / 2;    // 16 KiB
+constexpr int kThreads = 384;                // 8 softmax warps, producer, MMA issuer, 2 idle
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;    // log2 units
+
+struct Smem {
+    // tiles first: 1024-byte alignment is required by the 128-byte swizzle atoms
+    uint8_t q[2][kTileBytes];
+    uint8_t k[kStages][kTileBytes];
+    uint8_t v[kStages][kTileBytes];
+    uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t s_full[2], p_ready[2], o_full[2], drain;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+struct PrefillParams {
+    __nv_bfloat16 *q;        // [B, S, Hq*D], read by the prologue when it rotates Q
+    __nv_bfloat16 *out;      // [B, S, Hq*D]
+    float *lse;              // [B, Hq, S] or null
+    const float *cos_tab, *sin_tab;  // rows pos0.. used when rotate_q
+    int *status;             // device status word: 0 ok, 1 a bounded wait gave up
+    float *dbg;              // optional debug dump (tests only)
+    int B, S, Hq, Hkv, pos0;
+    int rotate_q;            // 1: stage Q through registers with RoPE; 0: Q is loaded by TMA
+    int write_back_q;        // with rotate_q: also store the rotated Q to global
+    float scale_log2e;
+};
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false when the CTA is aborting (this wait or another one gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 63) == 63) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > 2000000000ull) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t *r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of the tcgen05 MMA: start address, leading / stride byte
+// offsets (all >> 4), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// A [128 x 128] bf16 tile in shared memory: two boxes of 64 columns; inside a box row r sits
+// at r*128 bytes and its eight 16-byte chunks are XOR-swizzled with (r & 7) -- the layout
+// a 128-byte-swizzle TMA box produces and the MMA descriptors above expect.
+__device__ __forceinline__ uint32_t tile_offset(int row, int col) {
+    int box = col >> 6, c = col & 63;
+    int chunk = (c >> 3) ^ (row & 7);
+    return (uint32_t)(box * kBoxBytes + row * 128 + chunk * 16 + (c & 7) * 2);
+}
+
+// ------------------------------------------------------------------ kernel
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                  const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.Hq / p.Hkv;
+    const int n_pairs = (p.S + 2 * kBM - 1) / (2 * kBM);
+    // heaviest query tiles first; consecutive CTAs walk the query heads of one sequence so
+    // that the heads sharing a KV head read its tiles from L2 together
+    const int per_pair = p.Hq * p.B;
+    const int t = n_pairs - 1 - (int)blockIdx.x / per_pair;
+    const int rem = (int)blockIdx.x % per_pair;
+    const int b = rem / p.Hq, h = rem % p.Hq;
+    const int kvh = h / G;
+    const int nkv_total = (p.S + kBN - 1) / kBN;
+    const int row_base = t * 2 * kBM;                 // first query row of tile 0
+    const bool active1 = row_base + kBM < p.S;
+    const int n0 = min(2 * t + 1, nkv_total);
+    const int n1 = active1 ? min(2 * t + 2, nkv_total) : 0;
+    const int nmax = max(n0, n1);
+    volatile int *abort_flag = &sm.abort_flag;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, p.rotate_q ? 256 : 1);
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
+        }
+        for (int w = 0; w < 2; w++) {
+            mbar_init(&sm.s_full[w], 1); mbar_init(&sm.p_ready[w], kBM); mbar_init(&sm.o_full[w], 1);
+        }
+        mbar_init(&sm.drain, 1);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 8) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            const int qx = h * kD, kx = kvh * kD;
+            const int y0 = b * p.S + row_base;
+            if (!p.rotate_q) {
+                mbar_expect_tx(&sm.q_full, active1 ? 2 * kTileBytes : kTileBytes);
+                tma_load_2d(sm.q[0], &q_map, qx, y0, &sm.q_full);
+                tma_load_2d(sm.q[0] + kBoxBytes, &q_map, qx + 64, y0, &sm.q_full);
+                if (active1) {
+                    tma_load_2d(sm.q[1], &q_map, qx, y0 + kBM, &sm.q_full);
+                    tma_load_2d(sm.q[1] + kBoxBytes, &q_map, qx + 64, y0 + kBM, &sm.q_full);
+                }
+            }
+            for (int j = 0; j < nmax; j++) {
+                const int s = j & 1, ph = (j >> 1) & 1;
+                const int y = b * p.S + j * kBN;
+                if (!mbar_wait(&sm.k_empty[s], ph ^ 1, abort_flag)) break;
+                mbar_expect_tx(&sm.k_full[s], kTileBytes);
+                tma_load_2d(sm.k[s], &k_map, kx, y, &sm.k_full[s]);
+                tma_load_2d(sm.k[s] + kBoxBytes, &k_map, kx + 64, y, &sm.k_full[s]);
+                if (!mbar_wait(&sm.v_empty[s], ph ^ 1, abort_flag)) break;
+                mbar_expect_tx(&sm.v_full[s], kTileBytes);
+                tma_load_2d(sm.v[s], &v_map, kx, y, &sm.v_full[s]);
+                tma_load_2d(sm.v[s] + kBoxBytes, &v_map, kx + 64, y, &sm.v_full[s]);
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc(kBM, kBN, 0, 0);   // A, B K-major
+            constexpr uint32_t idesc_pv = instr_desc(kBM, kD, 0, 1);    // A from TMEM, B (V) MN-major
+            const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
+            const uint32_t s_tmem[2] = {tmem + 0, tmem + 128};
+            const uint32_t o_tmem[2] = {tmem + 256, tmem + 384};
+            const int n_w[2] = {n0, n1};
+            bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
+            tc_fence_after();
+
+            // S_w = Q_w K^T : 8 steps of 16 along D; both operands K-major, 128-byte swizzle,
+            // 1024 bytes between 8-row groups; a step advances 32 bytes inside the 128-byte row
+            auto issue_qk = [&](int w, int stage) {
+                const uint32_t ka = smem_u32(sm.k[stage]);
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ks++) {
+                    const uint32_t off = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
+                    mma_ss(s_tmem[w], smem_desc(q_addr[w] + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_qk, ks > 0);
+                }
+                tc_commit(&sm.s_full[w]);
+            };
+            // O_w += P_w V : 8 steps of 16 KV rows; P (bf16 pairs, 8 columns per step) from TMEM,
+            // V MN-major: 16 rows = 2048 bytes per step, 64-column boxes 16 KiB apart
+            auto issue_pv = [&](int w, int stage, int j) {
+                const uint32_t va = smem_u32(sm.v[stage]);
+#pragma unroll
+                for (int ks = 0; ks < kBN / 16; ks++)
+                    mma_ts(o_tmem[w], s_tmem[w] + ks * 8, smem_desc(va + ks * 2048, kBoxBytes, 1024), idesc_pv,
+                           (j > 0 || ks > 0) ? 1u : 0u);
+                if (j == n_w[w] - 1) tc_commit(&sm.o_full[w]);
+            };
+
+            if (ok && nmax > 0) ok = mbar_wait(&sm.k_full[0], 0, abort_flag);
+            if (ok && nmax > 0) {
+                tc_fence_after();
+                if (n0 > 0) issue_qk(0, 0);
+                if (n1 > 0) issue_qk(1, 0);
+                tc_commit(&sm.k_empty[0]);
+            }
+            for (int j = 0; ok && j < nmax; j++) {
+                const int s = j & 1, ph = (j >> 1) & 1;
+                const int sn = (j + 1) & 1, phn = ((j + 1) >> 1) & 1;
+                const bool next = j + 1 < nmax;
+                if (!(ok = mbar_wait(&sm.v_full[s], ph, abort_flag))) break;
+                if (next && !(ok = mbar_wait(&sm.k_full[sn], phn, abort_flag))) break;
+#pragma unroll
+                for (int w = 0; w < 2; w++) {
+                    if (j < n_w[w]) {
+                        if (!(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) break;
+                        tc_fence_after();
+                        issue_pv(w, s, j);
+                    }
+                    if (w == 1) tc_commit(&sm.v_empty[s]);
+                    if (j + 1 < n_w[w]) issue_qk(w, sn);
+                }
+                if (!ok) break;
+                if (next) tc_commit(&sm.k_empty[sn]);
+            }
+            // every MMA issued by this thread has completed once this commit arrives
+            tc_commit(&sm.drain);
+            mbar_wait(&sm.drain, 0, abort_flag);
+        }
+    } else if (warp < 8) {
+        // ---------------------------------------------------------------- softmax groups
+        const int w = warp >> 2;                       // query tile of this group
+        const int r = (warp & 3) * 32 + lane;          // row inside the tile = TMEM lane
+        const int qrow = row_base + w * kBM + r;       // query position inside the sequence
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_base + (w ? 128u : 0u);
+        const uint32_t o_addr = lane_base + (w ? 384u : 256u);
+        const int n = w ? n1 : n0;
+        const int diag = 2 * t + w;                    // KV tile holding this tile's diagonal
+        const float c = p.scale_log2e;
+        bool ok = true;
+
+        if (p.rotate_q) {
+            // Stage Q through registers: thread r of group w owns row r of tile w.  Rotate
+            // pairs (f, f + 64) with the table row of the token's position, store bf16 into
+            // the swizzled tile (and back to global when the caller keeps the rotated Q).
+            const bool valid = qrow < p.S && (w == 0 || active1);
+            __nv_bfloat16 *qg = p.q + ((int64_t)b * p.S + qrow) * p.Hq * kD + (int64_t)h * kD;
+            const float *ct = p.cos_tab + (int64_t)(p.pos0 + qrow) * (kD / 2);
+            const float *st = p.sin_tab + (int64_t)(p.pos0 + qrow) * (kD / 2);
+            uint8_t *tile = sm.q[w];
+#pragma unroll 2
+            for (int f = 0; f < kD / 2; f += 8) {
+                uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+                if (valid) {
+                    lo = *reinterpret_cast<const uint4 *>(qg + f);
+                    hi = *reinterpret_cast<const uint4 *>(qg + f + kD / 2);
+                    float x0[8], x1[8];
+                    Elem<__nv_bfloat16>::unpack(lo, x0);
+                    Elem<__nv_bfloat16>::unpack(hi, x1);
+                    float cs[8], sn[8];
+                    *reinterpret_cast<float4 *>(cs) = *reinterpret_cast<const float4 *>(ct + f);
+                    *reinterpret_cast<float4 *>(cs + 4) = *reinterpret_cast<const float4 *>(ct + f + 4);
+                    *reinterpret_cast<float4 *>(sn) = *reinterpret_cast<const float4 *>(st + f);
+                    *reinterpret_cast<float4 *>(sn + 4) = *reinterpret_cast<const float4 *>(st + f + 4);
+                    float a[8], d[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        a[i] = x0[i] * cs[i] - x1[i] * sn[i];
+                        d[i] = x0[i] * sn[i] + x1[i] * cs[i];
+                    }
+                    lo = make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
+                    hi = make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
+                    if (p.write_back_q) {
+                        *reinterpret_cast<uint4 *>(qg + f) = lo;
+                        *reinterpret_cast<uint4 *>(qg + f + kD / 2) = hi;
+                    }
+                }
+                *reinterpret_cast<uint4 *>(tile + tile_offset(r, f)) = lo;
+                *reinterpret_cast<uint4 *>(tile + tile_offset(r, f + kD / 2)) = hi;
+            }
+            // make the generic-proxy stores visible to the tensor core's async proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&sm.q_full);
+        }
+
+        float m_ref = -INFINITY, l = 0.f;
+        for (int j = 0; j < n; j++) {
+            // warp-uniform outcome: the aligned TMEM instructions below need the whole warp
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_full[w], j & 1, abort_flag)))) break;
+            tc_fence_after();
+            const bool masked = (j == diag);
+            const int col0 = j * kBN;
+
+            // pass 1: row maximum of the raw scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t v[32];
+                tmem_ld32(s_addr + ch * 32, v);
+                tc_wait_ld();
+                if (p.dbg && blockIdx.x == 0 && w == 0 && j == 0)
+                    for (int i = 0; i < 32; i++) p.dbg[r * 128 + ch * 32 + i] = __uint_as_float(v[i]);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float x = __uint_as_float(v[i]);
+                    if (masked && col0 + ch * 32 + i > qrow) x = -INFINITY;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float mx_s = mx * c;
+            float corr = 1.f;
+            bool grow = false;
+            if (j == 0) {
+                m_ref = mx_s;
+            } else if (mx_s > m_ref + kRescaleThreshold) {
+                corr = ex2(m_ref - mx_s);
+                m_ref = mx_s;
+                l *= corr;
+                grow = true;
+            }
+            if (__any_sync(0xffffffffu, grow)) {
+                // rare: bring O down to the new reference maximum.  S_j is complete, so every
+                // earlier MMA (the last PV of this tile included) has finished with O.
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ch++) {
+                    uint32_t v[32];
+                    tmem_ld32(o_addr + ch * 32, v);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                    tmem_st32(o_addr + ch * 32, v);
+                }
+                tc_wait_st();
+            }
+
+            // pass 2: P = exp2(S*c - m_ref) as bf16 pairs over the first 64 columns of S
+            const float neg_m = -m_ref;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t v[32], pk[16];
+                tmem_ld32(s_addr + ch * 32, v);
+                tc_wait_ld();
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = fmaf(__uint_as_float(v[i]), c, neg_m);
+                    float x1 = fmaf(__uint_as_float(v[i + 1]), c, neg_m);
+                    if (masked) {
+                        if (col0 + ch * 32 + i > qrow) x0 = -INFINITY;
+                        if (col0 + ch * 32 + i + 1 > qrow) x1 = -INFINITY;
+                    }
+                    float p0 = ex2(x0), p1 = ex2(x1);
+                    sum += p0 + p1;
+                    pk[i >> 1] = pack_bf16(p0, p1);
+                }
+                l += sum;
+                tmem_st16(s_addr + ch * 16, pk);
+            }
+            tc_wait_st();
+            if (p.dbg && blockIdx.x == 0 && w == 0 && j == 0) p.dbg[32768 + 256 + r] = mx;
+            tc_fence_before();
+            mbar_arrive(&sm.p_ready[w]);
+        }
+
+        // epilogue: O / l -> bf16 -> global
+        if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_full[w], 0, abort_flag));
+        if (ok && n > 0) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16 *og = p.out + ((int64_t)b * p.S + qrow) * p.Hq * kD + (int64_t)h * kD;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t v[32];
+                tmem_ld32(o_addr + ch * 32, v);
+                tc_wait_ld();
+                if (p.dbg && blockIdx.x == 0 && w == 0)
+                    for (int i = 0; i < 32; i++) p.dbg[16384 + r * 128 + ch * 32 + i] = __uint_as_float(v[i]);
+                if (qrow < p.S) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 o4 = make_uint4(
+                            pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv),
+                            pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv),
+                            pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv),
+                            pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv));
+                        *reinterpret_cast<uint4 *>(og + ch * 32 + i) = o4;
+                    }
+                }
+            }
+            if (p.lse && qrow < p.S)
+                p.lse[((int64_t)b * p.Hq + h) * p.S + qrow] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+            if (p.dbg && blockIdx.x == 0 && w == 0) { p.dbg[32768 + r] = l; p.dbg[32768 + 128 + r] = m_ref; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && sm.abort_flag) atomicExch(p.status, 1);
+    if (warp == 9) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] row-major; box = 64 columns x 128 rows, 128-byte swizzle.
+int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(NIMLLM_ERR_CUDA, "attn_prefill: cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NIMLLM_ERR_CUDA, "attn_prefill: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return NIMLLM_OK;
+}
+
+}  // namespace
+
+// status word (4 bytes) + optional debug area
+size_t prefill_tc_workspace_bytes(int, int, int, int, int) { return 256; }
+
+float *g_prefill_dbg = nullptr;  // testing hook: device buffer of 33152 floats, or null
+
+int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *lse, const float *cos_tab,
+                      const float *sin_tab, int pos0, int write_back_q, int B, int S, int Hq, int Hkv, int D,
+                      float scale, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (D != kD) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: head_dim %d (the tensor-core kernel is built for 128)", D);
+    if (!workspace || workspace_bytes < 256) return fail(NIMLLM_ERR_WORKSPACE, "attn_prefill bf16: workspace %zu bytes, need 256", workspace_bytes);
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
+        return fail(NIMLLM_ERR_ARG, "attn_prefill bf16: q, k, v, out must be 16-byte aligned");
+    if ((int64_t)B * S > 0x7fffffff) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: B*S too large");
+
+    static bool attr_set[64] = {false};
+    const size_t smem_bytes = sizeof(Smem) + 1024;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: shared memory opt-in: %s", cudaGetErrorString(e));
+        attr_set[dev] = true;
+    }
+
+    CUtensorMap q_map, k_map, v_map;
+    int rc;
+    if ((rc = make_map(&q_map, q, (uint64_t)B * S, (uint64_t)Hq * D))) return rc;
+    if ((rc = make_map(&k_map, k, (uint64_t)B * S, (uint64_t)Hkv * D))) return rc;
+    if ((rc = make_map(&v_map, v, (uint64_t)B * S, (uint64_t)Hkv * D))) return rc;
+
+    PrefillParams p;
+    p.q = (__nv_bfloat16 *)q; p.out = (__nv_bfloat16 *)out; p.lse = lse;
+    p.cos_tab = cos_tab; p.sin_tab = sin_tab;
+    p.status = (int *)workspace; p.dbg = g_prefill_dbg;
+    p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.pos0 = pos0;
+    p.rotate_q = cos_tab ? 1 : 0;
+    p.write_back_q = write_back_q;
+    p.scale_log2e = scale * kLog2e;
+
+    cudaError_t e = cudaMemsetAsync(workspace, 0, 4, st);
+    if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: %s", cudaGetErrorString(e));
+    const int n_pairs = (S + 2 * kBM - 1) / (2 * kBM);
+    dim3 grid((unsigned)n_pairs * Hq * B);
+    prefill_tc_kernel<<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
+    NIMLLM_CHECK_LAUNCH("attn_prefill bf16");
+    return NIMLLM_OK;
+}
+
+}  // namespace nimllm
+
+extern "C" void nimllm_attn_debug_prefill_dump(float *device_buffer) { nimllm::g_prefill_dbg = device_buffer; }
