@@ -302,6 +302,94 @@ def run_decode(args, dist, name):
     return line
 
 
+# ------------------------------------------------------------------------------------ c4
+def run_prefill(args, dist):
+    """C4: causal prefill 4 x 8192, 32 q / 8 kv heads, D = 128, bf16, RoPE base 500000.  The
+    KV heads (with their query heads) are split over the ranks; no collective."""
+    import torch
+    from nimllm_b200 import attention as A
+    B, S, Hq, Hkv, D = 4, 8192, 32, 8, 128
+    if Hkv % dist.world:
+        raise SystemExit("c4 splits 8 KV heads: --gpus must divide 8")
+    hq, hkv = Hq // dist.world, Hkv // dist.world
+    gen = torch.Generator(device="cuda").manual_seed(SEEDS["c4"] + 1000 * dist.rank)
+    q = torch.randn(B, S, hq * D, generator=gen, device="cuda").bfloat16()
+    k = torch.randn(B, S, hkv * D, generator=gen, device="cuda").bfloat16()
+    v = torch.randn(B, S, hkv * D, generator=gen, device="cuda").bfloat16()
+    cos, sin = A.rope_tables(S, D, 500000.0)
+    scale = 1.0 / math.sqrt(D)
+    flops_rank = 4.0 * B * hq * D * S * (S + 1) / 2
+    box = {}
+
+    def step():
+        # RoPE(K) pre-pass in place + tensor-core kernel with RoPE(Q) fused into its prologue
+        box["out"] = A.attn_forward(q, k, v, cos, sin, n_head=hq, n_kv_head=hkv, head_dim=D, save_cache=False,
+                                    scale=scale)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    sampler = ClockSampler(dist.local)
+    with sampler:
+        ms = timed_steps(torch, step, args.steps, args.warmup, flush, dist)
+    t_max = dist.max(sum(ms) / 1e3)
+    value = flops_rank * dist.world * args.steps / t_max / 1e12
+
+    # end to end: pinned host q/k/v -> device, attention, result back to pinned host
+    hq_, hk_, hv_ = (torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v))
+    hq_.copy_(q); hk_.copy_(k); hv_.copy_(v)
+    hout = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+
+    def e2e_step():
+        q.copy_(hq_, non_blocking=True); k.copy_(hk_, non_blocking=True); v.copy_(hv_, non_blocking=True)
+        out = A.attn_forward(q, k, v, cos, sin, n_head=hq, n_kv_head=hkv, head_dim=D, save_cache=False, scale=scale)
+        hout.copy_(out, non_blocking=True)
+
+    e_steps = max(3, min(args.steps, 5))
+    e2e_ms = timed_steps(torch, e2e_step, e_steps, 3, flush, dist)
+    e2e_t = dist.max(sum(e2e_ms) / 1e3)
+    pk = peaks()
+    achieved = flops_rank / (sum(ms) / len(ms) / 1e3) / 1e12
+    line = {
+        "metric": "prefill_attn_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": dist.world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_max / args.steps * 1e3, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "C4 causal prefill: 4 x 8192 tokens, 32q/8kv heads, D=128, bf16, RoPE base 500000",
+                   "parallelism": f"KV heads split over {dist.world} GPU(s), no collective",
+                   "l2": "256 MiB flush between timed steps",
+                   "tokens_per_s": round(B * S / (t_max / args.steps), 1)},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": pk["bf16"], "unit": "TFLOP/s",
+                     "frac": round(achieved / pk["bf16"], 4), "frac_of_sustained": round(achieved / pk["bf16_sustained"], 4),
+                     "traffic": NCU_TRAFFIC_BYTES["c4"], "peak_source": pk["source"],
+                     "algorithmic_flops_per_step": flops_rank,
+                     "kernel": "prefill_tc_kernel (+ rope_append_kernel pre-pass on K) per step"},
+        "e2e": {"value": round(flops_rank * dist.world * e_steps / e2e_t / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": q.numel() * 2,
+                "ms_per_step": round(e2e_t / e_steps * 1e3, 4), "steps": e_steps},
+        "gpu_launches": 2 * args.steps,
+        "clocks": sampler.summary(),
+    }
+    if dist.rank == 0 and dist.world == 1:
+        line["cpu_baseline"] = cpu_baseline_prefill(q, k, v, hq, hkv, D, scale)
+    return line
+
+
+def cpu_baseline_prefill(q, k, v, Hq, Hkv, D, scale):
+    """The CPU restatement of forward()'s per-head attention loop (oracle_attn_forward: fp32,
+    S x S scores per head, OpenMP over heads) on a sample of the workload's (batch, head) pairs."""
+    from oracle import oracle as O
+    heads_q, heads_kv, S = 8, 2, 4096          # 8 query heads over 2 KV heads of sequence 0, first 4096 tokens
+    qs = q[0, :S, :heads_q * D].float().cpu().numpy().copy()
+    ks = k[0, :S, :heads_kv * D].float().cpu().numpy().copy()
+    vs = v[0, :S, :heads_kv * D].float().cpu().numpy().copy()
+    cos, sin = O.rope_tables(S, D, 500000.0)
+    t0 = time.perf_counter()
+    O.attn_forward(qs, ks, vs, cos, sin, heads_q, heads_kv, D)
+    dt = time.perf_counter() - t0
+    flops = 4.0 * heads_q * D * S * (S + 1) / 2
+    return {"value": round(flops / dt / 1e12, 5), "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"{heads_q} query heads x first {S} tokens of sequence 0 (fp32 restatement, S x S scores per head); "
+                      f"{dt:.2f} s", "host_cpus": os.cpu_count()}
+
+
 def lib_needs_combine(_lib, B, Hq, Hkv, D, max_len, chunk_rows):
     return _lib.lib().nimllm_attn_decode_workspace_bytes(B, Hq, Hkv, D, max_len, chunk_rows) > 0
 
@@ -428,8 +516,7 @@ def main():
     if args.workload in ("c3", "c5"):
         line = run_decode(args, dist, args.workload)
     else:
-        from nimllm_b200 import bench_prefill
-        line = bench_prefill.run(args, dist, peaks(), ClockSampler, timed_steps)
+        line = run_prefill(args, dist)
     if dist.rank == 0:
         print(json.dumps(line), flush=True)
     dist.close()

@@ -28,6 +28,8 @@
 // Every wait on an mbarrier is bounded: after ~2 s without progress the CTA raises an abort
 // flag, all roles leave their loops, TMEM is released and a status word is set.
 #include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -41,9 +43,9 @@ constexpr int kBN = 128;           // KV rows per tile
 constexpr int kStages = 2;
 constexpr int kTileBytes = kBN * kD * 2;     // 32 KiB: one [128 x 128] bf16 tile = two swizzled 64-column boxes
 constexpr int kBoxBytes = kTileBytes / 2;    // 16 KiB
-constexpr int kThreads = 384;                // 8 softmax warps, producer, MMA issuer, 2 idle
+constexpr int kThreads = 384;                // 8 softmax warps + one warpgroup holding producer, MMA issuer, 2 idle
 constexpr uint32_t kTmemCols = 512;
-constexpr float kRescaleThreshold = 8.0f;    // log2 units
+constexpr float kRescaleThreshold = 8.0f;    // log2 units: O is rescaled when a row maximum grows by more
 
 struct Smem {
     // tiles first: 1024-byte alignment is required by the 128-byte swizzle atoms
@@ -99,11 +101,13 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 // Bounded wait: false when the CTA is aborting (this wait or another one gave up).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    if (mbar_try(bar, parity)) return true;
+    // fast path: plain polling, no timer (reading %globaltimer is slow)
+    for (int it = 0; it < 4096; ++it)
+        if (mbar_try(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t it = 0;; ++it) {
         if (mbar_try(bar, parity)) return true;
-        if ((it & 63) == 63) {
+        if ((it & 255) == 255) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > 2000000000ull) {
                 *abort_flag = 1;
@@ -198,7 +202,26 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int col) {
     return (uint32_t)(box * kBoxBytes + row * 128 + chunk * 16 + (c & 7) * 2);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// 2^x without the special-function unit: n = round(x) through the 1.5*2^23 trick, a cubic
+// for 2^f on f = x - n in [-0.5, 0.5] (relative error < 1e-4, far below the bf16 rounding of
+// P), and n added into the exponent field.  (ex2.approx.ftz.bf16x2 was tried instead and
+// measured slower than the fp32 special-function path.)
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -125.f);
+    const float t = x + 12582912.f;
+    const float f = x - (t - 12582912.f);
+    const float p = fmaf(fmaf(fmaf(0.05517164617776871f, f, 0.2426111251115799f), f, 0.6932609677314758f), f,
+                         0.9999280571937561f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+
 // ------------------------------------------------------------------ kernel
+template <int kEmu>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                   const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
@@ -230,7 +253,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
         }
         for (int w = 0; w < 2; w++) {
-            mbar_init(&sm.s_full[w], 1); mbar_init(&sm.p_ready[w], kBM); mbar_init(&sm.o_full[w], 1);
+            mbar_init(&sm.s_full[w], 1); mbar_init(&sm.p_ready[w], 4); mbar_init(&sm.o_full[w], 1);
         }
         mbar_init(&sm.drain, 1);
         sm.abort_flag = 0;
@@ -245,8 +268,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
+    // Registers follow the work: the softmax warpgroups hold a whole row of S (128 values) plus
+    // the packed P, the third warpgroup only issues copies and MMAs.  168 per thread at launch.
     if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         if (lane == 0) {
             const int qx = h * kD, kx = kvh * kD;
             const int y0 = b * p.S + row_base;
@@ -274,6 +300,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         }
     } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(kBM, kBN, 0, 0);   // A, B K-major
             constexpr uint32_t idesc_pv = instr_desc(kBM, kD, 0, 1);    // A from TMEM, B (V) MN-major
@@ -322,7 +349,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 #pragma unroll
                 for (int w = 0; w < 2; w++) {
                     if (j < n_w[w]) {
-                        if (!(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) break;
+                        if (kEmu != 12 && !(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) break;
                         tc_fence_after();
                         issue_pv(w, s, j);
                     }
@@ -338,6 +365,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         }
     } else if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         const int w = warp >> 2;                       // query tile of this group
         const int r = (warp & 3) * 32 + lane;          // row inside the tile = TMEM lane
         const int qrow = row_base + w * kBM + r;       // query position inside the sequence
@@ -394,28 +422,45 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         }
 
         float m_ref = -INFINITY, l = 0.f;
-        for (int j = 0; j < n; j++) {
+        for (int j = 0; j < (kEmu == 12 ? 0 : n); j++) {
             // warp-uniform outcome: the aligned TMEM instructions below need the whole warp
             if (!(ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_full[w], j & 1, abort_flag)))) break;
             tc_fence_after();
             const bool masked = (j == diag);
             const int col0 = j * kBN;
 
-            // pass 1: row maximum of the raw scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ch++) {
-                uint32_t v[32];
-                tmem_ld32(s_addr + ch * 32, v);
-                tc_wait_ld();
-                if (p.dbg && blockIdx.x == 0 && w == 0 && j == 0)
-                    for (int i = 0; i < 32; i++) p.dbg[r * 128 + ch * 32 + i] = __uint_as_float(v[i]);
+            // the whole row of S in registers with ONE TMEM round trip (four loads in flight)
+            uint32_t v[128];
+            tmem_ld32(s_addr, v);
+            tmem_ld32(s_addr + 32, v + 32);
+            tmem_ld32(s_addr + 64, v + 64);
+            tmem_ld32(s_addr + 96, v + 96);
+            tc_wait_ld();
+            if (p.dbg && blockIdx.x == 0 && w == 0 && j == 0)
+                for (int i = 0; i < 128; i++) p.dbg[r * 128 + i] = __uint_as_float(v[i]);
+
+            // row maximum of the raw scores, four independent chains
+            float mx;
+            if (masked) {
+                float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float x = __uint_as_float(v[i]);
-                    if (masked && col0 + ch * 32 + i > qrow) x = -INFINITY;
-                    mx = fmaxf(mx, x);
+                for (int i = 0; i < 128; i += 2) {
+                    if (col0 + i <= qrow) m0 = fmaxf(m0, __uint_as_float(v[i]));
+                    if (col0 + i + 1 <= qrow) m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
                 }
+                mx = fmaxf(m0, m1);
+            } else if (kEmu == 11) {
+                mx = __uint_as_float(v[0]);
+            } else {
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 128; i += 8) {
+                    m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                    m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                    m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                    m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             }
             const float mx_s = mx * c;
             float corr = 1.f;
@@ -433,43 +478,44 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 // earlier MMA (the last PV of this tile included) has finished with O.
 #pragma unroll 1
                 for (int ch = 0; ch < 4; ch++) {
-                    uint32_t v[32];
-                    tmem_ld32(o_addr + ch * 32, v);
+                    uint32_t o[32];
+                    tmem_ld32(o_addr + ch * 32, o);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                    tmem_st32(o_addr + ch * 32, v);
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    tmem_st32(o_addr + ch * 32, o);
                 }
                 tc_wait_st();
             }
 
-            // pass 2: P = exp2(S*c - m_ref) as bf16 pairs over the first 64 columns of S
+            // P = exp2(S*c - m_ref) as bf16 pairs, written over the first 64 columns of S
             const float neg_m = -m_ref;
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ch++) {
-                uint32_t v[32], pk[16];
-                tmem_ld32(s_addr + ch * 32, v);
-                tc_wait_ld();
-                float sum = 0.f;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            uint32_t pk[64];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = fmaf(__uint_as_float(v[i]), c, neg_m);
-                    float x1 = fmaf(__uint_as_float(v[i + 1]), c, neg_m);
-                    if (masked) {
-                        if (col0 + ch * 32 + i > qrow) x0 = -INFINITY;
-                        if (col0 + ch * 32 + i + 1 > qrow) x1 = -INFINITY;
-                    }
-                    float p0 = ex2(x0), p1 = ex2(x1);
-                    sum += p0 + p1;
-                    pk[i >> 1] = pack_bf16(p0, p1);
+            for (int i = 0; i < 128; i += 4) {
+                float x[4], e[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    x[u] = fmaf(__uint_as_float(v[i + u]), c, neg_m);
+                    if (masked && col0 + i + u > qrow) x[u] = -INFINITY;
+                    // kEmu of every 8 exponentials run as a polynomial on the FMA pipe, the rest on
+                    // the special-function unit
+                    if (kEmu == 11) e[u] = fmaf(x[u], 1e-3f, 1.f);
+                    else e[u] = (((i + u) & 7) < kEmu) ? exp2_poly(x[u]) : ex2(x[u]);
                 }
-                l += sum;
-                tmem_st16(s_addr + ch * 16, pk);
+                sum0 += e[0]; sum1 += e[1]; sum2 += e[2]; sum3 += e[3];
+                pk[i >> 1] = pack_bf16(e[0], e[1]);
+                pk[(i >> 1) + 1] = pack_bf16(e[2], e[3]);
             }
+            tmem_st32(s_addr, pk);
+            tmem_st32(s_addr + 32, pk + 32);
+            l += (sum0 + sum1) + (sum2 + sum3);
             tc_wait_st();
             if (p.dbg && blockIdx.x == 0 && w == 0 && j == 0) p.dbg[32768 + 256 + r] = mx;
             tc_fence_before();
-            mbar_arrive(&sm.p_ready[w]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_ready[w]);     // one arrival per warp
         }
 
         // epilogue: O / l -> bf16 -> global
@@ -501,6 +547,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 p.lse[((int64_t)b * p.Hq + h) * p.S + qrow] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
             if (p.dbg && blockIdx.x == 0 && w == 0) { p.dbg[32768 + r] = l; p.dbg[32768 + 128 + r] = m_ref; }
         }
+    }
+
+    else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");   // warps 10, 11: same warpgroup as 8, 9
     }
 
     tc_fence_before();
@@ -562,11 +612,19 @@ int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *l
     if ((int64_t)B * S > 0x7fffffff) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: B*S too large");
 
     static bool attr_set[64] = {false};
+    static int emu = -1;
+    if (emu < 0) {
+        const char *e = getenv("NIMLLM_PREFILL_EMU");
+        emu = e ? atoi(e) : 2;
+    }
     const size_t smem_bytes = sizeof(Smem) + 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        cudaFuncSetAttribute(prefill_tc_kernel<11>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        cudaFuncSetAttribute(prefill_tc_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: shared memory opt-in: %s", cudaGetErrorString(e));
         attr_set[dev] = true;
     }
@@ -590,7 +648,10 @@ int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *l
     if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: %s", cudaGetErrorString(e));
     const int n_pairs = (S + 2 * kBM - 1) / (2 * kBM);
     dim3 grid((unsigned)n_pairs * Hq * B);
-    prefill_tc_kernel<<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
+    if (emu == 0) prefill_tc_kernel<0><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
+    else if (emu == 11) prefill_tc_kernel<11><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
+    else if (emu == 12) prefill_tc_kernel<12><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
+    else prefill_tc_kernel<2><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
     NIMLLM_CHECK_LAUNCH("attn_prefill bf16");
     return NIMLLM_OK;
 }
