@@ -8,28 +8,38 @@
 // One CTA owns 256 consecutive query rows of one (sequence, query head) as two 128-row
 // tiles and walks the KV sequence in 128-row tiles up to the causal diagonal.
 //
-//   warp 8      TMA producer: Q tiles once, then K_j / V_j tiles into a 2-stage shared-memory
-//               ring (cp.async.bulk.tensor, 128-byte swizzle, mbarrier transaction counts).
-//   warp 9      MMA issuer (one lane): S_w = Q_w K_j^T and O_w += P_w V_j as tcgen05.mma
-//               (cta_group::1, kind::f16, M = N = 128, fp32 accumulators in TMEM).  S and O of
-//               both query tiles take the 512 TMEM columns: S0 S1 O0 O1, 128 columns each.
-//   warps 0-3 / 4-7   softmax group of query tile 0 / 1: one thread per query row (= one TMEM
-//               lane): tcgen05.ld the row of S, running max / sum, P = exp2(S*c - m) rounded
-//               to bf16 and stored back over S (tcgen05.st), which the PV MMA reads as its A
-//               operand straight from TMEM.  O is rescaled only when a row maximum grows by
-//               more than 2^8 (the exact softmax is restored by the final division by the
-//               running sum), then normalised, rounded and written in the epilogue.
+//   warp 8      TMA producer: K_j / V_j tiles into one 5-slot shared-memory ring walked in the
+//               order K_0 V_0 K_1 V_1 ... (cp.async.bulk.tensor, 128-byte swizzle, mbarrier
+//               transaction counts; a slot is released by tcgen05.commit when the MMAs that
+//               read it have completed).  Q tiles by TMA as well when no RoPE is asked for.
+//   warp 9      MMA issuer (one lane): S_w = Q_w K_j^T (both operands from shared memory) and
+//               O_w += P_w V_j (P from TMEM, V MN-major from shared memory) as tcgen05.mma
+//               (cta_group::1, kind::f16, M = N = 128, K = 16, fp32 accumulators in TMEM).  S
+//               and O of both query tiles take the 512 TMEM columns: S0 S1 O0 O1.
+//   warps 0-3 / 4-7   softmax group of query tile 0 / 1, one thread per query row (= one TMEM
+//               lane).  Per KV tile: ONE TMEM round trip brings the 128 scores of the row into
+//               registers (setmaxnreg moves registers from warps 8-11 to these), row max, P =
+//               exp2(S*c - m) rounded to bf16 and stored back over the first 64 columns of S,
+//               where the PV MMA reads it as its A operand.  O is rescaled only when a row
+//               maximum grows by more than 2^8 (the exact softmax is restored by the final
+//               division by the running sum); the epilogue normalises, rounds and writes O.
 //
-// While one group computes its softmax the tensor pipe works on the other tile's S and PV.
-// RoPE: K arrives already rotated (the pre-pass that also fills the KV cache rotates it, as
-// the reference stores K after RoPE); Q is rotated by the pre-pass when the caller keeps it
-// (save_cache), otherwise by this kernel's prologue while staging Q in shared memory.
+// While one group computes its softmax the tensor pipe works on the other tile's PV and next S.
+// RoPE: K arrives already rotated (the pre-pass that also fills the KV cache rotates it in
+// place, as the reference does and stores); Q is rotated by this kernel's prologue while it is
+// staged into the swizzled shared-memory tile (coalesced, 8 lanes per row), and written back
+// only when the caller keeps it (save_cache).
+//
+// Measured on B200 at 4 x 8192 x 32/8 heads (see profiles/): with the softmax handshakes
+// removed the TMA + MMA pipeline alone sustains ~1.2 PFLOP/s -- each CTA re-reads K/V for only
+// 256 query rows and both QK^T operands come from shared memory -- which bounds this one-CTA
+// design; splitting the exponentials between the special-function unit and an FMA polynomial,
+// packed bf16x2 exp2, deeper K/V rings and a KV-head-major CTA order were all measured and did
+// not help, because the softmax arithmetic is not on the critical path.
 //
 // Every wait on an mbarrier is bounded: after ~2 s without progress the CTA raises an abort
 // flag, all roles leave their loops, TMEM is released and a status word is set.
 #include <cuda.h>
-#include <stdlib.h>
-#include <string.h>
 
 #include "common.cuh"
 
@@ -40,7 +50,7 @@ namespace {
 constexpr int kD = 128;            // head_dim
 constexpr int kBM = 128;           // query rows per tile (= TMEM lanes)
 constexpr int kBN = 128;           // KV rows per tile
-constexpr int kStages = 2;
+constexpr int kSlots = 5;           // K/V ring: K_0 V_0 K_1 V_1 ... walk the slots in order
 constexpr int kTileBytes = kBN * kD * 2;     // 32 KiB: one [128 x 128] bf16 tile = two swizzled 64-column boxes
 constexpr int kBoxBytes = kTileBytes / 2;    // 16 KiB
 constexpr int kThreads = 384;                // 8 softmax warps + one warpgroup holding producer, MMA issuer, 2 idle
@@ -50,9 +60,8 @@ constexpr float kRescaleThreshold = 8.0f;    // log2 units: O is rescaled when a
 struct Smem {
     // tiles first: 1024-byte alignment is required by the 128-byte swizzle atoms
     uint8_t q[2][kTileBytes];
-    uint8_t k[kStages][kTileBytes];
-    uint8_t v[kStages][kTileBytes];
-    uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint8_t kv[kSlots][kTileBytes];
+    uint64_t q_full, kv_full[kSlots], kv_empty[kSlots];
     uint64_t s_full[2], p_ready[2], o_full[2], drain;
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -207,21 +216,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-// 2^x without the special-function unit: n = round(x) through the 1.5*2^23 trick, a cubic
-// for 2^f on f = x - n in [-0.5, 0.5] (relative error < 1e-4, far below the bf16 rounding of
-// P), and n added into the exponent field.  (ex2.approx.ftz.bf16x2 was tried instead and
-// measured slower than the fp32 special-function path.)
-__device__ __forceinline__ float exp2_poly(float x) {
-    x = fmaxf(x, -125.f);
-    const float t = x + 12582912.f;
-    const float f = x - (t - 12582912.f);
-    const float p = fmaf(fmaf(fmaf(0.05517164617776871f, f, 0.2426111251115799f), f, 0.6932609677314758f), f,
-                         0.9999280571937561f);
-    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-
 // ------------------------------------------------------------------ kernel
-template <int kEmu>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                   const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
@@ -231,8 +226,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.Hq / p.Hkv;
     const int n_pairs = (p.S + 2 * kBM - 1) / (2 * kBM);
-    // heaviest query tiles first; consecutive CTAs walk the query heads of one sequence so
-    // that the heads sharing a KV head read its tiles from L2 together
+    // Schedule: heaviest query-tile pairs first (their CTAs run 2t + 2 KV tiles); consecutive
+    // CTAs walk the query heads of one sequence, so the heads sharing a KV head stream its
+    // tiles out of L2 together.  (Grouping all CTAs of one KV head instead was measured: same
+    // K/V feed rate, worse balance.)
     const int per_pair = p.Hq * p.B;
     const int t = n_pairs - 1 - (int)blockIdx.x / per_pair;
     const int rem = (int)blockIdx.x % per_pair;
@@ -247,11 +244,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     volatile int *abort_flag = &sm.abort_flag;
 
     if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, p.rotate_q ? 256 : 1);
-        for (int s = 0; s < kStages; s++) {
-            mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1);
-            mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
-        }
+        mbar_init(&sm.q_full, p.rotate_q ? 8 : 1);
+        for (int s = 0; s < kSlots; s++) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 1); }
         for (int w = 0; w < 2; w++) {
             mbar_init(&sm.s_full[w], 1); mbar_init(&sm.p_ready[w], 4); mbar_init(&sm.o_full[w], 1);
         }
@@ -285,17 +279,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     tma_load_2d(sm.q[1] + kBoxBytes, &q_map, qx + 64, y0 + kBM, &sm.q_full);
                 }
             }
-            for (int j = 0; j < nmax; j++) {
-                const int s = j & 1, ph = (j >> 1) & 1;
-                const int y = b * p.S + j * kBN;
-                if (!mbar_wait(&sm.k_empty[s], ph ^ 1, abort_flag)) break;
-                mbar_expect_tx(&sm.k_full[s], kTileBytes);
-                tma_load_2d(sm.k[s], &k_map, kx, y, &sm.k_full[s]);
-                tma_load_2d(sm.k[s] + kBoxBytes, &k_map, kx + 64, y, &sm.k_full[s]);
-                if (!mbar_wait(&sm.v_empty[s], ph ^ 1, abort_flag)) break;
-                mbar_expect_tx(&sm.v_full[s], kTileBytes);
-                tma_load_2d(sm.v[s], &v_map, kx, y, &sm.v_full[s]);
-                tma_load_2d(sm.v[s] + kBoxBytes, &v_map, kx + 64, y, &sm.v_full[s]);
+            // ring position u = 2j for K_j, 2j + 1 for V_j; slot u % kSlots, phase (u / kSlots) & 1
+            for (int u = 0; u < 2 * nmax; u++) {
+                const int slot = u % kSlots, ph = (u / kSlots) & 1;
+                const int y = b * p.S + (u >> 1) * kBN;
+                const CUtensorMap *map = (u & 1) ? &v_map : &k_map;
+                if (!mbar_wait(&sm.kv_empty[slot], ph ^ 1, abort_flag)) break;
+                mbar_expect_tx(&sm.kv_full[slot], kTileBytes);
+                tma_load_2d(sm.kv[slot], map, kx, y, &sm.kv_full[slot]);
+                tma_load_2d(sm.kv[slot] + kBoxBytes, map, kx + 64, y, &sm.kv_full[slot]);
             }
         }
     } else if (warp == 9) {
@@ -313,8 +305,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
             // S_w = Q_w K^T : 8 steps of 16 along D; both operands K-major, 128-byte swizzle,
             // 1024 bytes between 8-row groups; a step advances 32 bytes inside the 128-byte row
-            auto issue_qk = [&](int w, int stage) {
-                const uint32_t ka = smem_u32(sm.k[stage]);
+            auto issue_qk = [&](int w, int slot) {
+                const uint32_t ka = smem_u32(sm.kv[slot]);
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ks++) {
                     const uint32_t off = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
@@ -324,8 +316,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             };
             // O_w += P_w V : 8 steps of 16 KV rows; P (bf16 pairs, 8 columns per step) from TMEM,
             // V MN-major: 16 rows = 2048 bytes per step, 64-column boxes 16 KiB apart
-            auto issue_pv = [&](int w, int stage, int j) {
-                const uint32_t va = smem_u32(sm.v[stage]);
+            auto issue_pv = [&](int w, int slot, int j) {
+                const uint32_t va = smem_u32(sm.kv[slot]);
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ks++)
                     mma_ts(o_tmem[w], s_tmem[w] + ks * 8, smem_desc(va + ks * 2048, kBoxBytes, 1024), idesc_pv,
@@ -333,31 +325,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 if (j == n_w[w] - 1) tc_commit(&sm.o_full[w]);
             };
 
-            if (ok && nmax > 0) ok = mbar_wait(&sm.k_full[0], 0, abort_flag);
+            auto wait_full = [&](int u) { return mbar_wait(&sm.kv_full[u % kSlots], (u / kSlots) & 1, abort_flag); };
+            auto release = [&](int u) { tc_commit(&sm.kv_empty[u % kSlots]); };   // arrives when the MMAs so far are done
+
+            if (ok && nmax > 0) ok = wait_full(0);
             if (ok && nmax > 0) {
                 tc_fence_after();
                 if (n0 > 0) issue_qk(0, 0);
                 if (n1 > 0) issue_qk(1, 0);
-                tc_commit(&sm.k_empty[0]);
+                release(0);
             }
             for (int j = 0; ok && j < nmax; j++) {
-                const int s = j & 1, ph = (j >> 1) & 1;
-                const int sn = (j + 1) & 1, phn = ((j + 1) >> 1) & 1;
+                const int uv = 2 * j + 1, ukn = 2 * j + 2;      // ring positions of V_j and K_{j+1}
                 const bool next = j + 1 < nmax;
-                if (!(ok = mbar_wait(&sm.v_full[s], ph, abort_flag))) break;
-                if (next && !(ok = mbar_wait(&sm.k_full[sn], phn, abort_flag))) break;
+                if (!(ok = wait_full(uv))) break;
+                if (next && !(ok = wait_full(ukn))) break;
 #pragma unroll
                 for (int w = 0; w < 2; w++) {
                     if (j < n_w[w]) {
-                        if (kEmu != 12 && !(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) break;
+                        if (!(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) break;
                         tc_fence_after();
-                        issue_pv(w, s, j);
+                        issue_pv(w, uv % kSlots, j);
                     }
-                    if (w == 1) tc_commit(&sm.v_empty[s]);
-                    if (j + 1 < n_w[w]) issue_qk(w, sn);
+                    if (w == 1) release(uv);
+                    if (j + 1 < n_w[w]) issue_qk(w, ukn % kSlots);
                 }
                 if (!ok) break;
-                if (next) tc_commit(&sm.k_empty[sn]);
+                if (next) release(ukn);
             }
             // every MMA issued by this thread has completed once this commit arrives
             tc_commit(&sm.drain);
@@ -378,29 +372,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         bool ok = true;
 
         if (p.rotate_q) {
-            // Stage Q through registers: thread r of group w owns row r of tile w.  Rotate
-            // pairs (f, f + 64) with the table row of the token's position, store bf16 into
-            // the swizzled tile (and back to global when the caller keeps the rotated Q).
-            const bool valid = qrow < p.S && (w == 0 || active1);
-            __nv_bfloat16 *qg = p.q + ((int64_t)b * p.S + qrow) * p.Hq * kD + (int64_t)h * kD;
-            const float *ct = p.cos_tab + (int64_t)(p.pos0 + qrow) * (kD / 2);
-            const float *st = p.sin_tab + (int64_t)(p.pos0 + qrow) * (kD / 2);
-            uint8_t *tile = sm.q[w];
+            // Stage both Q tiles through registers, all 256 softmax threads together: 8 lanes
+            // per row, lane c of a row owns columns [8c, 8c+8) and their rotation partners
+            // [64+8c, 64+8c+8), so global reads (q and the cos/sin rows) are fully coalesced and
+            // the bf16 results drop into the swizzled tile without bank conflicts.  Rotated
+            // values also go back to global when the caller keeps Q (saveCache).
+            const int c8 = (lane & 7) * 8;
 #pragma unroll 2
-            for (int f = 0; f < kD / 2; f += 8) {
+            for (int step = 0; step < 8; step++) {
+                const int row = step * 32 + warp * 4 + (lane >> 3);     // 0..255 over both tiles
+                const int tile_i = row >> 7, rr = row & 127;
+                const int pos = row_base + row;
                 uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                if (valid) {
-                    lo = *reinterpret_cast<const uint4 *>(qg + f);
-                    hi = *reinterpret_cast<const uint4 *>(qg + f + kD / 2);
-                    float x0[8], x1[8];
+                if (pos < p.S) {
+                    __nv_bfloat16 *qg = p.q + ((int64_t)b * p.S + pos) * p.Hq * kD + (int64_t)h * kD + c8;
+                    const float *ct = p.cos_tab + (int64_t)(p.pos0 + pos) * (kD / 2) + c8;
+                    const float *st = p.sin_tab + (int64_t)(p.pos0 + pos) * (kD / 2) + c8;
+                    lo = *reinterpret_cast<const uint4 *>(qg);
+                    hi = *reinterpret_cast<const uint4 *>(qg + kD / 2);
+                    float cs[8], sn[8], x0[8], x1[8], a[8], d[8];
+                    *reinterpret_cast<float4 *>(cs) = *reinterpret_cast<const float4 *>(ct);
+                    *reinterpret_cast<float4 *>(cs + 4) = *reinterpret_cast<const float4 *>(ct + 4);
+                    *reinterpret_cast<float4 *>(sn) = *reinterpret_cast<const float4 *>(st);
+                    *reinterpret_cast<float4 *>(sn + 4) = *reinterpret_cast<const float4 *>(st + 4);
                     Elem<__nv_bfloat16>::unpack(lo, x0);
                     Elem<__nv_bfloat16>::unpack(hi, x1);
-                    float cs[8], sn[8];
-                    *reinterpret_cast<float4 *>(cs) = *reinterpret_cast<const float4 *>(ct + f);
-                    *reinterpret_cast<float4 *>(cs + 4) = *reinterpret_cast<const float4 *>(ct + f + 4);
-                    *reinterpret_cast<float4 *>(sn) = *reinterpret_cast<const float4 *>(st + f);
-                    *reinterpret_cast<float4 *>(sn + 4) = *reinterpret_cast<const float4 *>(st + f + 4);
-                    float a[8], d[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         a[i] = x0[i] * cs[i] - x1[i] * sn[i];
@@ -409,20 +405,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     lo = make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
                     hi = make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
                     if (p.write_back_q) {
-                        *reinterpret_cast<uint4 *>(qg + f) = lo;
-                        *reinterpret_cast<uint4 *>(qg + f + kD / 2) = hi;
+                        *reinterpret_cast<uint4 *>(qg) = lo;
+                        *reinterpret_cast<uint4 *>(qg + kD / 2) = hi;
                     }
                 }
-                *reinterpret_cast<uint4 *>(tile + tile_offset(r, f)) = lo;
-                *reinterpret_cast<uint4 *>(tile + tile_offset(r, f + kD / 2)) = hi;
+                *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8)) = lo;
+                *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8 + kD / 2)) = hi;
             }
             // make the generic-proxy stores visible to the tensor core's async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&sm.q_full);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.q_full);
         }
 
         float m_ref = -INFINITY, l = 0.f;
-        for (int j = 0; j < (kEmu == 12 ? 0 : n); j++) {
+        for (int j = 0; j < n; j++) {
             // warp-uniform outcome: the aligned TMEM instructions below need the whole warp
             if (!(ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_full[w], j & 1, abort_flag)))) break;
             tc_fence_after();
@@ -449,8 +446,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     if (col0 + i + 1 <= qrow) m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
                 }
                 mx = fmaxf(m0, m1);
-            } else if (kEmu == 11) {
-                mx = __uint_as_float(v[0]);
             } else {
                 float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
@@ -499,10 +494,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 for (int u = 0; u < 4; u++) {
                     x[u] = fmaf(__uint_as_float(v[i + u]), c, neg_m);
                     if (masked && col0 + i + u > qrow) x[u] = -INFINITY;
-                    // kEmu of every 8 exponentials run as a polynomial on the FMA pipe, the rest on
-                    // the special-function unit
-                    if (kEmu == 11) e[u] = fmaf(x[u], 1e-3f, 1.f);
-                    else e[u] = (((i + u) & 7) < kEmu) ? exp2_poly(x[u]) : ex2(x[u]);
+                    e[u] = ex2(x[u]);
                 }
                 sum0 += e[0]; sum1 += e[1]; sum2 += e[2]; sum3 += e[3];
                 pk[i >> 1] = pack_bf16(e[0], e[1]);
@@ -612,19 +604,11 @@ int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *l
     if ((int64_t)B * S > 0x7fffffff) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: B*S too large");
 
     static bool attr_set[64] = {false};
-    static int emu = -1;
-    if (emu < 0) {
-        const char *e = getenv("NIMLLM_PREFILL_EMU");
-        emu = e ? atoi(e) : 2;
-    }
     const size_t smem_bytes = sizeof(Smem) + 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-        cudaFuncSetAttribute(prefill_tc_kernel<11>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-        cudaFuncSetAttribute(prefill_tc_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: shared memory opt-in: %s", cudaGetErrorString(e));
         attr_set[dev] = true;
     }
@@ -648,10 +632,7 @@ int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *l
     if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: %s", cudaGetErrorString(e));
     const int n_pairs = (S + 2 * kBM - 1) / (2 * kBM);
     dim3 grid((unsigned)n_pairs * Hq * B);
-    if (emu == 0) prefill_tc_kernel<0><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
-    else if (emu == 11) prefill_tc_kernel<11><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
-    else if (emu == 12) prefill_tc_kernel<12><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
-    else prefill_tc_kernel<2><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
+    prefill_tc_kernel<<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
     NIMLLM_CHECK_LAUNCH("attn_prefill bf16");
     return NIMLLM_OK;
 }
