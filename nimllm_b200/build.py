@@ -75,7 +75,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed")
     if force or procs or not os.path.exists(LIB):
         subprocess.check_call([_nvcc(), "-shared", "-o", LIB, *objs, "-lcudart"])
+    build_host(force or bool(procs))
     return LIB
+
+
+HOST_LIB = os.path.join(HERE, "libnimllm_attn_host.so")
+
+
+def build_host(force: bool = False) -> str:
+    """The C++ host mirror (nimllm_b200/host): plain C++ over the C ABI, linked against the
+    kernel library next to it."""
+    srcs = [os.path.join(HERE, "host", "attn_host.cpp")]
+    deps = srcs + [os.path.join(HERE, "host", "attn_host.hpp"), os.path.join(HERE, "..", "include", "nimllm_attn.h")]
+    if force or _stale(HOST_LIB, deps):
+        subprocess.check_call([_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", HOST_LIB, *srcs,
+                               "-L" + HERE, "-lnimllm_attn", "-Xlinker", "-rpath=$ORIGIN", "-lcudart"])
+        with open(HOST_LIB + ".sha", "w") as f:
+            f.write(_digest(deps))
+    return HOST_LIB
 
 
 if __name__ == "__main__":

@@ -1,0 +1,77 @@
+// attn_host.hpp -- C++ host layer over the C ABI, named after the reference's Nim procedures.
+//
+// nimllm's host code is Nim (compiled to C); no Nim compiler exists on the build image, so the
+// host-side mirror a compiled caller would use is given in C++:
+//
+//   reference (src/model.nim, src/gpu.nim, src/autograd.nim)      here
+//   GpuBuf {data, numel}            (src/gpu.nim:114-117)         nimllm::GpuBuf
+//   trackedCreate / freeStepAllocations (src/autograd.nim:37-65)  nimllm::Arena (bump allocator)
+//   KvCache, initKvCache, resetKvCache  (src/model.nim:70-73,729-746)   nimllm::KvCache
+//   forward()'s attention block         (src/model.nim:494-508)   nimllm::attnForward
+//   forwardCached()'s attention block   (src/model.nim:788-840)   nimllm::attnForwardCached
+//
+// Everything computes through include/nimllm_attn.h; nothing here runs on the CPU.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/nimllm_attn.h"
+
+namespace nimllm {
+
+struct GpuBuf {          // src/gpu.nim:114-117
+    void *data = nullptr;
+    size_t numel = 0;    // float32 elements
+};
+
+struct ModelShape {      // the compile-time consts of src/model.nim:12-23, at run time
+    int nLayer, nHead, nKvHead, headDim, blockSize;
+    int nEmbd() const { return nHead * headDim; }
+    int nKvDim() const { return nKvHead * headDim; }
+    int kvRepeat() const { return nHead / nKvHead; }
+};
+
+// Bump allocator over one device allocation (src/autograd.nim:16-65): 128-byte aligned
+// slices, reset once per step; no cudaMalloc between init and destruction.
+class Arena {
+  public:
+    explicit Arena(size_t bytes);
+    ~Arena();
+    GpuBuf trackedCreate(size_t numel);     // float32 elements, zero-filled by freeStepAllocations
+    void *bytes(size_t n);                  // raw slice
+    void freeStepAllocations();             // memset of the high-water mark, offset back to 0
+    size_t used() const { return off_; }
+
+  private:
+    char *base_ = nullptr;
+    size_t cap_ = 0, off_ = 0;
+};
+
+// One K and one V buffer per layer, [nKvHead, blockSize, headDim] fp32, zero-filled; host pos.
+struct KvCache {
+    std::vector<GpuBuf> k, v;
+    int pos = 0;
+};
+
+KvCache initKvCache(const ModelShape &m);
+void resetKvCache(KvCache &kv);
+void freeKvCache(KvCache &kv);
+
+// RoPE tables as initModel builds them (src/model.nim:153-163), uploaded to the device.
+void initRope(const ModelShape &m, float ropeTheta, GpuBuf &ropeCos, GpuBuf &ropeSin);
+
+// forward()'s attention block: q [S,nEmbd], k, v [S,nKvDim] (rotated in place), attnOut [S,nEmbd].
+// Returns the ABI status; lastError() explains a non-zero one.
+int attnForward(const ModelShape &m, GpuBuf q, GpuBuf k, GpuBuf v, GpuBuf ropeCos, GpuBuf ropeSin,
+                GpuBuf attnOut, int S, bool saveCache);
+
+// forwardCached()'s attention block for ONE new token (newTokens == 1) of layer li: RoPE at row
+// kv.pos, append, attend rows 0..kv.pos.  The caller advances kv.pos after the last layer.
+int attnForwardCached(const ModelShape &m, KvCache &kv, int li, GpuBuf q, GpuBuf kNew, GpuBuf vNew,
+                      GpuBuf ropeCos, GpuBuf ropeSin, GpuBuf attnOut, Arena &arena);
+
+std::string lastError();
+
+}  // namespace nimllm
