@@ -120,6 +120,30 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
                        int n_kv_head, int head_dim, float scale, int chunk_rows,
                        void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- GQA decode for callers that cannot allocate ------------------------------------
+ * No counterpart in the reference.  Same computation and arguments as nimllm_attn_decode,
+ * minus the workspace: the chunk records of split sequences go to a fixed 8 MiB array that
+ * lives inside the library (every GPU that loads the library carries it until the process
+ * exits).  It exists for host code that has no device memory to hand over when the call is
+ * made: nimllm sizes its scratch arena once at start-up and bump-allocates from it
+ * (src/autograd.nim:16-65), so a decode step that arrives when the arena is exhausted, or a
+ * caller that must not touch cudaMalloc because it synchronises the device, can still run.
+ * The function itself never allocates or frees.
+ *   - A call whose records do not fit (nimllm_attn_decode_workspace_bytes(...) larger than
+ *     nimllm_attn_decode_noalloc_max_bytes()) is refused with NIMLLM_ERR_WORKSPACE.
+ *   - The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - All calls on a device share the array, and it keeps what the last call left there
+ *     (nothing in it needs clearing: every record is written before it is read).  Two calls
+ *     that may overlap on the GPU -- different streams, no ordering between them -- race on
+ *     it; give such calls their own workspace through nimllm_attn_decode instead. */
+size_t nimllm_attn_decode_noalloc_max_bytes(void);
+int nimllm_attn_decode_noalloc(const void *q, int q_dtype, const void *k_cache, const void *v_cache,
+                               int cache_dtype, const int64_t *kv_off, int64_t seq_stride,
+                               int64_t head_stride, const int32_t *seq_len, int max_len, void *out,
+                               int out_dtype, float *partials_out, int batch, int n_head,
+                               int n_kv_head, int head_dim, float scale, int chunk_rows, void *stream);
+
 /* ---- merge of (max, sum, output) partials ----------------------------------------
  * No counterpart in the reference (it never splits a softmax row, src/kernels.cu:
  * 267-303 sees the whole row).  parts [n_parts, rows, rec_stride] fp32 records

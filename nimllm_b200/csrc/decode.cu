@@ -591,6 +591,47 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
     return NIMLLM_OK;
 }
 
+// ---- decode without a caller-provided workspace ------------------------------------------
+// The chunk records of a split decode normally live in the caller's workspace.  This variant
+// keeps them in a fixed array inside the library instead, for callers that have nowhere to
+// get device memory from at the moment of the call (see include/nimllm_attn.h).
+constexpr size_t kBuiltinScratchBytes = 8u << 20;   // 8 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+size_t nimllm_attn_decode_noalloc_max_bytes(void) { return kBuiltinScratchBytes; }
+
+int nimllm_attn_decode_noalloc(const void *q, int q_dtype, const void *k_cache, const void *v_cache,
+                               int cache_dtype, const int64_t *kv_off, int64_t seq_stride,
+                               int64_t head_stride, const int32_t *seq_len, int max_len, void *out,
+                               int out_dtype, float *partials_out, int batch, int n_head,
+                               int n_kv_head, int head_dim, float scale, int chunk_rows, void *stream) {
+    // In host code the array's name is only a handle; the device address has to be asked for,
+    // once per device, with that device current.  No lock: racing first calls would store the
+    // same address.
+    static void *scratch_ptr[64] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64)
+        return fail(NIMLLM_ERR_CUDA, "attn_decode_noalloc: no usable current device (%s)", cudaGetErrorString(e));
+    if (!scratch_ptr[dev]) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_builtin_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(NIMLLM_ERR_CUDA, "attn_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                        cudaGetErrorString(e));
+        scratch_ptr[dev] = ptr;
+    }
+    const size_t need = nimllm_attn_decode_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
+    if (need > kBuiltinScratchBytes)
+        return fail(NIMLLM_ERR_WORKSPACE,
+                    "attn_decode_noalloc: this call needs %zu bytes of chunk records but the built-in scratch holds "
+                    "%zu; use nimllm_attn_decode with a workspace, or a larger chunk_rows",
+                    need, kBuiltinScratchBytes);
+    return nimllm_attn_decode(q, q_dtype, k_cache, v_cache, cache_dtype, kv_off, seq_stride, head_stride, seq_len,
+                              max_len, out, out_dtype, partials_out, batch, n_head, n_kv_head, head_dim, scale,
+                              chunk_rows, scratch_ptr[dev], kBuiltinScratchBytes, stream);
+}
+
 int nimllm_attn_combine(const float *parts, int n_parts, int rows, int head_dim, int rec_stride_,
                         void *out, int out_dtype, float *partials_out, void *stream) {
     if (!parts || (!out && !partials_out)) return fail(NIMLLM_ERR_ARG, "attn_combine: null pointer");
