@@ -338,9 +338,11 @@ __device__ __forceinline__ void consume_frag(const KvFrag<D> &f, const uint32_t 
         }
 }
 
-// MINB = resident CTAs per SM the register budget is held to (3 at D = 64, 2 at D = 128;
-// forcing 4 at D = 64 spilled and measured no faster).
-template <int D, int MINB>
+// MINB = resident CTAs per SM the register budget is held to.
+// BLK = 16-row blocks per prefetched fragment set: what a lane keeps in flight is BLK * D/8
+// 16-byte loads; 8 KiB per warp (BLK = 2 at D = 64, 1 at D = 128) is what it takes to approach
+// the HBM rate with 8 warps per SM.
+template <int D, int MINB, int BLK>
 __global__ void __launch_bounds__(kWarps * 32, MINB) decode_mma_kernel(DecodeParams p) {
     constexpr int NH = 8;  // head rows kept (G <= 8)
     __shared__ float sm_m[kWarps * NH], sm_l[kWarps * NH];
@@ -380,17 +382,25 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) decode_mma_kernel(DecodePar
     const __nv_bfloat16 *kb = reinterpret_cast<const __nv_bfloat16 *>(p.k) + base;
     const __nv_bfloat16 *vb = reinterpret_cast<const __nv_bfloat16 *>(p.v) + base;
 
-    constexpr int STEP = kWarps * 16;
-    int rb = r0 + warp * 16;
-    KvFrag<D> fa, fb;
-    if (rb < r1) load_frag<D>(fa, kb, vb, rb, r1 - 1, g, t);
+    constexpr int STEP = kWarps * 16 * BLK;
+    int rb = r0 + warp * 16 * BLK;
+    KvFrag<D> fa[BLK], fb[BLK];
+    auto load = [&](KvFrag<D> *f, int row) {
+#pragma unroll
+        for (int u = 0; u < BLK; u++) load_frag<D>(f[u], kb, vb, row + u * 16, r1 - 1, g, t);
+    };
+    auto consume = [&](const KvFrag<D> *f, int row) {
+#pragma unroll
+        for (int u = 0; u < BLK; u++) consume_frag<D>(f[u], qreg, o, m, l, row + u * 16, r1, t, p.scale_log2e);
+    };
+    if (rb < r1) load(fa, rb);
     while (rb < r1) {
-        if (rb + STEP < r1) load_frag<D>(fb, kb, vb, rb + STEP, r1 - 1, g, t);
-        consume_frag<D>(fa, qreg, o, m, l, rb, r1, t, p.scale_log2e);
+        if (rb + STEP < r1) load(fb, rb + STEP);
+        consume(fa, rb);
         rb += STEP;
         if (rb >= r1) break;
-        if (rb + STEP < r1) load_frag<D>(fa, kb, vb, rb + STEP, r1 - 1, g, t);
-        consume_frag<D>(fb, qreg, o, m, l, rb, r1, t, p.scale_log2e);
+        if (rb + STEP < r1) load(fa, rb + STEP);
+        consume(fb, rb);
         rb += STEP;
     }
 
@@ -480,6 +490,11 @@ int g_force_kernel = 0;  // 0 auto, 1 generic, 2 mma (testing hook)
 
 
 int auto_chunk_rows(int B, int Hkv, int max_len) {
+    // enough (sequence, KV head) pairs for a few waves of the ~2 resident CTAs per SM: do not
+    // split at all (no partial records, no combine launch; measured best on the ragged batch.
+    // Dispatching the CTAs longest-sequence-first was also measured: the in-kernel ranking costs
+    // more than the shorter tail saves)
+    if ((int64_t)B * Hkv >= (int64_t)sm_count() * 4 && max_len <= 8192) return (max_len + 63) / 64 * 64;
     int64_t total = (int64_t)B * Hkv * max_len;
     // measured on B200: long chunks win (fewer CTA start-ups and partial records) until the
     // grid drops below a few waves of the ~3 resident CTAs per SM
@@ -568,8 +583,8 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
         return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: mma kernel needs a bf16 cache and Hq/Hkv <= 8");
     const bool use_mma = mma_ok && g_force_kernel != 1;
     if (use_mma) {
-        if (head_dim == 64) decode_mma_kernel<64, 3><<<grid, kWarps * 32, 0, st>>>(p);
-        else decode_mma_kernel<128, 2><<<grid, kWarps * 32, 0, st>>>(p);
+        if (head_dim == 64) decode_mma_kernel<64, 2, 2><<<grid, kWarps * 32, 0, st>>>(p);
+        else decode_mma_kernel<128, 2, 1><<<grid, kWarps * 32, 0, st>>>(p);
     } else if (cache_dtype == NIMLLM_BF16) {
         if (head_dim == 64) launch_generic<__nv_bfloat16, 64>(p, grid, st);
         else launch_generic<__nv_bfloat16, 128>(p, grid, st);
