@@ -38,9 +38,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SEEDS = {"c3": 20253, "c4": 20254, "c5": 20255}
+SHAPE_OVERRIDE = None   # set by --shape; the default shapes are the configurations of BASELINE.json
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, taken from the
 # ncu summaries under profiles/ (None until a capture exists for that workload)
-NCU_TRAFFIC_BYTES = {"c3": None, "c5": None, "c4": None}
+NCU_TRAFFIC_BYTES = {"c3": 462457088 + 4210944, "c5": 4295200000 + 8700000, "c4": 1860400000 + 226800000}
 
 
 def log(*a):
@@ -187,8 +188,8 @@ def decode_workload(name, rank, world, device="cuda"):
         rows = cap
     else:
         B, Hq, Hkv, D, L = 8, 32, 8, 128, 131072
-        if os.environ.get("NIMLLM_BENCH_SHAPE"):       # experiments only
-            B, Hq, Hkv, D, L = [int(x) for x in os.environ["NIMLLM_BENCH_SHAPE"].split(",")]
+        if SHAPE_OVERRIDE:                              # --shape B,Hq,Hkv,D,L: profiling / experiments
+            B, Hq, Hkv, D, L = SHAPE_OVERRIDE
         gen.manual_seed(SEEDS[name] + 1000 * rank)
         rows = L // world           # this rank's contiguous slice of every KV head
         cap = rows
@@ -241,6 +242,25 @@ def run_decode(args, dist, name):
             dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
             A.combine(gathered, D)
 
+    graphed = False
+    if sharded:
+        # the sharded step is three dependent launches (decode, NCCL all-gather of 133 KB, merge);
+        # replaying them as one CUDA graph takes the host's launch latency off the critical path
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            eager_step, step = step, graph.replay
+            graphed = True
+        except Exception as e:  # pragma: no cover
+            log(f"CUDA graph capture of the sharded step failed ({e}); timing eager launches")
     flush = None        # inputs larger than L2 (see decode_workload); no flush kernel
     sampler = ClockSampler(dist.local)
     with sampler:
@@ -298,7 +318,7 @@ def run_decode(args, dist, name):
         "config": {"workload": {"c3": "C3 batched GQA decode: 256 ragged sequences per GPU, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
                                 "c5": "C5 long-context decode: 8 x 131072 rows, 32q/8kv heads, D=128, bf16 KV, KV sequence sharded over the GPUs"}[name],
                    "batch_per_gpu": B, "kv_rows_total": int(w["lens"].astype(np.int64).sum()),
-                   "parallelism": ("kv-sequence shards + NCCL all-gather of (o,m,l)" if sharded else
+                   "parallelism": ("kv-sequence shards + NCCL all-gather of (o,m,l)" + (", step replayed as a CUDA graph" if graphed else "") if sharded else
                                    f"independent sequences x{dist.world}, no collective"),
                    "l2": ("inputs larger than L2: the timed loop rotates over 3 replicas of the 453 MB batch"
                           if name == "c3" else "inputs larger than L2: 4.3 GB (or its shard) streamed once per step") +
@@ -307,7 +327,7 @@ def run_decode(args, dist, name):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm"], 4), "traffic": NCU_TRAFFIC_BYTES[name],
                      "peak_source": pk["source"], "algorithmic_bytes_per_step": int(w["bytes"]),
-                     "kernel": "decode_mma_kernel (+ combine_kernel) per step, CUDA events on the launching stream"},
+                     "kernel": "decode_mma_kernel (+ combine_kernel when sequences are split) per step, CUDA events on the launching stream; traffic from profiles/decode_mma_c3.md"},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": B * (E + 2 * Ekv) * 4,
                 "d2h_bytes_per_step": B * E * 4, "ms_per_step": round(e2e_t / args.steps * 1e3, 5)},
         "gpu_launches": launches_per_step * args.steps,
@@ -325,6 +345,8 @@ def run_prefill(args, dist):
     import torch
     from nimllm_b200 import attention as A
     B, S, Hq, Hkv, D = 4, 8192, 32, 8, 128
+    if SHAPE_OVERRIDE:                                  # --shape B,S,Hq,Hkv: small case for ncu captures
+        B, S, Hq, Hkv = SHAPE_OVERRIDE[:4]
     if Hkv % dist.world:
         raise SystemExit("c4 splits 8 KV heads: --gpus must divide 8")
     hq, hkv = Hq // dist.world, Hkv // dist.world
@@ -368,7 +390,7 @@ def run_prefill(args, dist):
         "metric": "prefill_attn_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": dist.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_max / args.steps * 1e3, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "C4 causal prefill: 4 x 8192 tokens, 32q/8kv heads, D=128, bf16, RoPE base 500000",
+        "config": {"workload": f"C4 causal prefill: {B} x {S} tokens, {Hq}q/{Hkv}kv heads, D=128, bf16, RoPE base 500000",
                    "parallelism": f"KV heads split over {dist.world} GPU(s), no collective",
                    "l2": "inputs larger than L2 (0.8 GB of q, k, v, out per step); no flush kernel",
                    "tokens_per_s": round(B * S / (t_max / args.steps), 1)},
@@ -376,7 +398,7 @@ def run_prefill(args, dist):
                      "frac": round(achieved / pk["bf16"], 4), "frac_of_sustained": round(achieved / pk["bf16_sustained"], 4),
                      "traffic": NCU_TRAFFIC_BYTES["c4"], "peak_source": pk["source"],
                      "algorithmic_flops_per_step": flops_rank,
-                     "kernel": "prefill_tc_kernel (+ rope_append_kernel pre-pass on K) per step"},
+                     "kernel": "prefill_tc_kernel (+ rope_append_kernel pre-pass on K) per step; traffic from profiles/prefill_tc_c4.md"},
         "e2e": {"value": round(flops_rank * dist.world * e_steps / e2e_t / 1e12, 2), "unit": "TFLOP/s",
                 "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": q.numel() * 2,
                 "ms_per_step": round(e2e_t / e_steps * 1e3, 4), "steps": e_steps},
@@ -512,7 +534,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=["c3", "c5", "c4"])
     ap.add_argument("--chunk-rows", type=int, default=0)
+    ap.add_argument("--shape", default="", help="override: c5 -> B,Hq,Hkv,D,L ; c4 -> B,S,Hq,Hkv (profiling only)")
     args = ap.parse_args()
+    global SHAPE_OVERRIDE
+    if args.shape:
+        SHAPE_OVERRIDE = [int(x) for x in args.shape.split(",")]
     if args.warmup < 3:
         args.warmup = 3
 

@@ -446,6 +446,8 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
     }
     const int64_t pstride = (int64_t)p.rows * p.W;
     const float *rec = p.parts + (int64_t)row * p.W;
+    // lane i holds (m, l) of parts i, i + 32, ...: one latency for all of them instead of a
+    // serial walk (the records of a long sequence sit in L2, ~1 us apart when read one by one)
     float M = -INFINITY;
     for (int i = lane; i < n; i += 32) {
         float li = rec[i * pstride + p.D + 1];
@@ -459,15 +461,34 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
     float wsum = 0.f;
-    for (int i = 0; i < n; i++) {
-        const float *r = rec + i * pstride;
-        float li = r[p.D + 1];
-        float w = li > 0.f ? li * ex2((r[p.D] - safe) * kLog2e) : 0.f;
-        wsum += w;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+        float w_mine = 0.f;
+        if (i0 + lane < n) {
+            const float *r = rec + (int64_t)(i0 + lane) * pstride;
+            float li = r[p.D + 1];
+            w_mine = li > 0.f ? li * ex2((r[p.D] - safe) * kLog2e) : 0.f;
+        }
+        const int cnt = min(32, n - i0);
+        for (int ii = 0; ii < cnt; ii += 4) {
+            // four parts per step: their loads are independent of the weights and of each other
+            float v[4][8], w[4];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            int d = lane + 32 * j;
-            if (d < p.D) acc[j] = fmaf(w, r[d], acc[j]);
+            for (int u = 0; u < 4; u++) {
+                const bool ok = ii + u < cnt;
+                const float *r = rec + (int64_t)(i0 + ii + (ok ? u : 0)) * pstride;
+                w[u] = ok ? __shfl_sync(0xffffffffu, w_mine, (ii + u) & 31) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    int d = lane + 32 * j;
+                    v[u][j] = d < p.D ? r[d] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                wsum += w[u];
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[j] = fmaf(w[u], v[u][j], acc[j]);
+            }
         }
     }
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeAppendParams p) {
     const int half = p.D / 2;
     const int f4_per_head = half / 4;
     const int n_q = p.q ? p.Hq : 0;
-    const int slots = n_q + 2 * p.Hkv;
+    const int slots = n_q + p.Hkv + (p.k_cache ? p.Hkv : 0);    // V rows only move when there is a cache
     const int64_t total = (int64_t)p.B * p.n * slots * f4_per_head;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
@@ -121,7 +121,7 @@ int launch_rope_append(void *q, int Hq, void *k_new, const void *v_new, int act_
     p.pos0 = pos0; p.cache_row0 = cache_row0; p.max_seq = max_seq;
     p.B = B; p.n = n; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.write_back_k = write_back_k;
 
-    int64_t total = (int64_t)B * n * ((q ? Hq : 0) + 2 * Hkv) * (D / 8);
+    int64_t total = (int64_t)B * n * ((q ? Hq : 0) + Hkv + (k_cache ? Hkv : 0)) * (D / 8);
     if (total == 0) return NIMLLM_OK;
     int64_t blocks = (total + 255) / 256;
     int64_t cap = (int64_t)sm_count() * 16;
