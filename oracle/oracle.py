@@ -202,6 +202,13 @@ def ref_lib() -> C.CDLL:
         R.ref_attn_forward_dev.argtypes = [C.c_void_p] * 7 + [C.c_int] * 5
         R.ref_decode_batch_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, i64p, i64p, i32p,
                                            C.c_void_p, C.c_void_p] + [C.c_int] * 5
+        R.ref_model_create.restype = C.c_void_p
+        R.ref_model_create.argtypes = [C.c_int] * 9 + [np.ctypeslib.ndpointer(dtype=np.uint64, flags="C_CONTIGUOUS")]
+        R.ref_model_set_attn.argtypes = [C.c_void_p] * 5
+        R.ref_model_reset.argtypes = [C.c_void_p]
+        R.ref_model_destroy.argtypes = [C.c_void_p]
+        R.ref_model_step.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, f32p]
+        R.ref_model_prefill_lib.argtypes = [C.c_void_p, i32p, C.c_int, C.c_void_p, f32p]
         _REF = R
     return _REF
 

@@ -18,6 +18,7 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <utility>
 #include <vector>
 
 /* the reference's launchers (src/kernels.cu, declared in src/gpu.nim:227-248,274-276) */
@@ -31,6 +32,11 @@ void gpu_extract_kv_head(const float *src, float *dst, int qHead, int kvRepeat, 
                          int n_kv_dim, int head_dim);
 void gpu_rope_fwd(float *data, const float *cos_tab, const float *sin_tab, int seq_len,
                   int n_embd, int n_head, int head_dim);
+/* non-attention launchers used by the whole-model harness (src/gpu.nim:219-232,282-290) */
+void gpu_embed_fwd(const float *wte, const int *tokens, float *out, int seq_len, int dim);
+void gpu_rmsnorm_affine_fwd(const float *x, const float *gamma, float *y, float *rms_out, int rows, int dim);
+void gpu_swiglu_fwd(const float *gate, const float *up, float *out, int n);
+void gpu_add(const float *a, const float *b, float *y, int n);
 }
 
 static cublasHandle_t g_cublas = nullptr;
@@ -250,6 +256,220 @@ int ref_decode_batch_dev(const float *q, const float *k, const float *v, const i
             gpu_softmax_fwd(scores, probs, 1, S);
             ref_sgemm(0, 1, D, S, probs, vH, out + (size_t)b * E + (size_t)h * D);
         }
+    return 0;
+}
+
+
+/* ===================================================================================
+ * Whole-model harness for the "only attention is swapped" configuration: the reference's
+ * forward passes (src/model.nim:454-549 forward, :748-895 forwardCached, float32 branch)
+ * restated around the reference's own non-attention kernels and cuBLAS, with the attention
+ * block either the reference's per-head loop (impl 0) or calls into the library under test
+ * through function pointers (impl 1).  Weights and RoPE tables are DEVICE buffers owned by the
+ * caller.  Test infrastructure only.
+ * =================================================================================== */
+typedef int (*PrefillFn)(void *, void *, const void *, int, const float *, const float *, int, void *, int, int, int,
+                         int, int, float, int, void *, void *, int, const int64_t *, int64_t, int64_t, int, float *,
+                         void *, size_t, void *);
+typedef int (*RopeAppendFn)(void *, int, void *, const void *, int, int, const float *, const float *, const int32_t *,
+                            int, void *, void *, int, const int64_t *, int64_t, int64_t, int, int, int, int, int, int,
+                            void *);
+typedef size_t (*DecodeWsFn)(int, int, int, int, int, int);
+typedef int (*DecodeFn)(const void *, int, const void *, const void *, int, const int64_t *, int64_t, int64_t,
+                        const int32_t *, int, void *, int, float *, int, int, int, int, float, int, void *, size_t,
+                        void *);
+
+struct RefModel {
+    int nLayer, nEmbd, nHead, nKvHead, headDim, ffnDim, vocab, maxSeq, maxPrefill;
+    const float *wte, *lmHead, *lnFg, *cosTab, *sinTab;
+    std::vector<const float *> wq, wk, wv, wo, gate, up, down, ln1, ln2;
+    std::vector<std::vector<float *>> kc, vc; /* reference cache: [layer][kv head] -> [maxSeq, D] */
+    int pos;
+    float *mk, *mv;                           /* library cache: [layer][kv head][maxSeq][D] */
+    int mpos;
+    int *tokIds;
+    float *x, *xn, *rms, *q, *k, *v, *attn, *proj, *x2, *gateo, *upo, *sw, *mlp, *xnew, *scores, *probs, *logits;
+    void *ws;
+    size_t wsBytes;
+    PrefillFn prefill; RopeAppendFn ropeAppend; DecodeWsFn decodeWs; DecodeFn decode;
+};
+
+static float *dalloc(size_t n) {
+    float *p = nullptr;
+    cudaMalloc(&p, n * sizeof(float));
+    cudaMemset(p, 0, n * sizeof(float));
+    return p;
+}
+
+/* ptrs: wte, lmHead, lnFg, cosTab, sinTab, then per layer wq wk wv wo gate up down ln1 ln2 */
+void *ref_model_create(int nLayer, int nEmbd, int nHead, int nKvHead, int headDim, int ffnDim, int vocab,
+                       int maxSeq, int maxPrefill, const uint64_t *ptrs) {
+    if (ref_init()) return nullptr;
+    RefModel *m = new RefModel();
+    m->nLayer = nLayer; m->nEmbd = nEmbd; m->nHead = nHead; m->nKvHead = nKvHead; m->headDim = headDim;
+    m->ffnDim = ffnDim; m->vocab = vocab; m->maxSeq = maxSeq; m->maxPrefill = maxPrefill;
+    m->wte = (const float *)ptrs[0]; m->lmHead = (const float *)ptrs[1]; m->lnFg = (const float *)ptrs[2];
+    m->cosTab = (const float *)ptrs[3]; m->sinTab = (const float *)ptrs[4];
+    for (int l = 0; l < nLayer; l++) {
+        const uint64_t *p = ptrs + 5 + 9 * l;
+        m->wq.push_back((const float *)p[0]); m->wk.push_back((const float *)p[1]); m->wv.push_back((const float *)p[2]);
+        m->wo.push_back((const float *)p[3]); m->gate.push_back((const float *)p[4]); m->up.push_back((const float *)p[5]);
+        m->down.push_back((const float *)p[6]); m->ln1.push_back((const float *)p[7]); m->ln2.push_back((const float *)p[8]);
+        std::vector<float *> kh, vh;
+        for (int h = 0; h < nKvHead; h++) {                 /* src/model.nim:729-739 */
+            kh.push_back(dalloc((size_t)maxSeq * headDim));
+            vh.push_back(dalloc((size_t)maxSeq * headDim));
+        }
+        m->kc.push_back(kh); m->vc.push_back(vh);
+    }
+    m->pos = 0; m->mpos = 0;
+    size_t cacheN = (size_t)nLayer * nKvHead * maxSeq * headDim;
+    m->mk = dalloc(cacheN); m->mv = dalloc(cacheN);
+    int S = maxPrefill, n = nEmbd, nKv = nKvHead * headDim;
+    cudaMalloc(&m->tokIds, S * sizeof(int));
+    m->x = dalloc((size_t)S * n); m->xn = dalloc((size_t)S * n); m->rms = dalloc(S);
+    m->q = dalloc((size_t)S * n); m->k = dalloc((size_t)S * nKv); m->v = dalloc((size_t)S * nKv);
+    m->attn = dalloc((size_t)S * n); m->proj = dalloc((size_t)S * n); m->x2 = dalloc((size_t)S * n);
+    m->gateo = dalloc((size_t)S * ffnDim); m->upo = dalloc((size_t)S * ffnDim); m->sw = dalloc((size_t)S * ffnDim);
+    m->mlp = dalloc((size_t)S * n); m->xnew = dalloc((size_t)S * n);
+    m->scores = dalloc(maxSeq); m->probs = dalloc(maxSeq);
+    m->logits = dalloc((size_t)S * vocab);
+    m->wsBytes = 16u << 20;
+    cudaMalloc(&m->ws, m->wsBytes);
+    m->prefill = nullptr; m->ropeAppend = nullptr; m->decodeWs = nullptr; m->decode = nullptr;
+    return m;
+}
+
+void ref_model_set_attn(void *h, void *prefill, void *ropeAppend, void *decodeWs, void *decode) {
+    RefModel *m = (RefModel *)h;
+    m->prefill = (PrefillFn)prefill; m->ropeAppend = (RopeAppendFn)ropeAppend;
+    m->decodeWs = (DecodeWsFn)decodeWs; m->decode = (DecodeFn)decode;
+}
+
+void ref_model_reset(void *h) {                              /* src/model.nim:741-746 */
+    RefModel *m = (RefModel *)h;
+    size_t per = (size_t)m->maxSeq * m->headDim * sizeof(float);
+    for (auto &l : m->kc) for (float *p : l) cudaMemset(p, 0, per);
+    for (auto &l : m->vc) for (float *p : l) cudaMemset(p, 0, per);
+    cudaMemset(m->mk, 0, per * m->nLayer * m->nKvHead);
+    cudaMemset(m->mv, 0, per * m->nLayer * m->nKvHead);
+    m->pos = 0; m->mpos = 0;
+}
+
+void ref_model_destroy(void *h) {
+    RefModel *m = (RefModel *)h;
+    for (auto &l : m->kc) for (float *p : l) cudaFree(p);
+    for (auto &l : m->vc) for (float *p : l) cudaFree(p);
+    float *bufs[] = {m->mk, m->mv, m->x, m->xn, m->rms, m->q, m->k, m->v, m->attn, m->proj, m->x2, m->gateo, m->upo,
+                     m->sw, m->mlp, m->xnew, m->scores, m->probs, m->logits};
+    for (float *p : bufs) cudaFree(p);
+    cudaFree(m->tokIds); cudaFree(m->ws);
+    delete m;
+}
+
+/* everything of a layer after the attention block: src/model.nim:510-532 / :842-875 */
+static float *ref_layer_tail(RefModel *m, int l, int S, float *x) {
+    int n = m->nEmbd, f = m->ffnDim;
+    ref_sgemm(2, S, n, n, m->attn, m->wo[l], m->proj);
+    gpu_add(x, m->proj, m->x2, S * n);
+    gpu_rmsnorm_affine_fwd(m->x2, m->ln2[l], m->xn, m->rms, S, n);
+    ref_sgemm(2, S, f, n, m->xn, m->gate[l], m->gateo);
+    ref_sgemm(2, S, f, n, m->xn, m->up[l], m->upo);
+    gpu_swiglu_fwd(m->gateo, m->upo, m->sw, S * f);
+    ref_sgemm(2, S, n, f, m->sw, m->down[l], m->mlp);
+    gpu_add(m->x2, m->mlp, m->xnew, S * n);
+    return m->xnew;
+}
+
+/* forwardCached with ONE new token (src/model.nim:748-895).  impl 0: the reference's attention
+ * (RoPE, cudaMemcpy append, per-head sgemm/scale/softmax/sgemm); impl 1: the library under test.
+ * attn_dump: device [nLayer, nEmbd] or NULL; logits_host: [vocab]. */
+int ref_model_step(void *h, int token, int impl, float *attn_dump, float *logits_host) {
+    RefModel *m = (RefModel *)h;
+    int n = m->nEmbd, D = m->headDim, Hq = m->nHead, Hkv = m->nKvHead, nKv = Hkv * D, G = Hq / Hkv, half = D / 2;
+    int &pos = impl ? m->mpos : m->pos;
+    if (pos + 1 > m->maxSeq) return -2;
+    int S = pos + 1;
+    float scale = 1.0f / sqrtf((float)D);
+    CK(cudaMemcpy(m->tokIds, &token, sizeof(int), cudaMemcpyHostToDevice));
+    float *x = m->x;
+    gpu_embed_fwd(m->wte, m->tokIds, x, 1, n);
+    float *cur = x;
+    for (int l = 0; l < m->nLayer; l++) {
+        gpu_rmsnorm_affine_fwd(cur, m->ln1[l], m->xn, m->rms, 1, n);
+        ref_sgemm(2, 1, n, n, m->xn, m->wq[l], m->q);
+        ref_sgemm(2, 1, nKv, n, m->xn, m->wk[l], m->k);
+        ref_sgemm(2, 1, nKv, n, m->xn, m->wv[l], m->v);
+        if (!impl) {
+            const float *cosp = m->cosTab + (size_t)pos * half, *sinp = m->sinTab + (size_t)pos * half;
+            gpu_rope_fwd(m->q, cosp, sinp, 1, n, Hq, D);
+            gpu_rope_fwd(m->k, cosp, sinp, 1, nKv, Hkv, D);
+            for (int kvh = 0; kvh < Hkv; kvh++) {
+                cudaMemcpy(m->kc[l][kvh] + (size_t)pos * D, m->k + (size_t)kvh * D, D * sizeof(float), cudaMemcpyDeviceToDevice);
+                cudaMemcpy(m->vc[l][kvh] + (size_t)pos * D, m->v + (size_t)kvh * D, D * sizeof(float), cudaMemcpyDeviceToDevice);
+            }
+            for (int hq = 0; hq < Hq; hq++) {
+                int kvh = hq / G;
+                ref_sgemm(2, 1, S, D, m->q + (size_t)hq * D, m->kc[l][kvh], m->scores);
+                gpu_scale(m->scores, scale, m->scores, S);
+                gpu_softmax_fwd(m->scores, m->probs, 1, S);
+                ref_sgemm(0, 1, D, S, m->probs, m->vc[l][kvh], m->attn + (size_t)hq * D);
+            }
+        } else {
+            int64_t headStride = (int64_t)m->maxSeq * D, seqStride = headStride * Hkv;
+            float *kcl = m->mk + (size_t)l * seqStride, *vcl = m->mv + (size_t)l * seqStride;
+            int rc = m->ropeAppend(m->q, Hq, m->k, m->v, 0, 1, m->cosTab, m->sinTab, nullptr, pos, kcl, vcl, 0, nullptr,
+                                   seqStride, headStride, 0, m->maxSeq, 1, 1, Hkv, D, nullptr);
+            if (rc) return 100 + rc;
+            size_t need = m->decodeWs(1, Hq, Hkv, D, S, 0);
+            if (need > m->wsBytes) return -3;
+            rc = m->decode(m->q, 0, kcl, vcl, 0, nullptr, seqStride, headStride, nullptr, S, m->attn, 0, nullptr, 1, Hq,
+                           Hkv, D, scale, 0, m->ws, need, nullptr);
+            if (rc) return 200 + rc;
+        }
+        if (attn_dump) cudaMemcpyAsync(attn_dump + (size_t)l * n, m->attn, n * sizeof(float), cudaMemcpyDeviceToDevice, 0);
+        float *nx = ref_layer_tail(m, l, 1, cur);
+        /* ping-pong between x and xnew so the next layer's residual input is not overwritten */
+        if (nx == m->xnew) { std::swap(m->x, m->xnew); cur = m->x; }
+    }
+    gpu_rmsnorm_affine_fwd(cur, m->lnFg, m->xn, m->rms, 1, n);
+    ref_sgemm(2, 1, m->vocab, n, m->xn, m->lmHead, m->logits);
+    pos += 1;
+    CK(cudaMemcpy(logits_host, m->logits, (size_t)m->vocab * sizeof(float), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+/* forward() over S prompt tokens (src/model.nim:454-549) with the LIBRARY's prefill as the
+ * attention block, filling the library-side cache.  attn_dump: device [nLayer, S, nEmbd] or
+ * NULL; logits_last_host: [vocab] of the last position. */
+int ref_model_prefill_lib(void *h, const int *tokens_host, int S, float *attn_dump, float *logits_last_host) {
+    RefModel *m = (RefModel *)h;
+    if (S > m->maxPrefill || !m->prefill) return -2;
+    int n = m->nEmbd, D = m->headDim, Hq = m->nHead, Hkv = m->nKvHead, nKv = Hkv * D;
+    float scale = 1.0f / sqrtf((float)D);
+    CK(cudaMemcpy(m->tokIds, tokens_host, S * sizeof(int), cudaMemcpyHostToDevice));
+    gpu_embed_fwd(m->wte, m->tokIds, m->x, S, n);
+    float *cur = m->x;
+    int64_t headStride = (int64_t)m->maxSeq * D, seqStride = headStride * Hkv;
+    for (int l = 0; l < m->nLayer; l++) {
+        gpu_rmsnorm_affine_fwd(cur, m->ln1[l], m->xn, m->rms, S, n);
+        ref_sgemm(2, S, n, n, m->xn, m->wq[l], m->q);
+        ref_sgemm(2, S, nKv, n, m->xn, m->wk[l], m->k);
+        ref_sgemm(2, S, nKv, n, m->xn, m->wv[l], m->v);
+        int rc = m->prefill(m->q, m->k, m->v, 0, m->cosTab, m->sinTab, 0, m->attn, 1, S, Hq, Hkv, D, scale, 0,
+                            m->mk + (size_t)l * seqStride, m->mv + (size_t)l * seqStride, 0, nullptr, seqStride,
+                            headStride, m->maxSeq, nullptr, nullptr, 0, nullptr);
+        if (rc) return 300 + rc;
+        if (attn_dump)
+            cudaMemcpyAsync(attn_dump + (size_t)l * S * n, m->attn, (size_t)S * n * sizeof(float), cudaMemcpyDeviceToDevice, 0);
+        float *nx = ref_layer_tail(m, l, S, cur);
+        if (nx == m->xnew) { std::swap(m->x, m->xnew); cur = m->x; }
+    }
+    gpu_rmsnorm_affine_fwd(cur, m->lnFg, m->xn, m->rms, S, n);
+    ref_sgemm(2, S, m->vocab, n, m->xn, m->lmHead, m->logits);
+    m->mpos = S;
+    CK(cudaMemcpy(logits_last_host, m->logits + (size_t)(S - 1) * m->vocab, (size_t)m->vocab * sizeof(float),
+                  cudaMemcpyDeviceToHost));
     return 0;
 }
 
