@@ -379,9 +379,6 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_kernel(DecodeParams 
 #pragma unroll
         for (int u = 0; u < BLK; u++) consume_frag<D>(f[u], qreg, o, m, l, row + u * 16, r1, t, p.scale_log2e);
     };
-    // the first K/V rows are requested before the query: neither address depends on the other,
-    // and the query's latency then hides behind the rows'
-    if (rb < r1) load(fa, rb);
     // A operand: Q[head g][c*32 + t*8 .. +7] as bf16 pairs (zero for padding heads)
 #pragma unroll
     for (int c = 0; c < D / 32; c++) {
@@ -393,6 +390,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_kernel(DecodeParams 
 #pragma unroll
         for (int i = 0; i < 4; i++) qreg[c][i] = pack_bf16(x[2 * i], x[2 * i + 1]);
     }
+    if (rb < r1) load(fa, rb);
     while (rb < r1) {
         if (rb + STEP < r1) load(fb, rb + STEP);
         consume(fa, rb);
