@@ -378,39 +378,54 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             // the bf16 results drop into the swizzled tile without bank conflicts.  Rotated
             // values also go back to global when the caller keeps Q (saveCache).
             const int c8 = (lane & 7) * 8;
-#pragma unroll 2
-            for (int step = 0; step < 8; step++) {
-                const int row = step * 32 + warp * 4 + (lane >> 3);     // 0..255 over both tiles
-                const int tile_i = row >> 7, rr = row & 127;
-                const int pos = row_base + row;
-                uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                if (pos < p.S) {
-                    __nv_bfloat16 *qg = p.q + ((int64_t)b * p.S + pos) * p.Hq * kD + (int64_t)h * kD + c8;
-                    const float *ct = p.cos_tab + (int64_t)(p.pos0 + pos) * (kD / 2) + c8;
-                    const float *st = p.sin_tab + (int64_t)(p.pos0 + pos) * (kD / 2) + c8;
-                    lo = *reinterpret_cast<const uint4 *>(qg);
-                    hi = *reinterpret_cast<const uint4 *>(qg + kD / 2);
-                    float cs[8], sn[8], x0[8], x1[8], a[8], d[8];
-                    *reinterpret_cast<float4 *>(cs) = *reinterpret_cast<const float4 *>(ct);
-                    *reinterpret_cast<float4 *>(cs + 4) = *reinterpret_cast<const float4 *>(ct + 4);
-                    *reinterpret_cast<float4 *>(sn) = *reinterpret_cast<const float4 *>(st);
-                    *reinterpret_cast<float4 *>(sn + 4) = *reinterpret_cast<const float4 *>(st + 4);
-                    Elem<__nv_bfloat16>::unpack(lo, x0);
-                    Elem<__nv_bfloat16>::unpack(hi, x1);
+#pragma unroll 1
+            for (int half_i = 0; half_i < 2; half_i++) {       // tile 0, then tile 1
+                // all 24 loads of four steps are issued before any of them is used
+                uint4 lo[4], hi[4];
+                float4 cs0[4], cs1[4], sn0[4], sn1[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int row = (half_i * 4 + u) * 32 + warp * 4 + (lane >> 3);     // 0..255 over both tiles
+                    const int pos = row_base + row;
+                    lo[u] = hi[u] = make_uint4(0, 0, 0, 0);
+                    cs0[u] = cs1[u] = sn0[u] = sn1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (pos < p.S) {
+                        const __nv_bfloat16 *qg = p.q + ((int64_t)b * p.S + pos) * p.Hq * kD + (int64_t)h * kD + c8;
+                        const float *ct = p.cos_tab + (int64_t)(p.pos0 + pos) * (kD / 2) + c8;
+                        const float *st = p.sin_tab + (int64_t)(p.pos0 + pos) * (kD / 2) + c8;
+                        lo[u] = *reinterpret_cast<const uint4 *>(qg);
+                        hi[u] = *reinterpret_cast<const uint4 *>(qg + kD / 2);
+                        cs0[u] = *reinterpret_cast<const float4 *>(ct);
+                        cs1[u] = *reinterpret_cast<const float4 *>(ct + 4);
+                        sn0[u] = *reinterpret_cast<const float4 *>(st);
+                        sn1[u] = *reinterpret_cast<const float4 *>(st + 4);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int row = (half_i * 4 + u) * 32 + warp * 4 + (lane >> 3);
+                    const int tile_i = row >> 7, rr = row & 127;
+                    const int pos = row_base + row;
+                    const float cs[8] = {cs0[u].x, cs0[u].y, cs0[u].z, cs0[u].w, cs1[u].x, cs1[u].y, cs1[u].z, cs1[u].w};
+                    const float sn[8] = {sn0[u].x, sn0[u].y, sn0[u].z, sn0[u].w, sn1[u].x, sn1[u].y, sn1[u].z, sn1[u].w};
+                    float x0[8], x1[8], a[8], d[8];
+                    Elem<__nv_bfloat16>::unpack(lo[u], x0);
+                    Elem<__nv_bfloat16>::unpack(hi[u], x1);
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         a[i] = x0[i] * cs[i] - x1[i] * sn[i];
                         d[i] = x0[i] * sn[i] + x1[i] * cs[i];
                     }
-                    lo = make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
-                    hi = make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
-                    if (p.write_back_q) {
-                        *reinterpret_cast<uint4 *>(qg) = lo;
-                        *reinterpret_cast<uint4 *>(qg + kD / 2) = hi;
+                    const uint4 rlo = make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
+                    const uint4 rhi = make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
+                    if (p.write_back_q && pos < p.S) {
+                        __nv_bfloat16 *qg = p.q + ((int64_t)b * p.S + pos) * p.Hq * kD + (int64_t)h * kD + c8;
+                        *reinterpret_cast<uint4 *>(qg) = rlo;
+                        *reinterpret_cast<uint4 *>(qg + kD / 2) = rhi;
                     }
+                    *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8)) = rlo;
+                    *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8 + kD / 2)) = rhi;
                 }
-                *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8)) = lo;
-                *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8 + kD / 2)) = hi;
             }
             // make the generic-proxy stores visible to the tensor core's async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
