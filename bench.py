@@ -227,9 +227,14 @@ def run_decode(args, dist, name):
                 seq_stride=Hkv * cap * D, head_stride=cap * D, scale=w["scale"], chunk_rows=args.chunk_rows)
     out = torch.empty(B, Hq * D, dtype=torch.float32, device="cuda")
     sharded = name == "c5" and dist.world > 1
+    xch = None
     if sharded:
         W = D + 4
         gathered = torch.empty(dist.world, B * Hq, W, dtype=torch.float32, device="cuda")
+        if args.exchange == "p2p":
+            from nimllm_b200 import sharding
+            xch = sharding.PeerExchange(B * Hq, D)
+            merged = torch.empty(B * Hq, D, dtype=torch.float32, device="cuda")
 
     turn = [0]
 
@@ -237,6 +242,11 @@ def run_decode(args, dist, name):
         i = turn[0] = (turn[0] + 1) % len(w["kcs"])
         if not sharded:
             A.decode_batch(w["q"], w["kcs"][i], w["vcs"][i], out=out, **geom)
+        elif xch is not None:
+            # records go straight into every peer's buffer (NVLink stores + flags), then a bounded
+            # wait and the merge: no collective library on the data path
+            _, rec = A.decode_batch(w["q"], w["kc"], w["vc"], out=out, partials=True, **geom)
+            xch.combine(rec, merged)
         else:
             _, rec = A.decode_batch(w["q"], w["kc"], w["vc"], out=out, partials=True, **geom)
             dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
@@ -296,6 +306,9 @@ def run_decode(args, dist, name):
         if not sharded:
             A.decode_batch(dq, kci, vci, out=out, **geom)
             hout.copy_(out, non_blocking=True)
+        elif xch is not None:
+            _, rec = A.decode_batch(dq, w["kc"], w["vc"], out=out, partials=True, **geom)
+            hout.copy_(xch.combine(rec, merged).view(B, E), non_blocking=True)
         else:
             _, rec = A.decode_batch(dq, w["kc"], w["vc"], out=out, partials=True, **geom)
             dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
@@ -318,7 +331,9 @@ def run_decode(args, dist, name):
         "config": {"workload": {"c3": "C3 batched GQA decode: 256 ragged sequences per GPU, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
                                 "c5": "C5 long-context decode: 8 x 131072 rows, 32q/8kv heads, D=128, bf16 KV, KV sequence sharded over the GPUs"}[name],
                    "batch_per_gpu": B, "kv_rows_total": int(w["lens"].astype(np.int64).sum()),
-                   "parallelism": ("kv-sequence shards + NCCL all-gather of (o,m,l)" + (", step replayed as a CUDA graph" if graphed else "") if sharded else
+                   "parallelism": (("kv-sequence shards, (o,m,l) records stored into the peers' buffers over NVLink + flags + merge"
+                                    if xch is not None else "kv-sequence shards + NCCL all-gather of (o,m,l) + merge") +
+                                   (", step replayed as a CUDA graph" if graphed else "") if sharded else
                                    f"independent sequences x{dist.world}, no collective"),
                    "l2": ("inputs larger than L2: the timed loop rotates over 3 replicas of the 453 MB batch"
                           if name == "c3" else "inputs larger than L2: 4.3 GB (or its shard) streamed once per step") +
@@ -333,6 +348,10 @@ def run_decode(args, dist, name):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": sampler.summary(),
     }
+    if xch is not None:
+        line["config"]["peer_exchange_ok"] = xch.ok()
+        dist.barrier()
+        xch.close()
     if dist.rank == 0 and dist.world == 1:
         line["cpu_baseline"] = cpu_baseline_decode(w, reps=3)
     return line
@@ -534,6 +553,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=["c3", "c5", "c4"])
     ap.add_argument("--chunk-rows", type=int, default=0)
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="c5 on several GPUs: how the shards' partial records meet (peer stores or NCCL all-gather)")
     ap.add_argument("--shape", default="", help="override: c5 -> B,Hq,Hkv,D,L ; c4 -> B,S,Hq,Hkv (profiling only)")
     args = ap.parse_args()
     global SHAPE_OVERRIDE

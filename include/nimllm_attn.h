@@ -152,6 +152,25 @@ int nimllm_attn_decode_noalloc(const void *q, int q_dtype, const void *k_cache, 
 int nimllm_attn_combine(const float *parts, int n_parts, int rows, int head_dim, int rec_stride,
                         void *out, int out_dtype, float *partials_out, void *stream);
 
+/* ---- exchange and merge of KV-sequence shards over peer memory ------------------------
+ * No counterpart in the reference (single GPU).  One process per GPU of a box; every rank's
+ * decode has produced records [rows, D+4] (partials_out above) for ITS rows of the KV sequence.
+ * nimllm_attn_combine_peers stores them into every peer's exchange buffer over NVLink (plain
+ * peer stores, then a per-rank flag), waits -- at most about a second, then *status_dev = 1 --
+ * for all peers' records, and merges them: the all-gather and the merge of
+ * nimllm_attn_combine in two small launches with no collective library on the path.
+ * Set-up: create a buffer per rank, pass every rank's 64-byte export handle to every other rank
+ * (any host transport), import them, then ready().  All ranks must call combine_peers the same
+ * number of times, in the same order. */
+typedef struct nimllm_peer_exchange nimllm_peer_exchange;
+nimllm_peer_exchange *nimllm_peer_exchange_create(int rank, int world, int rows_max, int head_dim);
+int nimllm_peer_exchange_export(nimllm_peer_exchange *x, void *handle_out_64_bytes);
+int nimllm_peer_exchange_import(nimllm_peer_exchange *x, int peer_rank, const void *handle_64_bytes);
+int nimllm_peer_exchange_ready(nimllm_peer_exchange *x);
+void nimllm_peer_exchange_destroy(nimllm_peer_exchange *x);
+int nimllm_attn_combine_peers(nimllm_peer_exchange *x, const float *rec_local, int rows, void *out, int out_dtype,
+                              int *status_dev, void *stream);
+
 /* ---- causal prefill ----------------------------------------------------------------
  * Replaces the attention block of forward(), src/model.nim:469-475,494-508: RoPE on
  * q and k, then per query head gather / cublasSgemm_v2 QK^T / gpu_causal_mask /

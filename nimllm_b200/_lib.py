@@ -38,6 +38,12 @@ PROTOTYPES = {
     "nimllm_attn_decode_noalloc": (i32, [vp, i32, vp, vp, i32, vp, i64, i64, vp, i32, vp, i32, vp, i32, i32, i32,
                                          i32, f32, i32, vp]),
     "nimllm_attn_combine": (i32, [vp, i32, i32, i32, i32, vp, i32, vp, vp]),
+    "nimllm_peer_exchange_create": (vp, [i32, i32, i32, i32]),
+    "nimllm_peer_exchange_export": (i32, [vp, vp]),
+    "nimllm_peer_exchange_import": (i32, [vp, i32, vp]),
+    "nimllm_peer_exchange_ready": (i32, [vp]),
+    "nimllm_peer_exchange_destroy": (None, [vp]),
+    "nimllm_attn_combine_peers": (i32, [vp, vp, i32, vp, i32, vp, vp]),
     "nimllm_attn_prefill_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "nimllm_attn_prefill": (i32, [vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, i32,
                                   vp, vp, i32, vp, i64, i64, i32, vp, vp, sz, vp]),

@@ -416,6 +416,275 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_kernel(DecodeParams 
     merge_warps_and_emit<D, NW>(p, sm_m, sm_l, sm_o, NH, p.G, b, hq0, chunk, n_chunks);
 }
 
+// ------------------------------------------------------- balanced mma kernel (no chunk grid)
+// The grid above gives every (sequence, KV head, chunk) its own CTA: a batch is a few rounds of
+// CTAs, and every round pays the start-up of a CTA again (sequence length -> offsets -> q ->
+// first rows: about 3.3 us per round measured on B200) plus the ragged tail of unequal lengths.
+// Here the whole batch is ONE flattened list of row units (U = 16 * BLK rows), ordered by
+// sequence, KV head, row; it is cut into as many equal spans as there are warps in a grid that
+// fills the GPU exactly once, and every warp streams its own span on its own:
+//   * one start-up per launch instead of one per round, no tail, no block-level barrier after
+//     the prefix sum;
+//   * a span may cover the end of one (sequence, KV head) pair, any number of whole pairs and
+//     the start of another.  Whole pairs are written out directly; the at most two cut pairs of
+//     a warp go to the warp's two record slots, and combine_balanced_kernel merges the pieces of
+//     every cut pair (the warps holding them are consecutive, so it finds them by arithmetic).
+constexpr int kBalMaxB = 4096;      // sequences whose unit counts fit the shared-memory prefix
+constexpr int kBalMinUnits = 4;     // a warp gets at least this many units (small batches use fewer warps)
+
+// warp w of wa owns units [w*T/wa, (w+1)*T/wa); the warp owning unit u:
+__device__ __forceinline__ int64_t bal_first_unit(int w, int64_t T, int wa) { return (int64_t)w * T / wa; }
+__device__ __forceinline__ int bal_owner(int64_t u, int64_t T, int wa) { return (int)(((u + 1) * wa - 1) / T); }
+__device__ __forceinline__ int bal_active_warps(int64_t T, int wk) {
+    int64_t a = T / kBalMinUnits;
+    return (int)(a < 1 ? 1 : (a > wk ? wk : a));
+}
+
+template <int D, int MINB, int BLK, int NW>
+__global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(DecodeParams p, int *cum_out) {
+    constexpr int U = 16 * BLK;
+    constexpr int W = D + 4;
+    __shared__ int s_cum[kBalMaxB + 1];
+    __shared__ int s_warp[NW];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n_uniform = (p.max_len + U - 1) / U;
+
+    if (p.seq_len) {
+        // exclusive prefix of the unit counts of the sequences (one KV head's worth)
+        const int per = (p.B + NW * 32 - 1) / (NW * 32);
+        const int i_beg = min(p.B, (int)threadIdx.x * per), i_end = min(p.B, i_beg + per);
+        int sum = 0;
+        for (int i = i_beg; i < i_end; i++) sum += (seq_rows(p, i) + U - 1) / U;
+        int incl = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += v;
+        }
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        int excl = incl - sum;
+        for (int w2 = 0; w2 < warp; w2++) excl += s_warp[w2];
+        for (int i = i_beg; i < i_end; i++) {
+            s_cum[i] = excl;
+            excl += (seq_rows(p, i) + U - 1) / U;
+        }
+        if (threadIdx.x == NW * 32 - 1) s_cum[p.B] = excl;
+        __syncthreads();
+        if (blockIdx.x == 0)
+            for (int i = threadIdx.x; i <= p.B; i += NW * 32) cum_out[i] = s_cum[i];
+    }
+    auto cum = [&](int b) -> int { return p.seq_len ? s_cum[b] : b * n_uniform; };
+
+    const int64_t T = (int64_t)p.Hkv * cum(p.B);
+    if (T == 0) return;                                   // every row is written (as zeros) by the combine kernel
+    const int wa = bal_active_warps(T, gridDim.x * NW);
+    const int w = warp * gridDim.x + blockIdx.x;          // active warps spread over all CTAs
+    if (w >= wa) return;
+    const int64_t u0 = bal_first_unit(w, T, wa), u1 = bal_first_unit(w + 1, T, wa);
+
+    int b;
+    {   // largest b whose first unit is at or before u0 (it is not empty)
+        int lo = 0, hi = p.B - 1;
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if ((int64_t)p.Hkv * cum(mid) <= u0) lo = mid; else hi = mid - 1;
+        }
+        b = lo;
+    }
+    const int E = p.Hq * D;
+    int64_t u = u0;
+    while (u < u1) {
+        const int cb = cum(b), nb = cum(b + 1) - cb;
+        const int64_t within = u - (int64_t)p.Hkv * cb;
+        if (within >= (int64_t)p.Hkv * nb) { b++; continue; }
+        const int kvh = (int)(within / nb), i0 = (int)(within % nb);
+        const int i1 = (int)min((int64_t)nb, (int64_t)i0 + (u1 - u));
+        const int r0 = i0 * U, r1 = min(seq_rows(p, b), i1 * U);
+        const int hq0 = kvh * p.G;
+        const int64_t base = (p.kv_off ? p.kv_off[b] : (int64_t)b * p.seq_stride) + (int64_t)kvh * p.head_stride;
+        const __nv_bfloat16 *kb = reinterpret_cast<const __nv_bfloat16 *>(p.k) + base;
+        const __nv_bfloat16 *vb = reinterpret_cast<const __nv_bfloat16 *>(p.v) + base;
+
+        KvFrag<D> fa[BLK], fb[BLK];
+        uint32_t qreg[D / 32][4];
+        float o[D / 8][2];
+#pragma unroll
+        for (int i = 0; i < D / 8; i++) { o[i][0] = 0.f; o[i][1] = 0.f; }
+        float m = -INFINITY, l = 0.f;
+        auto load = [&](KvFrag<D> *f, int row) {
+#pragma unroll
+            for (int x = 0; x < BLK; x++) load_frag<D>(f[x], kb, vb, row + x * 16, r1 - 1, g, t);
+        };
+        auto consume = [&](const KvFrag<D> *f, int row) {
+#pragma unroll
+            for (int x = 0; x < BLK; x++) consume_frag<D>(f[x], qreg, o, m, l, row + x * 16, r1, t, p.scale_log2e);
+        };
+        int rb = r0;
+        load(fa, rb);                                     // in flight together with the q loads below
+#pragma unroll
+        for (int c = 0; c < D / 32; c++) {
+            float x[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                x[i] = g < p.G ? load_as_f32(p.q, p.q_dtype, (int64_t)b * E + (int64_t)(hq0 + g) * D + c * 32 + t * 8 + i)
+                               : 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; i++) qreg[c][i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+        }
+        while (rb < r1) {
+            if (rb + U < r1) load(fb, rb + U);
+            consume(fa, rb);
+            rb += U;
+            if (rb >= r1) break;
+            if (rb + U < r1) load(fa, rb + U);
+            consume(fb, rb);
+            rb += U;
+        }
+
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        if (g < p.G) {
+            if (i0 == 0 && i1 == nb) {                    // the whole pair: final result
+                const int64_t row = (int64_t)b * p.Hq + hq0 + g;
+                // accumulator tile h*8+j, element e  <->  column h*64 + (2t+e)*8 + j
+#pragma unroll
+                for (int h = 0; h < D / 64; h++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const int col = h * 64 + (2 * t + e) * 8 + j;
+                            const float val = o[h * 8 + j][e] * inv;
+                            if (p.out) store_from_f32(p.out, p.out_dtype, row * D + col, val);
+                            if (p.partials_out) p.partials_out[row * W + col] = val;
+                        }
+                if (p.partials_out && t == 0) {
+                    float *rec = p.partials_out + row * W;
+                    rec[D] = m * kLn2; rec[D + 1] = l; rec[D + 2] = 0.f; rec[D + 3] = 0.f;
+                }
+            } else {                                      // a piece: slot 0 if it opens the span, else 1
+                const int slot = (u == u0) ? 0 : 1;
+                float *rec = p.ws + (((int64_t)w * 2 + slot) * p.G + g) * W;
+#pragma unroll
+                for (int h = 0; h < D / 64; h++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        float4 lo4 = make_float4(o[h * 8 + 0][e] * inv, o[h * 8 + 1][e] * inv, o[h * 8 + 2][e] * inv, o[h * 8 + 3][e] * inv);
+                        float4 hi4 = make_float4(o[h * 8 + 4][e] * inv, o[h * 8 + 5][e] * inv, o[h * 8 + 6][e] * inv, o[h * 8 + 7][e] * inv);
+                        float4 *dst = reinterpret_cast<float4 *>(rec + h * 64 + (2 * t + e) * 8);
+                        dst[0] = lo4;
+                        dst[1] = hi4;
+                    }
+                if (t == 0) *reinterpret_cast<float4 *>(rec + D) = make_float4(m * kLn2, l, 0.f, 0.f);
+            }
+        }
+        u += i1 - i0;
+    }
+}
+
+struct BalCombineParams {
+    const float *recs;
+    const int *cum;
+    const int32_t *seq_len;
+    void *out;
+    float *partials_out;
+    int out_dtype;
+    int B, Hq, Hkv, G, D, W, U, max_len, wk;
+};
+
+// One warp per output row (sequence, query head): rows of empty sequences become zeros, rows
+// whose pair one warp covered are already final, the others merge the records of the
+// consecutive warps that hold their pieces.
+__global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams c) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= c.B * c.Hq) return;
+    const int b = row / c.Hq, hq = row % c.Hq, kvh = hq / c.G, g = hq % c.G;
+    const int n_uniform = (c.max_len + c.U - 1) / c.U;
+    const int cb = c.seq_len ? c.cum[b] : b * n_uniform;
+    const int nb = (c.seq_len ? c.cum[b + 1] : (b + 1) * n_uniform) - cb;
+    const int64_t T = (int64_t)c.Hkv * (c.seq_len ? c.cum[c.B] : c.B * n_uniform);
+    if (nb == 0) {
+        for (int d = lane; d < c.D; d += 32) {
+            if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, 0.f);
+            if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = 0.f;
+        }
+        if (c.partials_out && lane == 0) {
+            float *o = c.partials_out + (int64_t)row * c.W;
+            o[c.D] = -INFINITY; o[c.D + 1] = 0.f; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
+        }
+        return;
+    }
+    const int wa = bal_active_warps(T, c.wk);
+    const int64_t s = (int64_t)c.Hkv * cb + (int64_t)kvh * nb;
+    const int w_first = bal_owner(s, T, wa), w_last = bal_owner(s + nb - 1, T, wa);
+    if (w_first == w_last) return;
+    const int n = w_last - w_first + 1;
+    const int slot_first = bal_first_unit(w_first, T, wa) < s ? 1 : 0;
+    auto rec_of = [&](int i) -> const float * {
+        return c.recs + (((int64_t)(w_first + i) * 2 + (i == 0 ? slot_first : 0)) * c.G + g) * c.W;
+    };
+    float M = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+        const float *r = rec_of(i);
+        if (r[c.D + 1] > 0.f) M = fmaxf(M, r[c.D]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float safe = (M == -INFINITY) ? 0.f : M;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    float wsum = 0.f;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+        float w_mine = 0.f;
+        if (i0 + lane < n) {
+            const float *r = rec_of(i0 + lane);
+            const float li = r[c.D + 1];
+            w_mine = li > 0.f ? li * ex2((r[c.D] - safe) * kLog2e) : 0.f;
+        }
+        const int cnt = min(32, n - i0);
+        for (int ii = 0; ii < cnt; ii += 4) {
+            float v[4][8], wt[4];
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const bool ok = ii + x < cnt;
+                const float *r = rec_of(i0 + ii + (ok ? x : 0));
+                wt[x] = ok ? __shfl_sync(0xffffffffu, w_mine, (ii + x) & 31) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int d = lane + 32 * j;
+                    v[x][j] = d < c.D ? r[d] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                wsum += wt[x];
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[j] = fmaf(wt[x], v[x][j], acc[j]);
+            }
+        }
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int d = lane + 32 * j;
+        if (d < c.D) {
+            const float val = acc[j] * inv;
+            if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, val);
+            if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = val;
+        }
+    }
+    if (c.partials_out && lane == 0) {
+        float *o = c.partials_out + (int64_t)row * c.W;
+        o[c.D] = M; o[c.D + 1] = wsum; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
+    }
+}
+
 // ------------------------------------------------------------------ combine kernel
 // One warp per output row (sequence, query head).  parts[(part * rows + row) * W].
 // With seq_len given, the number of parts of a row is the number of chunks of its
@@ -504,7 +773,40 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
     }
 }
 
-int g_force_kernel = 0;  // 0 auto, 1 generic, 2 mma (testing hook)
+int g_force_kernel = 0;  // 0 auto, 1 generic, 2 mma on the chunk grid, 3 balanced mma (testing hook)
+
+int auto_chunk_rows(int B, int Hkv, int max_len);
+
+// launch shape of the balanced kernel: a grid that fills the GPU exactly once
+struct BalShape { int minb, nw, unit, grid; };
+BalShape bal_shape(int head_dim) {
+    BalShape s;
+    s.minb = head_dim == 64 ? 1 : 2;
+    s.nw = head_dim == 64 ? 8 : 4;
+    s.unit = head_dim == 64 ? 32 : 16;
+    s.grid = sm_count() * s.minb;
+    return s;
+}
+size_t bal_record_bytes(int n_head, int n_kv_head, int head_dim) {
+    BalShape s = bal_shape(head_dim);
+    size_t b = (size_t)s.grid * s.nw * 2 * (n_head / n_kv_head) * rec_stride(head_dim) * sizeof(float);
+    return (b + 15) / 16 * 16;
+}
+// 0 when the shape is outside what the balanced kernel takes
+size_t bal_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim, int max_len, bool ragged) {
+    if (head_dim != 64 && head_dim != 128) return 0;
+    if (n_head % n_kv_head != 0 || n_head / n_kv_head > 8) return 0;
+    if (ragged && batch > kBalMaxB) return 0;
+    BalShape s = bal_shape(head_dim);
+    if ((int64_t)batch * ((max_len + s.unit - 1) / s.unit) >= (1ll << 30)) return 0;
+    return bal_record_bytes(n_head, n_kv_head, head_dim) + ((size_t)batch + 1) * sizeof(int);
+}
+size_t split_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim, int max_len, int chunk_rows) {
+    if (chunk_rows <= 0) chunk_rows = auto_chunk_rows(batch, n_kv_head, max_len);
+    int max_chunks = (max_len + chunk_rows - 1) / chunk_rows;
+    if (max_chunks <= 1) return 0;
+    return (size_t)max_chunks * batch * n_head * rec_stride(head_dim) * sizeof(float);
+}
 
 
 int auto_chunk_rows(int B, int Hkv, int max_len) {
@@ -551,10 +853,12 @@ void nimllm_attn_debug_force_decode_kernel(int which) { g_force_kernel = which; 
 size_t nimllm_attn_decode_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim,
                                           int max_len, int chunk_rows) {
     if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || max_len <= 0) return 0;
-    if (chunk_rows <= 0) chunk_rows = auto_chunk_rows(batch, n_kv_head, max_len);
-    int max_chunks = (max_len + chunk_rows - 1) / chunk_rows;
-    if (max_chunks <= 1) return 0;
-    return (size_t)max_chunks * batch * n_head * rec_stride(head_dim) * sizeof(float);
+    // with chunk_rows = 0 the library picks the kernel: enough for either choice (the balanced
+    // kernel keeps two records per warp and the prefix of the sequences' unit counts)
+    const size_t split = split_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
+    if (chunk_rows > 0 || n_head % n_kv_head != 0) return split;
+    const size_t bal = bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, true);
+    return split > bal ? split : bal;
 }
 
 int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const void *v_cache,
@@ -575,13 +879,23 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
     if (chunk_rows < 0 || (chunk_rows > 0 && chunk_rows % 64 != 0))
         return fail(NIMLLM_ERR_ARG, "attn_decode: chunk_rows must be a multiple of 64");
     if (batch > 65535) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: batch %d > 65535", batch);
-    if (chunk_rows == 0) chunk_rows = auto_chunk_rows(batch, n_kv_head, max_len);
-    const int max_chunks = (max_len + chunk_rows - 1) / chunk_rows;
-    const size_t need = nimllm_attn_decode_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
-    if (need > 0 && (!workspace || workspace_bytes < need))
-        return fail(NIMLLM_ERR_WORKSPACE, "attn_decode: workspace %zu bytes, need %zu", workspace_bytes, need);
     if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
         return fail(NIMLLM_ERR_ARG, "attn_decode: cache pointers must be 16-byte aligned");
+    const bool mma_ok = cache_dtype == NIMLLM_BF16 && n_head / n_kv_head <= 8;
+    // The balanced kernel is the default for a bf16 cache when the caller leaves the chunking to
+    // the library and the workspace holds its records; an explicit chunk_rows keeps the chunk grid.
+    const size_t bal_need = (mma_ok && chunk_rows == 0 && g_force_kernel != 1 && g_force_kernel != 2)
+                                ? bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, seq_len != nullptr)
+                                : 0;
+    const bool balanced = bal_need > 0 && workspace && workspace_bytes >= bal_need && !((uintptr_t)workspace & 15);
+    if (g_force_kernel == 3 && !balanced)
+        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: the balanced kernel needs a bf16 cache, Hq/Hkv <= 8, "
+                                            "chunk_rows = 0 and a workspace of %zu bytes", bal_need);
+    if (chunk_rows == 0) chunk_rows = auto_chunk_rows(batch, n_kv_head, max_len);
+    const int max_chunks = (max_len + chunk_rows - 1) / chunk_rows;
+    const size_t need = balanced ? bal_need : split_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(NIMLLM_ERR_WORKSPACE, "attn_decode: workspace %zu bytes, need %zu", workspace_bytes, need);
     if (need > 0 && ((uintptr_t)workspace & 15))
         return fail(NIMLLM_ERR_ARG, "attn_decode: workspace must be 16-byte aligned");
 
@@ -595,8 +909,23 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
     p.scale_log2e = scale * kLog2e;
     cudaStream_t st = (cudaStream_t)stream;
 
+    if (balanced) {
+        const BalShape bs = bal_shape(head_dim);
+        int *cum = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(workspace) +
+                                           bal_record_bytes(n_head, n_kv_head, head_dim));
+        if (head_dim == 64) decode_mma_balanced_kernel<64, 1, 2, 8><<<bs.grid, 256, 0, st>>>(p, cum);
+        else decode_mma_balanced_kernel<128, 2, 1, 4><<<bs.grid, 128, 0, st>>>(p, cum);
+        NIMLLM_CHECK_LAUNCH("attn_decode balanced");
+        BalCombineParams c;
+        c.recs = p.ws; c.cum = cum; c.seq_len = seq_len; c.out = out; c.partials_out = partials_out;
+        c.out_dtype = out_dtype; c.B = batch; c.Hq = n_head; c.Hkv = n_kv_head; c.G = p.G; c.D = head_dim;
+        c.W = rec_stride(head_dim); c.U = bs.unit; c.max_len = max_len; c.wk = bs.grid * bs.nw;
+        combine_balanced_kernel<<<(batch * n_head + 3) / 4, 128, 0, st>>>(c);
+        NIMLLM_CHECK_LAUNCH("attn_decode balanced combine");
+        return NIMLLM_OK;
+    }
+
     dim3 grid(max_chunks, n_kv_head, batch);
-    const bool mma_ok = cache_dtype == NIMLLM_BF16 && p.G <= 8;
     if (g_force_kernel == 2 && !mma_ok)
         return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: mma kernel needs a bf16 cache and Hq/Hkv <= 8");
     const bool use_mma = mma_ok && g_force_kernel != 1;
@@ -657,7 +986,8 @@ int nimllm_attn_decode_noalloc(const void *q, int q_dtype, const void *k_cache, 
                         cudaGetErrorString(e));
         scratch_ptr[dev] = ptr;
     }
-    const size_t need = nimllm_attn_decode_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
+    // what the chunk grid needs; the balanced kernel is used when its records fit as well
+    const size_t need = split_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
     if (need > kBuiltinScratchBytes)
         return fail(NIMLLM_ERR_WORKSPACE,
                     "attn_decode_noalloc: this call needs %zu bytes of chunk records but the built-in scratch holds "

@@ -59,3 +59,49 @@ def gather_partials(rec, group=None):
     out = torch.empty((world,) + tuple(rec.shape), dtype=rec.dtype, device=rec.device)
     dist.all_gather_into_tensor(out.view(-1), rec.contiguous().view(-1), group=group)
     return out
+
+
+class PeerExchange:
+    """Per-rank exchange buffer for KV-sequence-shard partials, wired to the other ranks of the
+    box through CUDA IPC handles passed over the (host-side) process group.  combine() is the
+    data path: peer stores + flags + bounded wait + merge, no collective."""
+
+    def __init__(self, rows_max: int, head_dim: int, group=None):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        from ._lib import check, lib
+        self._lib, self._check = lib(), check
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.head_dim = head_dim
+        self.handle = self._lib.nimllm_peer_exchange_create(self.rank, self.world, rows_max, head_dim)
+        if not self.handle:
+            raise RuntimeError(self._lib.nimllm_attn_last_error().decode())
+        mine = C.create_string_buffer(64)
+        check(self._lib.nimllm_peer_exchange_export(self.handle, mine))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(mine.raw), group=group)
+        for r, h in enumerate(handles):
+            check(self._lib.nimllm_peer_exchange_import(self.handle, r, C.create_string_buffer(h, 64)))
+        check(self._lib.nimllm_peer_exchange_ready(self.handle))
+        dist.barrier(group)                      # every rank has mapped every buffer before first use
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def combine(self, rec, out=None):
+        """rec [rows, D+4] fp32 (this rank's records) -> merged [rows, D] fp32."""
+        import torch
+        rows = rec.shape[0]
+        if out is None:
+            out = torch.empty((rows, self.head_dim), dtype=torch.float32, device=rec.device)
+        self._check(self._lib.nimllm_attn_combine_peers(self.handle, rec.data_ptr(), rows, out.data_ptr(), 0,
+                                                        self.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        return out
+
+    def ok(self) -> bool:
+        """False if a wait for a peer's records ever ran out (synchronises)."""
+        return int(self.status.item()) == 0
+
+    def close(self):
+        if self.handle:
+            self._lib.nimllm_peer_exchange_destroy(self.handle)
+            self.handle = None

@@ -60,6 +60,41 @@ def test_bf16_cache_matches_f64_ground_truth(Hq, Hkv, D, chunk_rows, force):
     np.testing.assert_allclose(rec[:, D] + np.log(rec[:, D + 1]), (m + np.log(l)).reshape(-1), atol=3e-2)
 
 
+BAL_LENS = [0, 1, 31, 32, 33, 0, 700, 64, 2049, 5, 0, 4096, 16, 333, 1025, 0]
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(9, 3, 64), (32, 8, 128), (8, 8, 64), (8, 1, 128), (16, 2, 64), (3, 1, 128)])
+@pytest.mark.parametrize("lens", [LENS, BAL_LENS, [4096], [40000, 3], [0, 0]], ids=["short", "ragged", "one", "long", "empty"])
+def test_balanced_kernel_matches_f64_ground_truth(Hq, Hkv, D, lens):
+    """The balanced kernel cuts the flattened batch into equal spans per warp: pieces of a pair
+    held by several warps, whole pairs inside one warp, empty sequences and warps with nothing
+    to do all occur in these cases."""
+    out, rec, ref32, ref64, m, l = _run(106, lens, Hq, Hkv, D, torch.bfloat16, 0, force=3, q_dtype=torch.bfloat16)
+    assert_close(out, ref64, TOL_BF16, "balanced decode vs fp64 ground truth")
+    assert_close(rec[:, :D].reshape(out.shape), out, 1e-6, "records carry the output")
+    live = np.repeat(np.asarray(lens) > 0, Hq)
+    np.testing.assert_allclose((rec[:, D] + np.log(rec[:, D + 1]))[live], (m + np.log(l)).reshape(-1)[live], atol=3e-2)
+    assert not out[~(np.asarray(lens) > 0)].any() and not rec[~live, D + 1].any()
+
+
+def test_balanced_kernel_uniform_cache_and_refusals():
+    Hq, Hkv, D, B, L, cap = 8, 2, 128, 5, 1000, 1024
+    kv = O.from_bf16(O.to_bf16(normal(107, 0, (2, B, Hkv, cap, D))))
+    q = O.from_bf16(O.to_bf16(normal(107, 1, (B, Hq * D))))
+    _lib.lib().nimllm_attn_debug_force_decode_kernel(3)
+    kw = dict(n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=L, seq_stride=Hkv * cap * D, head_stride=cap * D)
+    out = A.decode_batch(dev(q, torch.bfloat16), dev(kv[0], torch.bfloat16), dev(kv[1], torch.bfloat16), **kw)
+    off = np.arange(B, dtype=np.int64) * Hkv * cap * D
+    ref = O.decode_batch(q, kv[0].reshape(-1), kv[1].reshape(-1), off, np.full(B, cap * D, np.int64),
+                         np.full(B, L, np.int32), Hq, Hkv, D, 1.0 / np.sqrt(D), acc64=True)
+    assert_close(host(out), ref, TOL_BF16, "balanced, seq_len = NULL")
+    # an explicit chunking or an fp32 cache keeps the chunk grid: forcing the balanced kernel is refused
+    with pytest.raises(RuntimeError):
+        A.decode_batch(dev(q, torch.bfloat16), dev(kv[0], torch.bfloat16), dev(kv[1], torch.bfloat16), chunk_rows=64, **kw)
+    with pytest.raises(RuntimeError):
+        A.decode_batch(dev(q), dev(kv[0]), dev(kv[1]), **kw)
+
+
 def test_mma_kernel_is_tight_when_p_is_exact():
     """With one attended row p = 1 exactly, so the tensor-core kernel must return that V row
     bit-exactly (bf16 -> fp32): checks fragment layouts without rounding noise."""
@@ -146,7 +181,9 @@ def test_kv_sequence_shards_combine_to_unsharded_c5_shape():
             _, rec = A.decode_batch(q, kc, vc, max_len=rows, kv_off=off, head_stride=L * D, partials=True, **base)
             recs.append(rec)
         merged = host(A.combine(torch.stack(recs), D)).reshape(B, Hq * D)
-        assert_close(merged, full, 1e-3, f"{N} shards vs unsharded")
+        # P is rounded to bf16 relative to the running maximum, which depends on where the rows
+        # are cut: sharded and unsharded agree to a fraction of the bf16 bound, not to fp32 noise
+        assert_close(merged, full, 5e-3, f"{N} shards vs unsharded", elem_tol=2e-2)
     kb, vb = bf16_bits(kc).reshape(-1), bf16_bits(vc).reshape(-1)
     ref = O.decode_batch(host(q), kb, vb, np.arange(B, dtype=np.int64) * Hkv * L * D, np.full(B, L * D, np.int64),
                          np.full(B, L, np.int32), Hq, Hkv, D, 1 / np.sqrt(D), acc64=True)
