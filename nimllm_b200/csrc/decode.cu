@@ -495,13 +495,21 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
         b = lo;
     }
     const int E = p.Hq * D;
-    int64_t u = u0;
-    while (u < u1) {
-        const int cb = cum(b), nb = cum(b + 1) - cb;
-        const int64_t within = u - (int64_t)p.Hkv * cb;
-        if (within >= (int64_t)p.Hkv * nb) { b++; continue; }
-        const int kvh = (int)(within / nb), i0 = (int)(within % nb);
-        const int i1 = (int)min((int64_t)nb, (int64_t)i0 + (u1 - u));
+    // position inside the span, kept as (sequence, KV head, unit) so that the loop carries no
+    // 64-bit state
+    int remaining = (int)(u1 - u0);
+    int kvh, i0;
+    {
+        const int nb0 = cum(b + 1) - cum(b);
+        const int64_t within = u0 - (int64_t)p.Hkv * cum(b);
+        kvh = (int)(within / nb0);
+        i0 = (int)(within % nb0);
+    }
+    bool first = true;
+    while (remaining > 0) {
+        const int nb = cum(b + 1) - cum(b);
+        if (kvh >= p.Hkv || nb == 0) { b++; kvh = 0; i0 = 0; continue; }
+        const int i1 = min(nb, i0 + remaining);
         const int r0 = i0 * U, r1 = min(seq_rows(p, b), i1 * U);
         const int hq0 = kvh * p.G;
         const int64_t base = (p.kv_off ? p.kv_off[b] : (int64_t)b * p.seq_stride) + (int64_t)kvh * p.head_stride;
@@ -567,7 +575,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
                     rec[D] = m * kLn2; rec[D + 1] = l; rec[D + 2] = 0.f; rec[D + 3] = 0.f;
                 }
             } else {                                      // a piece: slot 0 if it opens the span, else 1
-                const int slot = (u == u0) ? 0 : 1;
+                const int slot = first ? 0 : 1;
                 float *rec = p.ws + (((int64_t)w * 2 + slot) * p.G + g) * W;
 #pragma unroll
                 for (int h = 0; h < D / 64; h++)
@@ -582,7 +590,10 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
                 if (t == 0) *reinterpret_cast<float4 *>(rec + D) = make_float4(m * kLn2, l, 0.f, 0.f);
             }
         }
-        u += i1 - i0;
+        remaining -= i1 - i0;
+        first = false;
+        i0 = i1;
+        if (i0 == nb) { i0 = 0; kvh++; }
     }
 }
 
@@ -628,44 +639,71 @@ __global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams 
     auto rec_of = [&](int i) -> const float * {
         return c.recs + (((int64_t)(w_first + i) * 2 + (i == 0 ? slot_first : 0)) * c.G + g) * c.W;
     };
-    float M = -INFINITY;
-    for (int i = lane; i < n; i += 32) {
-        const float *r = rec_of(i);
-        if (r[c.D + 1] > 0.f) M = fmaxf(M, r[c.D]);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-    const float safe = (M == -INFINITY) ? 0.f : M;
+    float M = -INFINITY, wsum = 0.f;
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
-    float wsum = 0.f;
-    for (int i0 = 0; i0 < n; i0 += 32) {
-        float w_mine = 0.f;
-        if (i0 + lane < n) {
-            const float *r = rec_of(i0 + lane);
-            const float li = r[c.D + 1];
-            w_mine = li > 0.f ? li * ex2((r[c.D] - safe) * kLog2e) : 0.f;
-        }
-        const int cnt = min(32, n - i0);
-        for (int ii = 0; ii < cnt; ii += 4) {
-            float v[4][8], wt[4];
+    if (n <= 4) {
+        // the usual case (a pair cut once or twice): every load of the merge is issued before
+        // anything is computed, so the warp waits for memory once
+        float mi[4], li[4], v[4][8];
 #pragma unroll
-            for (int x = 0; x < 4; x++) {
-                const bool ok = ii + x < cnt;
-                const float *r = rec_of(i0 + ii + (ok ? x : 0));
-                wt[x] = ok ? __shfl_sync(0xffffffffu, w_mine, (ii + x) & 31) : 0.f;
+        for (int x = 0; x < 4; x++) {
+            const float *r = rec_of(x < n ? x : 0);
+            mi[x] = r[c.D];
+            li[x] = x < n ? r[c.D + 1] : 0.f;
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const int d = lane + 32 * j;
-                    v[x][j] = d < c.D ? r[d] : 0.f;
-                }
+            for (int j = 0; j < 8; j++) {
+                const int d = lane + 32 * j;
+                v[x][j] = d < c.D ? r[d] : 0.f;
             }
+        }
 #pragma unroll
-            for (int x = 0; x < 4; x++) {
-                wsum += wt[x];
+        for (int x = 0; x < 4; x++)
+            if (li[x] > 0.f) M = fmaxf(M, mi[x]);
+        const float safe = (M == -INFINITY) ? 0.f : M;
 #pragma unroll
-                for (int j = 0; j < 8; j++) acc[j] = fmaf(wt[x], v[x][j], acc[j]);
+        for (int x = 0; x < 4; x++) {
+            const float wt = li[x] > 0.f ? li[x] * ex2((mi[x] - safe) * kLog2e) : 0.f;
+            wsum += wt;
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] = fmaf(wt, v[x][j], acc[j]);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            const float *r = rec_of(i);
+            if (r[c.D + 1] > 0.f) M = fmaxf(M, r[c.D]);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        const float safe = (M == -INFINITY) ? 0.f : M;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            float w_mine = 0.f;
+            if (i0 + lane < n) {
+                const float *r = rec_of(i0 + lane);
+                const float li = r[c.D + 1];
+                w_mine = li > 0.f ? li * ex2((r[c.D] - safe) * kLog2e) : 0.f;
+            }
+            const int cnt = min(32, n - i0);
+            for (int ii = 0; ii < cnt; ii += 4) {
+                float v[4][8], wt[4];
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    const bool ok = ii + x < cnt;
+                    const float *r = rec_of(i0 + ii + (ok ? x : 0));
+                    wt[x] = ok ? __shfl_sync(0xffffffffu, w_mine, (ii + x) & 31) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int d = lane + 32 * j;
+                        v[x][j] = d < c.D ? r[d] : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    wsum += wt[x];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[j] = fmaf(wt[x], v[x][j], acc[j]);
+                }
             }
         }
     }
