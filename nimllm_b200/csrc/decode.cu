@@ -607,10 +607,11 @@ struct BalCombineParams {
     int B, Hq, Hkv, G, D, W, U, max_len, wk;
 };
 
-// One warp per output row (sequence, query head): rows of empty sequences become zeros, rows
+// Variant for batches of many pairs cut into few pieces (measured faster there than the
+// four-warp CTA per row below): one warp per output row; rows of empty sequences become zeros, rows
 // whose pair one warp covered are already final, the others merge the records of the
 // consecutive warps that hold their pieces.
-__global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams c) {
+__global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombineParams c) {
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= c.B * c.Hq) return;
@@ -718,6 +719,96 @@ __global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams 
         }
     }
     if (c.partials_out && lane == 0) {
+        float *o = c.partials_out + (int64_t)row * c.W;
+        o[c.D] = M; o[c.D + 1] = wsum; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
+    }
+}
+
+// One CTA of four warps per output row (sequence, query head): rows of empty sequences become
+// zeros, rows whose pair one warp covered are already final, the others merge the records of the
+// consecutive warps that hold their pieces.  Warp k takes pieces k, k+4, ... and loads them
+// before the row maximum is known, so the usual row (up to 16 pieces) waits for memory once for
+// its indices and once for its records; the four partial sums meet in shared memory.
+__global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams c) {
+    __shared__ float s_acc[4][256];
+    __shared__ float s_w[4];
+    const int row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = row / c.Hq, hq = row % c.Hq, kvh = hq / c.G, g = hq % c.G;
+    const int n_uniform = (c.max_len + c.U - 1) / c.U;
+    const int cb = c.seq_len ? c.cum[b] : b * n_uniform;
+    const int nb = (c.seq_len ? c.cum[b + 1] : (b + 1) * n_uniform) - cb;
+    const int64_t T = (int64_t)c.Hkv * (c.seq_len ? c.cum[c.B] : c.B * n_uniform);
+    if (nb == 0) {
+        for (int d = threadIdx.x; d < c.D; d += 128) {
+            if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, 0.f);
+            if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = 0.f;
+        }
+        if (c.partials_out && threadIdx.x == 0) {
+            float *o = c.partials_out + (int64_t)row * c.W;
+            o[c.D] = -INFINITY; o[c.D + 1] = 0.f; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
+        }
+        return;
+    }
+    const int wa = bal_active_warps(T, c.wk);
+    const int64_t s = (int64_t)c.Hkv * cb + (int64_t)kvh * nb;
+    const int w_first = bal_owner(s, T, wa), w_last = bal_owner(s + nb - 1, T, wa);
+    if (w_first == w_last) return;
+    const int n = w_last - w_first + 1;
+    const int slot_first = bal_first_unit(w_first, T, wa) < s ? 1 : 0;
+    auto rec_of = [&](int i) -> const float * {
+        return c.recs + (((int64_t)(w_first + i) * 2 + (i == 0 ? slot_first : 0)) * c.G + g) * c.W;
+    };
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    float wsum = 0.f;
+    float mi[4], li[4], v[4][8];
+    auto load_batch = [&](int i_base) {
+#pragma unroll
+        for (int x = 0; x < 4; x++) {
+            const int i = i_base + 4 * x;
+            const float *r = rec_of(i < n ? i : 0);
+            mi[x] = r[c.D];
+            li[x] = i < n ? r[c.D + 1] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int d = lane + 32 * j;
+                v[x][j] = d < c.D ? r[d] : 0.f;
+            }
+        }
+    };
+    load_batch(warp);
+    float M = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+        const float *r = rec_of(i);
+        if (r[c.D + 1] > 0.f) M = fmaxf(M, r[c.D]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float safe = (M == -INFINITY) ? 0.f : M;
+    for (int i_base = warp; i_base < n; i_base += 16) {
+        if (i_base != warp) load_batch(i_base);
+#pragma unroll
+        for (int x = 0; x < 4; x++) {
+            const float wt = li[x] > 0.f ? li[x] * ex2((mi[x] - safe) * kLog2e) : 0.f;
+            wsum += wt;
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] = fmaf(wt, v[x][j], acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) s_acc[warp][lane + 32 * j] = acc[j];
+    if (lane == 0) s_w[warp] = wsum;
+    __syncthreads();
+    wsum = (s_w[0] + s_w[1]) + (s_w[2] + s_w[3]);
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    for (int d = threadIdx.x; d < c.D; d += 128) {
+        const float val = ((s_acc[0][d] + s_acc[1][d]) + (s_acc[2][d] + s_acc[3][d])) * inv;
+        if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, val);
+        if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = val;
+    }
+    if (c.partials_out && threadIdx.x == 0) {
         float *o = c.partials_out + (int64_t)row * c.W;
         o[c.D] = M; o[c.D + 1] = wsum; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
     }
@@ -958,7 +1049,11 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
         c.recs = p.ws; c.cum = cum; c.seq_len = seq_len; c.out = out; c.partials_out = partials_out;
         c.out_dtype = out_dtype; c.B = batch; c.Hq = n_head; c.Hkv = n_kv_head; c.G = p.G; c.D = head_dim;
         c.W = rec_stride(head_dim); c.U = bs.unit; c.max_len = max_len; c.wk = bs.grid * bs.nw;
-        combine_balanced_kernel<<<(batch * n_head + 3) / 4, 128, 0, st>>>(c);
+        // few pieces per pair (a large batch): one warp per row; many pieces: a CTA per row
+        if ((int64_t)c.wk < 4ll * batch * n_kv_head)
+            combine_balanced_warp_kernel<<<(batch * n_head + 3) / 4, 128, 0, st>>>(c);
+        else
+            combine_balanced_kernel<<<batch * n_head, 128, 0, st>>>(c);
         NIMLLM_CHECK_LAUNCH("attn_decode balanced combine");
         return NIMLLM_OK;
     }
