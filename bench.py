@@ -363,6 +363,9 @@ def run_prefill(args, dist):
     KV heads (with their query heads) are split over the ranks; no collective."""
     import torch
     from nimllm_b200 import attention as A
+    if getattr(args, "prefill_variant", 0):
+        from nimllm_b200 import _lib as _l
+        _l.lib().nimllm_attn_debug_prefill_variant(args.prefill_variant)
     B, S, Hq, Hkv, D = 4, 8192, 32, 8, 128
     if SHAPE_OVERRIDE:                                  # --shape B,S,Hq,Hkv: small case for ncu captures
         B, S, Hq, Hkv = SHAPE_OVERRIDE[:4]
@@ -553,6 +556,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=["c3", "c5", "c4"])
     ap.add_argument("--chunk-rows", type=int, default=0)
+    ap.add_argument("--prefill-variant", type=int, default=0, choices=[0, 1, 2],
+                    help="c4: 0 library default, 1 one CTA per 256 query rows, 2 CTA pairs (tcgen05 cta_group::2)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="c5 on several GPUs: how the shards' partial records meet (peer stores or NCCL all-gather)")
     ap.add_argument("--shape", default="", help="override: c5 -> B,Hq,Hkv,D,L ; c4 -> B,S,Hq,Hkv (profiling only)")

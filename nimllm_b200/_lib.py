@@ -61,6 +61,7 @@ PROTOTYPES = {
 _EXTRA = {
     "nimllm_attn_debug_force_decode_kernel": (None, [i32]),
     "nimllm_attn_debug_prefill_dump": (None, [vp]),
+    "nimllm_attn_debug_prefill_variant": (None, [i32]),
 }
 
 

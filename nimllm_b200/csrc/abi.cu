@@ -184,6 +184,9 @@ int nimllm_attn_prefill(void *q, void *k, const void *v, int dtype, const float 
                                     seq_len, n_kv_head, head_dim, stream);
         if (rc) return rc;
     }
+    if (g_prefill_variant == 2)
+        return launch_prefill_tc2(q, k, v, out, lse, rope_cos, rope_sin, pos0, save_cache ? 1 : 0, batch, seq_len,
+                             n_head, n_kv_head, head_dim, scale, workspace, workspace_bytes, st);
     return launch_prefill_tc(q, k, v, out, lse, rope_cos, rope_sin, pos0, save_cache ? 1 : 0, batch, seq_len,
                              n_head, n_kv_head, head_dim, scale, workspace, workspace_bytes, st);
 }

@@ -14,6 +14,16 @@ D = 128
 BASE = 500000.0
 
 
+@pytest.fixture(autouse=True, params=[1, 2], ids=["one-cta", "cta-pair"])
+def _kernel_variant(request):
+    """Every test runs on both tensor-core kernels: one CTA per 256 query rows (the default) and
+    CTA pairs issuing tcgen05 cta_group::2 MMAs over 512 query rows."""
+    from nimllm_b200 import _lib
+    _lib.lib().nimllm_attn_debug_prefill_variant(request.param)
+    yield
+    _lib.lib().nimllm_attn_debug_prefill_variant(1)
+
+
 def _inputs(seed, B, S, Hq, Hkv):
     g = torch.Generator(device="cuda").manual_seed(seed)
     q = torch.randn(B, S, Hq * D, generator=g, device="cuda").bfloat16()
