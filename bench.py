@@ -41,7 +41,7 @@ SEEDS = {"c3": 20253, "c4": 20254, "c5": 20255}
 SHAPE_OVERRIDE = None   # set by --shape; the default shapes are the configurations of BASELINE.json
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, taken from the
 # ncu summaries under profiles/ (None until a capture exists for that workload)
-NCU_TRAFFIC_BYTES = {"c3": 462457088 + 4210944, "c5": 4295200000 + 8700000, "c4": 1860400000 + 226800000}
+NCU_TRAFFIC_BYTES = {"c3": 462484992 + 5016320, "c5": 4295632725 + 2294528, "c4": 1860400000 + 226800000}
 
 
 def log(*a):
@@ -342,7 +342,7 @@ def run_decode(args, dist, name):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": pk["hbm"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm"], 4), "traffic": NCU_TRAFFIC_BYTES[name],
                      "peak_source": pk["source"], "algorithmic_bytes_per_step": int(w["bytes"]),
-                     "kernel": "decode_mma_kernel (+ combine_kernel when sequences are split) per step, CUDA events on the launching stream; traffic from profiles/decode_mma_c3.md"},
+                     "kernel": "decode_mma_balanced_kernel + its merge launch per step, CUDA events on the launching stream; traffic of the decode kernel from profiles/decode_mma_c3.md"},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": B * (E + 2 * Ekv) * 4,
                 "d2h_bytes_per_step": B * E * 4, "ms_per_step": round(e2e_t / args.steps * 1e3, 5)},
         "gpu_launches": launches_per_step * args.steps,
