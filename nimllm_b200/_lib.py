@@ -61,6 +61,7 @@ PROTOTYPES = {
 _EXTRA = {
     "nimllm_attn_debug_force_decode_kernel": (None, [i32]),
     "nimllm_attn_debug_prefill_dump": (None, [vp]),
+    "nimllm_attn_debug_balanced_plan": (i32, [vp, i32, i32, i32, i32, vp, i32, vp]),
     "nimllm_attn_debug_prefill_variant": (None, [i32]),
 }
 

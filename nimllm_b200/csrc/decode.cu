@@ -433,11 +433,64 @@ constexpr int kBalMaxB = 4096;      // sequences whose unit counts fit the share
 constexpr int kBalMinUnits = 4;     // a warp gets at least this many units (small batches use fewer warps)
 
 // warp w of wa owns units [w*T/wa, (w+1)*T/wa); the warp owning unit u:
-__device__ __forceinline__ int64_t bal_first_unit(int w, int64_t T, int wa) { return (int64_t)w * T / wa; }
-__device__ __forceinline__ int bal_owner(int64_t u, int64_t T, int wa) { return (int)(((u + 1) * wa - 1) / T); }
-__device__ __forceinline__ int bal_active_warps(int64_t T, int wk) {
+__host__ __device__ __forceinline__ int64_t bal_first_unit(int w, int64_t T, int wa) { return (int64_t)w * T / wa; }
+__host__ __device__ __forceinline__ int bal_owner(int64_t u, int64_t T, int wa) { return (int)(((u + 1) * wa - 1) / T); }
+__host__ __device__ __forceinline__ int bal_active_warps(int64_t T, int wk) {
     int64_t a = T / kBalMinUnits;
     return (int)(a < 1 ? 1 : (a > wk ? wk : a));
+}
+
+// Walk of one warp's span, segment by segment.  `cum(b)` = units of one KV head of the sequences
+// before b.  The position is kept as (sequence, KV head, unit) so the loop carries no 64-bit state.
+// Shared by the kernel and by the host-side plan used in the CPU tests.
+struct BalWalk {
+    int b, kvh, i0, remaining;
+    bool first;
+};
+struct BalSeg {
+    int b, kvh, i0, i1, nb, slot;      // units [i0, i1) of the pair's nb; record slot when the pair is cut
+    bool whole;
+};
+template <typename CumFn>
+__host__ __device__ __forceinline__ void bal_walk_init(BalWalk &wk, int64_t u0, int64_t u1, int B, int Hkv, CumFn cum) {
+    int lo = 0, hi = B - 1;            // largest b whose first unit is at or before u0 (it is not empty)
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if ((int64_t)Hkv * cum(mid) <= u0) lo = mid; else hi = mid - 1;
+    }
+    wk.b = lo;
+    wk.remaining = (int)(u1 - u0);
+    wk.first = true;
+    wk.kvh = 0; wk.i0 = 0;
+    if (wk.remaining > 0) {
+        const int nb0 = cum(lo + 1) - cum(lo);
+        const int64_t within = u0 - (int64_t)Hkv * cum(lo);
+        wk.kvh = (int)(within / nb0);
+        wk.i0 = (int)(within % nb0);
+    }
+}
+template <typename CumFn>
+__host__ __device__ __forceinline__ bool bal_walk_next(BalWalk &wk, int Hkv, CumFn cum, BalSeg &sg) {
+    while (wk.remaining > 0) {
+        const int nb = cum(wk.b + 1) - cum(wk.b);
+        if (wk.kvh >= Hkv || nb == 0) { wk.b++; wk.kvh = 0; wk.i0 = 0; continue; }
+        sg.b = wk.b; sg.kvh = wk.kvh; sg.i0 = wk.i0; sg.nb = nb;
+        sg.i1 = nb < wk.i0 + wk.remaining ? nb : wk.i0 + wk.remaining;
+        sg.whole = sg.i0 == 0 && sg.i1 == nb;
+        sg.slot = wk.first ? 0 : 1;
+        wk.remaining -= sg.i1 - sg.i0;
+        wk.first = false;
+        wk.i0 = sg.i1;
+        if (wk.i0 == nb) { wk.i0 = 0; wk.kvh++; }
+        return true;
+    }
+    return false;
+}
+// merge side: the consecutive warps holding the pieces of the pair that starts at unit s
+__host__ __device__ __forceinline__ void bal_pair_pieces(int64_t s, int nb, int64_t T, int wa, int &w_first, int &n, int &slot_first) {
+    w_first = bal_owner(s, T, wa);
+    n = bal_owner(s + nb - 1, T, wa) - w_first + 1;
+    slot_first = bal_first_unit(w_first, T, wa) < s ? 1 : 0;
 }
 
 template <int D, int MINB, int BLK, int NW>
@@ -485,31 +538,12 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
     if (w >= wa) return;
     const int64_t u0 = bal_first_unit(w, T, wa), u1 = bal_first_unit(w + 1, T, wa);
 
-    int b;
-    {   // largest b whose first unit is at or before u0 (it is not empty)
-        int lo = 0, hi = p.B - 1;
-        while (lo < hi) {
-            int mid = (lo + hi + 1) >> 1;
-            if ((int64_t)p.Hkv * cum(mid) <= u0) lo = mid; else hi = mid - 1;
-        }
-        b = lo;
-    }
     const int E = p.Hq * D;
-    // position inside the span, kept as (sequence, KV head, unit) so that the loop carries no
-    // 64-bit state
-    int remaining = (int)(u1 - u0);
-    int kvh, i0;
-    {
-        const int nb0 = cum(b + 1) - cum(b);
-        const int64_t within = u0 - (int64_t)p.Hkv * cum(b);
-        kvh = (int)(within / nb0);
-        i0 = (int)(within % nb0);
-    }
-    bool first = true;
-    while (remaining > 0) {
-        const int nb = cum(b + 1) - cum(b);
-        if (kvh >= p.Hkv || nb == 0) { b++; kvh = 0; i0 = 0; continue; }
-        const int i1 = min(nb, i0 + remaining);
+    BalWalk walk;
+    bal_walk_init(walk, u0, u1, p.B, p.Hkv, cum);
+    BalSeg sg;
+    while (bal_walk_next(walk, p.Hkv, cum, sg)) {
+        const int b = sg.b, kvh = sg.kvh, i0 = sg.i0, i1 = sg.i1;
         const int r0 = i0 * U, r1 = min(seq_rows(p, b), i1 * U);
         const int hq0 = kvh * p.G;
         const int64_t base = (p.kv_off ? p.kv_off[b] : (int64_t)b * p.seq_stride) + (int64_t)kvh * p.head_stride;
@@ -556,7 +590,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         if (g < p.G) {
-            if (i0 == 0 && i1 == nb) {                    // the whole pair: final result
+            if (sg.whole) {                               // the whole pair: final result
                 const int64_t row = (int64_t)b * p.Hq + hq0 + g;
                 // accumulator tile h*8+j, element e  <->  column h*64 + (2t+e)*8 + j
 #pragma unroll
@@ -575,8 +609,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
                     rec[D] = m * kLn2; rec[D + 1] = l; rec[D + 2] = 0.f; rec[D + 3] = 0.f;
                 }
             } else {                                      // a piece: slot 0 if it opens the span, else 1
-                const int slot = first ? 0 : 1;
-                float *rec = p.ws + (((int64_t)w * 2 + slot) * p.G + g) * W;
+                float *rec = p.ws + (((int64_t)w * 2 + sg.slot) * p.G + g) * W;
 #pragma unroll
                 for (int h = 0; h < D / 64; h++)
 #pragma unroll
@@ -590,10 +623,6 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
                 if (t == 0) *reinterpret_cast<float4 *>(rec + D) = make_float4(m * kLn2, l, 0.f, 0.f);
             }
         }
-        remaining -= i1 - i0;
-        first = false;
-        i0 = i1;
-        if (i0 == nb) { i0 = 0; kvh++; }
     }
 }
 
@@ -633,10 +662,9 @@ __global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombinePa
     }
     const int wa = bal_active_warps(T, c.wk);
     const int64_t s = (int64_t)c.Hkv * cb + (int64_t)kvh * nb;
-    const int w_first = bal_owner(s, T, wa), w_last = bal_owner(s + nb - 1, T, wa);
-    if (w_first == w_last) return;
-    const int n = w_last - w_first + 1;
-    const int slot_first = bal_first_unit(w_first, T, wa) < s ? 1 : 0;
+    int w_first, n, slot_first;
+    bal_pair_pieces(s, nb, T, wa, w_first, n, slot_first);
+    if (n == 1) return;
     auto rec_of = [&](int i) -> const float * {
         return c.recs + (((int64_t)(w_first + i) * 2 + (i == 0 ? slot_first : 0)) * c.G + g) * c.W;
     };
@@ -752,10 +780,9 @@ __global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams 
     }
     const int wa = bal_active_warps(T, c.wk);
     const int64_t s = (int64_t)c.Hkv * cb + (int64_t)kvh * nb;
-    const int w_first = bal_owner(s, T, wa), w_last = bal_owner(s + nb - 1, T, wa);
-    if (w_first == w_last) return;
-    const int n = w_last - w_first + 1;
-    const int slot_first = bal_first_unit(w_first, T, wa) < s ? 1 : 0;
+    int w_first, n, slot_first;
+    bal_pair_pieces(s, nb, T, wa, w_first, n, slot_first);
+    if (n == 1) return;
     auto rec_of = [&](int i) -> const float * {
         return c.recs + (((int64_t)(w_first + i) * 2 + (i == 0 ? slot_first : 0)) * c.G + g) * c.W;
     };
@@ -978,6 +1005,49 @@ using namespace nimllm;
 extern "C" {
 
 void nimllm_attn_debug_force_decode_kernel(int which) { g_force_kernel = which; }
+
+// Host-side replay of the balanced kernel's work split (testing hook, no GPU needed): the same
+// walk and merge arithmetic the kernels run, for `warps` workers over sequences of `lens` rows.
+// segs_out receives (warp, sequence, kv head, first unit, end unit, slot or -1 for a whole pair)
+// per segment, pairs_out (first warp, pieces, slot of the first piece) per (sequence, KV head);
+// returns the number of segments, or -1 when max_segs is too small.
+int nimllm_attn_debug_balanced_plan(const int32_t *lens, int batch, int n_kv_head, int unit, int warps,
+                                    int32_t *segs_out, int max_segs, int32_t *pairs_out) {
+    if (!lens || batch <= 0 || n_kv_head <= 0 || unit <= 0 || warps <= 0) return -1;
+    int *cum_v = new int[batch + 1];
+    cum_v[0] = 0;
+    for (int b = 0; b < batch; b++) cum_v[b + 1] = cum_v[b] + ((lens[b] < 0 ? 0 : lens[b]) + unit - 1) / unit;
+    auto cum = [&](int b) -> int { return cum_v[b]; };
+    const int64_t T = (int64_t)n_kv_head * cum_v[batch];
+    int n_segs = 0;
+    if (T > 0) {
+        const int wa = bal_active_warps(T, warps);
+        for (int w = 0; w < wa && n_segs >= 0; w++) {
+            BalWalk walk;
+            bal_walk_init(walk, bal_first_unit(w, T, wa), bal_first_unit(w + 1, T, wa), batch, n_kv_head, cum);
+            BalSeg sg;
+            while (bal_walk_next(walk, n_kv_head, cum, sg)) {
+                if (n_segs >= max_segs) { n_segs = -1; break; }
+                int32_t *o = segs_out + 6 * n_segs++;
+                o[0] = w; o[1] = sg.b; o[2] = sg.kvh; o[3] = sg.i0; o[4] = sg.i1; o[5] = sg.whole ? -1 : sg.slot;
+            }
+        }
+        if (pairs_out)
+            for (int b = 0; b < batch; b++)
+                for (int h = 0; h < n_kv_head; h++) {
+                    int32_t *o = pairs_out + 3 * (b * n_kv_head + h);
+                    const int nb = cum_v[b + 1] - cum_v[b];
+                    o[0] = o[1] = o[2] = 0;
+                    if (nb > 0) {
+                        int wf, n, sf;
+                        bal_pair_pieces((int64_t)n_kv_head * cum_v[b] + (int64_t)h * nb, nb, T, wa, wf, n, sf);
+                        o[0] = wf; o[1] = n; o[2] = sf;
+                    }
+                }
+    }
+    delete[] cum_v;
+    return n_segs;
+}
 
 size_t nimllm_attn_decode_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim,
                                           int max_len, int chunk_rows) {

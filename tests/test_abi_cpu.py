@@ -91,3 +91,53 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         assert False, "expected NimllmAttnError"
     except _lib.NimllmAttnError as e:
         assert "no fallback" in str(e)
+
+
+def test_balanced_decode_plan_covers_every_unit_once():
+    """The balanced decode kernel cuts the flattened batch into equal spans per warp.  Replayed on
+    the host (same code as the kernels): every unit of every (sequence, KV head) pair is covered
+    exactly once, whole pairs are never also cut, a warp cuts at most two pairs, and the merge
+    side finds exactly the records the walk wrote."""
+    import ctypes as C
+    import numpy as np
+    from nimllm_b200 import _lib
+    L = _lib.lib()
+    rng = np.random.default_rng(11)
+    for trial in range(300):
+        B = int(rng.integers(1, 40)); Hkv = int(rng.integers(1, 9)); unit = int(rng.choice([16, 32]))
+        lens = rng.choice([0, 0, 1, 5, 16, 33, 100, 700, 4096, int(rng.integers(0, 3000))], size=B).astype(np.int32)
+        warps = int(rng.choice([8, 37, 1184]))
+        segs = np.zeros((20000, 6), np.int32); pairs = np.zeros((B * Hkv, 3), np.int32)
+        n = L.nimllm_attn_debug_balanced_plan(lens.ctypes.data_as(C.c_void_p), B, Hkv, unit, warps,
+                                              segs.ctypes.data_as(C.c_void_p), len(segs), pairs.ctypes.data_as(C.c_void_p))
+        assert n >= 0
+        segs = segs[:n]
+        units = (lens + unit - 1) // unit
+        cover = {}
+        records = {}
+        for w, b, h, i0, i1, slot in segs.tolist():
+            assert 0 <= i0 < i1 <= units[b]
+            cover.setdefault((b, h), []).append((i0, i1, w, slot))
+            if slot >= 0:
+                assert (w, slot) not in records and slot in (0, 1)
+                records[(w, slot)] = (b, h, i0, i1)
+        for b in range(B):
+            for h in range(Hkv):
+                pieces = sorted(cover.get((b, h), []))
+                if units[b] == 0:
+                    assert not pieces
+                    continue
+                assert pieces[0][0] == 0 and pieces[-1][1] == units[b]
+                assert all(pieces[i][1] == pieces[i + 1][0] for i in range(len(pieces) - 1))
+                wf, cnt, sf = pairs[b * Hkv + h].tolist()
+                assert cnt == len(pieces)
+                if cnt == 1:
+                    assert pieces[0][3] == -1               # a whole pair is written directly
+                else:
+                    for i, (i0, i1, w, slot) in enumerate(pieces):
+                        assert w == wf + i and slot == (sf if i == 0 else 0)
+                        assert records[(w, slot)] == (b, h, i0, i1)
+        total = int(units.sum()) * Hkv
+        if total:
+            per_warp = np.bincount(segs[:, 0], weights=(segs[:, 4] - segs[:, 3]))
+            assert per_warp.max() - per_warp[per_warp > 0].min() <= 1     # equal spans
