@@ -1,4 +1,4 @@
-// prefill_tc.cu -- causal GQA prefill attention on the Blackwell tensor cores (bf16, D = 128).
+// prefill_tc.cu -- causal GQA prefill attention on the Blackwell tensor cores (bf16, D = 128 or 64).
 //
 // Replaces, for bf16 activations, the per-query-head loop of forward() in the reference
 // (src/model.nim:498-508: gather, cublasSgemm_v2 QK^T, gpu_causal_mask, gpu_softmax_fwd,
@@ -43,24 +43,26 @@
 
 namespace nimllm {
 
+float *g_prefill_dbg = nullptr;  // testing hook: device buffer of 33152 floats, or null
+
 namespace {
 
 using namespace tc;
 
-constexpr int kD = 128;            // head_dim
 constexpr int kBM = 128;           // query rows per tile (= TMEM lanes)
 constexpr int kBN = 128;           // KV rows per tile
 constexpr int kSlots = 5;           // K/V ring: K_0 V_0 K_1 V_1 ... walk the slots in order
-constexpr int kTileBytes = kBN * kD * 2;     // 32 KiB: one [128 x 128] bf16 tile = two swizzled 64-column boxes
-static_assert(kTileBytes == 2 * kBoxBytes, "a tile is two swizzled 64-column boxes");
+// head_dim kD is a template parameter (128 or 64): a [128 x kD] bf16 tile is kD/64 swizzled 64-column
+// boxes of 16 KiB
+template <int kD> constexpr int tile_bytes() { return kBN * kD * 2; }
 constexpr int kThreads = 384;                // 8 softmax warps + one warpgroup holding producer, MMA issuer, 2 idle
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units: O is rescaled when a row maximum grows by more
 
-struct Smem {
+template <int kD> struct Smem {
     // tiles first: 1024-byte alignment is required by the 128-byte swizzle atoms
-    uint8_t q[2][kTileBytes];
-    uint8_t kv[kSlots][kTileBytes];
+    uint8_t q[2][tile_bytes<kD>()];
+    uint8_t kv[kSlots][tile_bytes<kD>()];
     uint64_t q_full, kv_full[kSlots], kv_empty[kSlots];
     uint64_t s_full[2], p_ready[2], o_full[2], drain;
     uint32_t tmem_base;
@@ -81,11 +83,15 @@ struct PrefillParams {
 };
 
 // ------------------------------------------------------------------ kernel
+template <int kD>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                   const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
-    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    static_assert(kD == 64 || kD == 128, "head_dim 64 or 128");
+    constexpr int kTileBytes = tile_bytes<kD>();
+    constexpr int kBoxes = kD / 64;
+    Smem<kD> &sm = *reinterpret_cast<Smem<kD> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.Hq / p.Hkv;
@@ -136,11 +142,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const int y0 = b * p.S + row_base;
             if (!p.rotate_q) {
                 mbar_expect_tx(&sm.q_full, active1 ? 2 * kTileBytes : kTileBytes);
-                tma_load_2d(sm.q[0], &q_map, qx, y0, &sm.q_full);
-                tma_load_2d(sm.q[0] + kBoxBytes, &q_map, qx + 64, y0, &sm.q_full);
-                if (active1) {
-                    tma_load_2d(sm.q[1], &q_map, qx, y0 + kBM, &sm.q_full);
-                    tma_load_2d(sm.q[1] + kBoxBytes, &q_map, qx + 64, y0 + kBM, &sm.q_full);
+                for (int bx = 0; bx < kBoxes; bx++) {
+                    tma_load_2d(sm.q[0] + bx * kBoxBytes, &q_map, qx + bx * 64, y0, &sm.q_full);
+                    if (active1) tma_load_2d(sm.q[1] + bx * kBoxBytes, &q_map, qx + bx * 64, y0 + kBM, &sm.q_full);
                 }
             }
             // ring position u = 2j for K_j, 2j + 1 for V_j; slot u % kSlots, phase (u / kSlots) & 1
@@ -150,8 +154,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 const CUtensorMap *map = (u & 1) ? &v_map : &k_map;
                 if (!mbar_wait(&sm.kv_empty[slot], ph ^ 1, abort_flag)) break;
                 mbar_expect_tx(&sm.kv_full[slot], kTileBytes);
-                tma_load_2d(sm.kv[slot], map, kx, y, &sm.kv_full[slot]);
-                tma_load_2d(sm.kv[slot] + kBoxBytes, map, kx + 64, y, &sm.kv_full[slot]);
+                for (int bx = 0; bx < kBoxes; bx++)
+                    tma_load_2d(sm.kv[slot] + bx * kBoxBytes, map, kx + bx * 64, y, &sm.kv_full[slot]);
             }
         }
     } else if (warp == 9) {
@@ -236,20 +240,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         bool ok = true;
 
         if (p.rotate_q) {
-            // Stage both Q tiles through registers, all 256 softmax threads together: 8 lanes
+            // Stage both Q tiles through registers, all 256 softmax threads together: kD/16 lanes
             // per row, lane c of a row owns columns [8c, 8c+8) and their rotation partners
-            // [64+8c, 64+8c+8), so global reads (q and the cos/sin rows) are fully coalesced and
+            // [kD/2+8c, kD/2+8c+8), so global reads (q and the cos/sin rows) are fully coalesced and
             // the bf16 results drop into the swizzled tile without bank conflicts.  Rotated
             // values also go back to global when the caller keeps Q (saveCache).
-            const int c8 = (lane & 7) * 8;
+            constexpr int kLpr = kD / 16;                      // lanes per row
+            constexpr int kRpw = 32 / kLpr;                    // rows per warp and step; 8 warps cover 8 * kRpw rows
+            const int c8 = (lane % kLpr) * 8;
 #pragma unroll 1
-            for (int half_i = 0; half_i < 2; half_i++) {       // tile 0, then tile 1
+            for (int half_i = 0; half_i < kLpr / 4; half_i++) {      // batches of four steps
                 // all 24 loads of four steps are issued before any of them is used
                 uint4 lo[4], hi[4];
                 float4 cs0[4], cs1[4], sn0[4], sn1[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    const int row = (half_i * 4 + u) * 32 + warp * 4 + (lane >> 3);     // 0..255 over both tiles
+                    const int row = (half_i * 4 + u) * (8 * kRpw) + warp * kRpw + lane / kLpr;     // 0..255 over both tiles
                     const int pos = row_base + row;
                     lo[u] = hi[u] = make_uint4(0, 0, 0, 0);
                     cs0[u] = cs1[u] = sn0[u] = sn1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -267,7 +273,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 }
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    const int row = (half_i * 4 + u) * 32 + warp * 4 + (lane >> 3);
+                    const int row = (half_i * 4 + u) * (8 * kRpw) + warp * kRpw + lane / kLpr;
                     const int tile_i = row >> 7, rr = row & 127;
                     const int pos = row_base + row;
                     const float cs[8] = {cs0[u].x, cs0[u].y, cs0[u].z, cs0[u].w, cs1[u].x, cs1[u].y, cs1[u].z, cs1[u].w};
@@ -351,7 +357,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 // rare: bring O down to the new reference maximum.  S_j is complete, so every
                 // earlier MMA (the last PV of this tile included) has finished with O.
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ch++) {
+                for (int ch = 0; ch < kD / 32; ch++) {
                     uint32_t o[32];
                     tmem_ld32(o_addr + ch * 32, o);
                     tc_wait_ld();
@@ -396,7 +402,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16 *og = p.out + ((int64_t)b * p.S + qrow) * p.Hq * kD + (int64_t)h * kD;
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ch++) {
+            for (int ch = 0; ch < kD / 32; ch++) {
                 uint32_t v[32];
                 tmem_ld32(o_addr + ch * 32, v);
                 tc_wait_ld();
@@ -471,37 +477,32 @@ int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols) {
 // status word (4 bytes) + optional debug area
 size_t prefill_tc_workspace_bytes(int, int, int, int, int) { return 256; }
 
-float *g_prefill_dbg = nullptr;  // testing hook: device buffer of 33152 floats, or null
+namespace {
 
-int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *lse, const float *cos_tab,
-                      const float *sin_tab, int pos0, int write_back_q, int B, int S, int Hq, int Hkv, int D,
-                      float scale, void *workspace, size_t workspace_bytes, cudaStream_t st) {
-    if (D != kD) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: head_dim %d (the tensor-core kernel is built for 128)", D);
-    if (!workspace || workspace_bytes < 256) return fail(NIMLLM_ERR_WORKSPACE, "attn_prefill bf16: workspace %zu bytes, need 256", workspace_bytes);
-    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
-        return fail(NIMLLM_ERR_ARG, "attn_prefill bf16: q, k, v, out must be 16-byte aligned");
-    if ((int64_t)B * S > 0x7fffffff) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: B*S too large");
-
+template <int kD>
+int launch_prefill_tc_d(void *q, const void *k, const void *v, void *out, float *lse, const float *cos_tab,
+                        const float *sin_tab, int pos0, int write_back_q, int B, int S, int Hq, int Hkv,
+                        float scale, void *workspace, cudaStream_t st) {
     static bool attr_set[64] = {false};
-    const size_t smem_bytes = sizeof(Smem) + 1024;
+    const size_t smem_bytes = sizeof(Smem<kD>) + 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<kD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: shared memory opt-in: %s", cudaGetErrorString(e));
         attr_set[dev] = true;
     }
 
     CUtensorMap q_map, k_map, v_map;
     int rc;
-    if ((rc = make_map(&q_map, q, (uint64_t)B * S, (uint64_t)Hq * D))) return rc;
-    if ((rc = make_map(&k_map, k, (uint64_t)B * S, (uint64_t)Hkv * D))) return rc;
-    if ((rc = make_map(&v_map, v, (uint64_t)B * S, (uint64_t)Hkv * D))) return rc;
+    if ((rc = make_map(&q_map, q, (uint64_t)B * S, (uint64_t)Hq * kD))) return rc;
+    if ((rc = make_map(&k_map, k, (uint64_t)B * S, (uint64_t)Hkv * kD))) return rc;
+    if ((rc = make_map(&v_map, v, (uint64_t)B * S, (uint64_t)Hkv * kD))) return rc;
 
     PrefillParams p;
     p.q = (__nv_bfloat16 *)q; p.out = (__nv_bfloat16 *)out; p.lse = lse;
     p.cos_tab = cos_tab; p.sin_tab = sin_tab;
-    p.status = (int *)workspace; p.dbg = g_prefill_dbg;
+    p.status = (int *)workspace; p.dbg = kD == 128 ? g_prefill_dbg : nullptr;
     p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.pos0 = pos0;
     p.rotate_q = cos_tab ? 1 : 0;
     p.write_back_q = write_back_q;
@@ -511,9 +512,25 @@ int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *l
     if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: %s", cudaGetErrorString(e));
     const int n_pairs = (S + 2 * kBM - 1) / (2 * kBM);
     dim3 grid((unsigned)n_pairs * Hq * B);
-    prefill_tc_kernel<<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
+    prefill_tc_kernel<kD><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
     NIMLLM_CHECK_LAUNCH("attn_prefill bf16");
     return NIMLLM_OK;
+}
+
+}  // namespace
+
+int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *lse, const float *cos_tab,
+                      const float *sin_tab, int pos0, int write_back_q, int B, int S, int Hq, int Hkv, int D,
+                      float scale, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (D != 64 && D != 128)
+        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: head_dim %d (the tensor-core kernel is built for 64 and 128)", D);
+    if (!workspace || workspace_bytes < 256) return fail(NIMLLM_ERR_WORKSPACE, "attn_prefill bf16: workspace %zu bytes, need 256", workspace_bytes);
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
+        return fail(NIMLLM_ERR_ARG, "attn_prefill bf16: q, k, v, out must be 16-byte aligned");
+    if ((int64_t)B * S > 0x7fffffff) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: B*S too large");
+    if (D == 64)
+        return launch_prefill_tc_d<64>(q, k, v, out, lse, cos_tab, sin_tab, pos0, write_back_q, B, S, Hq, Hkv, scale, workspace, st);
+    return launch_prefill_tc_d<128>(q, k, v, out, lse, cos_tab, sin_tab, pos0, write_back_q, B, S, Hq, Hkv, scale, workspace, st);
 }
 
 }  // namespace nimllm

@@ -125,6 +125,34 @@ def test_c4_shape_sampled_rows_and_determinism():
 
 
 def test_unsupported_head_dim_is_an_error_not_a_fallback():
-    q = torch.zeros(1, 128, 64, dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros(1, 128, 32, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(Exception, match="head_dim"):
-        A.attn_forward(q, q.clone(), q.clone(), None, None, n_head=1, n_kv_head=1, head_dim=64)
+        A.attn_forward(q, q.clone(), q.clone(), None, None, n_head=1, n_kv_head=1, head_dim=32)
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 3, 1), (2, 384, 9, 3), (1, 300, 6, 3), (1, 1000, 9, 3), (1, 1, 3, 3)])
+@pytest.mark.parametrize("rope,save_cache", [(False, False), (True, True)])
+def test_prefill_bf16_head_dim_64(B, S, Hq, Hkv, rope, save_cache, request):
+    """The reference's own model shape (9 q / 3 kv heads of 64, RoPE base 10000) in bf16."""
+    if "cta-pair" in request.node.name:
+        pytest.skip("the CTA-pair kernel is built for head_dim 128")
+    d, base = 64, 10000.0
+    g = torch.Generator(device="cuda").manual_seed(900 + S)
+    q = torch.randn(B, S, Hq * d, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv * d, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv * d, generator=g, device="cuda").bfloat16()
+    q0, k0 = host(q).copy(), host(k).copy()
+    cos, sin = A.rope_tables(S, d, base) if rope else (None, None)
+    out = A.attn_forward(q, k, v, cos, sin, n_head=Hq, n_kv_head=Hkv, head_dim=d, save_cache=save_cache)
+    torch.cuda.synchronize()
+    assert _status_ok()
+    if rope:
+        ct, st = O.rope_tables(S, d, base)
+        for b in range(B):
+            O.rope_fwd(q0[b], ct, st, Hq, d)
+            O.rope_fwd(k0[b], ct, st, Hkv, d)
+        q0, k0 = O.from_bf16(O.to_bf16(q0)), O.from_bf16(O.to_bf16(k0))
+        np.testing.assert_array_equal(host(k), k0)
+        np.testing.assert_array_equal(host(q), q0)           # save_cache leaves the rotated Q
+    ref = O.prefill_f64(q0, k0, host(v), Hq, Hkv, d, 1 / np.sqrt(d))
+    assert_close(host(out), ref, TOL_BF16, "prefill bf16, head_dim 64")
