@@ -233,8 +233,12 @@ def run_decode(args, dist, name):
         gathered = torch.empty(dist.world, B * Hq, W, dtype=torch.float32, device="cuda")
         if args.exchange == "p2p":
             from nimllm_b200 import sharding
-            xch = sharding.PeerExchange(B * Hq, D)
-            merged = torch.empty(B * Hq, D, dtype=torch.float32, device="cuda")
+            try:
+                xch = sharding.PeerExchange(B * Hq, D)
+                merged = torch.empty(B * Hq, D, dtype=torch.float32, device="cuda")
+            except Exception as e:      # e.g. no peer access between these GPUs: every rank fails alike
+                log(f"peer exchange unavailable ({e}); using the NCCL all-gather")
+                xch = None
 
     turn = [0]
 

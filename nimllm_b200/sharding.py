@@ -81,10 +81,20 @@ class PeerExchange:
         check(self._lib.nimllm_peer_exchange_export(self.handle, mine))
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(mine.raw), group=group)
-        for r, h in enumerate(handles):
-            check(self._lib.nimllm_peer_exchange_import(self.handle, r, C.create_string_buffer(h, 64)))
-        check(self._lib.nimllm_peer_exchange_ready(self.handle))
-        dist.barrier(group)                      # every rank has mapped every buffer before first use
+        err = None
+        try:
+            for r, h in enumerate(handles):
+                check(self._lib.nimllm_peer_exchange_import(self.handle, r, C.create_string_buffer(h, 64)))
+            check(self._lib.nimllm_peer_exchange_ready(self.handle))
+        except Exception as e:                   # e.g. no peer access between two of the GPUs
+            err = str(e)
+        # every rank learns whether every rank mapped every buffer (this also orders the mapping
+        # before first use); on a failure all ranks raise together instead of one leaving the others waiting
+        errs = [None] * self.world
+        dist.all_gather_object(errs, err, group=group)
+        if any(errs):
+            self.close()
+            raise RuntimeError("peer exchange setup failed: " + "; ".join(f"rank {r}: {e}" for r, e in enumerate(errs) if e))
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def combine(self, rec, out=None):
