@@ -286,9 +286,11 @@ def run_decode(args, dist, name):
 
     # ---- end to end through the host-facing call: H2D activations, RoPE + append + decode, D2H
     E, Ekv = Hq * D, Hkv * D
-    hq = torch.randn(B, E).pin_memory(); hk = torch.randn(B, Ekv).pin_memory(); hv = torch.randn(B, Ekv).pin_memory()
+    # the step's activations q | k | v sit back to back in one pinned buffer: one host-to-device copy
+    hin = torch.randn(B * (E + 2 * Ekv)).pin_memory()
     hout = torch.empty(B, E).pin_memory()
-    dq = torch.empty(B, E, device="cuda"); dk = torch.empty(B, Ekv, device="cuda"); dv = torch.empty(B, Ekv, device="cuda")
+    din = torch.empty(B * (E + 2 * Ekv), device="cuda")
+    dq, dk, dv = din[:B * E].view(B, E), din[B * E:B * (E + Ekv)].view(B, Ekv), din[B * (E + Ekv):].view(B, Ekv)
     # the new token overwrites the last attended row, so the batch keeps its lengths from step to
     # step; in c5 that is global row 131071, which only the last KV-sequence shard stores
     if name == "c5":
@@ -303,7 +305,7 @@ def run_decode(args, dist, name):
     def e2e_step():
         i = turn[0] = (turn[0] + 1) % len(w["kcs"])
         kci, vci = w["kcs"][i], w["vcs"][i]
-        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
+        din.copy_(hin, non_blocking=True)
         A.rope_append(dq.view(B, 1, E), dk.view(B, 1, Ekv), dv.view(B, 1, Ekv), cos, sin, n_head=Hq, n_kv_head=Hkv,
                       head_dim=D, seq_pos=seq_pos, k_cache=kci, v_cache=vci, seq_stride=Hkv * cap * D,
                       head_stride=cap * D, cache_row0=row0, max_seq=cap)
