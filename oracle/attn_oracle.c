@@ -243,6 +243,122 @@ ORACLE_API void oracle_attn_forward(float *q, float *k, const float *v, const fl
     }
 }
 
+/* ------------------------------------------------------- attention backward
+ * src/model.nim:639-685: per QUERY head h the probabilities are recomputed (scores = qH kH^T,
+ * causal mask + scale, softmax), then dWeights = doutH vH^T, dvH = probs^T doutH,
+ * dScores = softmax_bwd(probs, dWeights) (src/kernels.cu:305-328: y * (dy - sum_j dy_j y_j)),
+ * dScores *= scale, dqH = dScores kH, dkH = dScores^T qH; dqH goes to columns h*D.. of dq, dkH and
+ * dvH are ADDED to the columns of KV head h / kvRepeat (src/kernels.cu:451-461), and finally the
+ * rotation is undone on dq and dk (gpu_rope_bwd, src/kernels.cu:425-431: k_rope with sign -1).
+ * q_rot, k_rot are the post-RoPE activations the forward saved (saveCache), v raw.
+ * dq [S, Hq*D], dk, dv [S, Hkv*D] are overwritten.  acc64 != 0 accumulates every product in
+ * float64 (ground truth for tolerance statements). */
+static void rope_bwd_rows(float *data, const float *cos_tab, const float *sin_tab, int seq_len,
+                          int n_embd, int n_head, int head_dim) {
+    int half = head_dim / 2;
+    for (int pos = 0; pos < seq_len; pos++)
+        for (int h = 0; h < n_head; h++)
+            for (int f = 0; f < half; f++) {
+                int64_t base = (int64_t)pos * n_embd + (int64_t)h * head_dim;
+                float c = cos_tab[(int64_t)pos * half + f];
+                float s = -sin_tab[(int64_t)pos * half + f];      /* sign = -1 */
+                float x0 = data[base + f];
+                float x1 = data[base + f + half];
+                data[base + f] = x0 * c - x1 * s;
+                data[base + f + half] = x0 * s + x1 * c;
+            }
+}
+
+ORACLE_API void oracle_rope_bwd(float *data, const float *cos_tab, const float *sin_tab,
+                                int seq_len, int n_embd, int n_head, int head_dim) {
+    rope_bwd_rows(data, cos_tab, sin_tab, seq_len, n_embd, n_head, head_dim);
+}
+
+ORACLE_API void oracle_attn_backward(const float *q_rot, const float *k_rot, const float *v,
+                                     const float *dout, const float *cos_tab, const float *sin_tab,
+                                     float *dq, float *dk, float *dv, int S, int Hq, int Hkv, int D,
+                                     int apply_rope, int acc64) {
+    int E = Hq * D, Ekv = Hkv * D, G = Hq / Hkv;
+    float scale = 1.0f / sqrtf((float)D);
+    memset(dq, 0, sizeof(float) * (size_t)S * E);
+    memset(dk, 0, sizeof(float) * (size_t)S * Ekv);
+    memset(dv, 0, sizeof(float) * (size_t)S * Ekv);
+    /* the query heads of one KV head are walked in order by one thread, like the reference's loop */
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int kvh = 0; kvh < Hkv; kvh++) {
+        float *probs = (float *)malloc(sizeof(float) * (size_t)S * S);
+        float *scores = (float *)malloc(sizeof(float) * (size_t)S * S);
+        double *dS = (double *)malloc(sizeof(double) * (size_t)S * S);
+        for (int h = kvh * G; h < (kvh + 1) * G; h++) {
+            const float *qh = q_rot + (int64_t)h * D, *kh = k_rot + (int64_t)kvh * D, *vh = v + (int64_t)kvh * D;
+            const float *doh = dout + (int64_t)h * D;
+            for (int i = 0; i < S; i++)
+                for (int j = 0; j < S; j++) {
+                    if (acc64) {
+                        double a = 0.0;
+                        for (int d = 0; d < D; d++) a += (double)qh[(int64_t)i * E + d] * kh[(int64_t)j * Ekv + d];
+                        scores[(int64_t)i * S + j] = (float)a;
+                    } else {
+                        float a = 0.0f;
+                        for (int d = 0; d < D; d++) a += qh[(int64_t)i * E + d] * kh[(int64_t)j * Ekv + d];
+                        scores[(int64_t)i * S + j] = a;
+                    }
+                }
+            oracle_causal_mask(scores, scale, S);
+            oracle_softmax_fwd(scores, probs, S, S);
+            for (int i = 0; i < S; i++) {
+                /* dWeights row, then softmax_bwd of the row, then * scale */
+                double dot = 0.0;
+                float dotf = 0.0f;
+                for (int j = 0; j < S; j++) {
+                    double a = 0.0;
+                    float af = 0.0f;
+                    for (int d = 0; d < D; d++) {
+                        a += (double)doh[(int64_t)i * E + d] * vh[(int64_t)j * Ekv + d];
+                        af += doh[(int64_t)i * E + d] * vh[(int64_t)j * Ekv + d];
+                    }
+                    dS[(int64_t)i * S + j] = acc64 ? a : (double)af;
+                    dot += dS[(int64_t)i * S + j] * probs[(int64_t)i * S + j];
+                    dotf += (float)dS[(int64_t)i * S + j] * probs[(int64_t)i * S + j];
+                }
+                for (int j = 0; j < S; j++) {
+                    float pij = probs[(int64_t)i * S + j];
+                    if (acc64) dS[(int64_t)i * S + j] = (double)pij * (dS[(int64_t)i * S + j] - dot) * scale;
+                    else dS[(int64_t)i * S + j] = (double)((pij * ((float)dS[(int64_t)i * S + j] - dotf)) * scale);
+                }
+            }
+            for (int j = 0; j < S; j++)
+                for (int d = 0; d < D; d++) {
+                    double av = 0.0, ak = 0.0;
+                    float avf = 0.0f, akf = 0.0f;
+                    for (int i = j; i < S; i++) {          /* rows above the diagonal have p = dS = 0 */
+                        av += (double)probs[(int64_t)i * S + j] * doh[(int64_t)i * E + d];
+                        ak += dS[(int64_t)i * S + j] * qh[(int64_t)i * E + d];
+                        avf += probs[(int64_t)i * S + j] * doh[(int64_t)i * E + d];
+                        akf += (float)dS[(int64_t)i * S + j] * qh[(int64_t)i * E + d];
+                    }
+                    dv[(int64_t)j * Ekv + (int64_t)kvh * D + d] += acc64 ? (float)av : avf;
+                    dk[(int64_t)j * Ekv + (int64_t)kvh * D + d] += acc64 ? (float)ak : akf;
+                }
+            for (int i = 0; i < S; i++)
+                for (int d = 0; d < D; d++) {
+                    double a = 0.0;
+                    float af = 0.0f;
+                    for (int j = 0; j <= i; j++) {
+                        a += dS[(int64_t)i * S + j] * kh[(int64_t)j * Ekv + d];
+                        af += (float)dS[(int64_t)i * S + j] * kh[(int64_t)j * Ekv + d];
+                    }
+                    dq[(int64_t)i * E + (int64_t)h * D + d] = acc64 ? (float)a : af;
+                }
+        }
+        free(probs); free(scores); free(dS);
+    }
+    if (apply_rope) {
+        rope_bwd_rows(dq, cos_tab, sin_tab, S, E, Hq, D);
+        rope_bwd_rows(dk, cos_tab, sin_tab, S, Ekv, Hkv, D);
+    }
+}
+
 /* ------------------------------------------------------------- KV append
  * src/model.nim:799-815: row pos (rows pos..pos+n-1) of KV head kvh's buffer
  * [max_seq, D] <- columns kvh*D.. of kNew / vNew [n, Hkv*D].  K arrives

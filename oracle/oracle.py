@@ -48,6 +48,8 @@ def lib() -> C.CDLL:
         L.oracle_insert_head.argtypes = [f32p, f32p] + [C.c_int] * 4
         L.oracle_attn_forward.argtypes = [f32p, f32p, f32p, f32p, f32p, f32p] + [C.c_int] * 5
         L.oracle_kv_append.argtypes = [f32p, f32p, f32p, f32p] + [C.c_int] * 5
+        L.oracle_attn_backward.argtypes = [f32p] * 9 + [C.c_int] * 6
+        L.oracle_rope_bwd.argtypes = [f32p, f32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int]
         L.oracle_attn_forward_cached.argtypes = [f32p] * 7 + [C.c_int, f32p] + [C.c_int] * 4
         L.oracle_decode_batch.argtypes = [f32p, C.c_void_p, C.c_void_p, i64p, i64p, i32p, f32p,
                                           C.c_int, C.c_int, C.c_int, C.c_int, C.c_float,
@@ -92,6 +94,18 @@ def attn_forward(q, k, v, cos, sin, Hq, Hkv, D, apply_rope=True):
     out = np.zeros((S, Hq * D), np.float32)
     lib().oracle_attn_forward(q, k, v, np.ascontiguousarray(cos), np.ascontiguousarray(sin), out, S, Hq, Hkv, D, int(apply_rope))
     return out, q, k
+
+
+def attn_backward(q_rot, k_rot, v, dout, cos, sin, Hq, Hkv, D, apply_rope=True, acc64=False):
+    """Reference backward() attention block (src/model.nim:639-685) for one sequence: returns
+    (dq, dk, dv) given the post-RoPE q, k the forward saved, raw v and the gradient of attnOut."""
+    q_rot = np.ascontiguousarray(q_rot, np.float32); k_rot = np.ascontiguousarray(k_rot, np.float32)
+    v = np.ascontiguousarray(v, np.float32); dout = np.ascontiguousarray(dout, np.float32)
+    S = q_rot.shape[0]
+    dq = np.zeros((S, Hq * D), np.float32); dk = np.zeros((S, Hkv * D), np.float32); dv = np.zeros((S, Hkv * D), np.float32)
+    lib().oracle_attn_backward(q_rot, k_rot, v, dout, np.ascontiguousarray(cos), np.ascontiguousarray(sin), dq, dk, dv,
+                               S, Hq, Hkv, D, int(apply_rope), int(acc64))
+    return dq, dk, dv
 
 
 class KvCache:

@@ -171,3 +171,46 @@ def test_legacy_pieces_restate_reference_kernels():
     O.lib().oracle_causal_mask(sc, 0.125, 5)
     assert (sc[np.triu_indices(5, 1)] == np.float32(-1e9)).all()
     np.testing.assert_array_equal(sc[np.tril_indices(5)], (ref * np.float32(0.125))[np.tril_indices(5)])
+
+
+def test_attention_backward_matches_autograd_of_an_independent_formulation():
+    """The restated backward (src/model.nim:639-685) against float64 autograd through a plain
+    softmax(QK^T)V with rotate-half RoPE written independently in torch."""
+    import torch
+    from oracle import oracle as O
+    S, Hq, Hkv, D = 37, 6, 2, 32
+    G = Hq // Hkv
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal((S, Hq * D)).astype(np.float32)
+    k = rng.standard_normal((S, Hkv * D)).astype(np.float32)
+    v = rng.standard_normal((S, Hkv * D)).astype(np.float32)
+    dout = rng.standard_normal((S, Hq * D)).astype(np.float32)
+    cos, sin = O.rope_tables(S, D, 10000.0)
+
+    def rope(x, n_head):
+        x = x.view(S, n_head, D)
+        c = torch.from_numpy(cos).double()[:, None, :]; s_ = torch.from_numpy(sin).double()[:, None, :]
+        x0, x1 = x[..., :D // 2], x[..., D // 2:]
+        return torch.cat([x0 * c - x1 * s_, x0 * s_ + x1 * c], dim=-1)
+
+    tq = torch.from_numpy(q).double().requires_grad_(); tk = torch.from_numpy(k).double().requires_grad_()
+    tv = torch.from_numpy(v).double().requires_grad_()
+    qr, kr = rope(tq, Hq), rope(tk, Hkv)
+    vv = tv.view(S, Hkv, D)
+    outs = []
+    mask = torch.tril(torch.ones(S, S, dtype=torch.bool))
+    for h in range(Hq):
+        sc = (qr[:, h] @ kr[:, h // G].T) / np.sqrt(D)
+        p = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=-1)
+        outs.append(p @ vv[:, h // G])
+    out = torch.stack(outs, dim=1).reshape(S, Hq * D)
+    out.backward(torch.from_numpy(dout).double())
+
+    q_rot, k_rot = q.copy(), k.copy()
+    O.rope_fwd(q_rot, cos, sin, Hq, D); O.rope_fwd(k_rot, cos, sin, Hkv, D)
+    for acc64, tol in ((True, 2e-6), (False, 2e-5)):
+        dq, dk, dv = O.attn_backward(q_rot, k_rot, v, dout, cos, sin, Hq, Hkv, D, acc64=acc64)
+        for name, got, want in (("dq", dq, tq.grad), ("dk", dk, tk.grad), ("dv", dv, tv.grad)):
+            want = want.numpy()
+            err = np.abs(got - want).max() / np.abs(want).max()
+            assert err <= tol, f"{name} acc64={acc64}: {err:.3e}"
