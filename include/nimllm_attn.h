@@ -198,6 +198,28 @@ int nimllm_attn_prefill(void *q, void *k, const void *v, int dtype, const float 
                         int64_t seq_stride, int64_t head_stride, int max_seq, float *lse,
                         void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- backward of the causal prefill (training with saveCache) -------------------------
+ * Replaces the attention block of backward(), src/model.nim:639-685 (per query head: recompute
+ * scores and probabilities, dWeights, softmax_bwd src/kernels.cu:305-328, dq / dk / dv products,
+ * accumulation of dk and dv over the query heads of a KV head with atomics
+ * src/kernels.cu:451-461) followed by ropeBwd on dq and dk (src/kernels.cu:425-431).  fp32.
+ *   q_rot, k_rot  the post-RoPE activations the forward left behind (save_cache = 1)
+ *   v, out        V as given to the forward, and the forward's output
+ *   dout          gradient of out, [B, S, Hq*D]
+ *   lse           [B, Hq, S] as written by nimllm_attn_prefill (required)
+ *   rope_cos/sin  the forward's tables: dq and dk come back in the pre-RoPE space, as ropeBwd
+ *                 leaves them (NULL: no rotation is undone)
+ *   dq [B, S, Hq*D], dk, dv [B, S, Hkv*D] are overwritten (the reference accumulates into
+ *                 zero-initialised buffers); sums run in a fixed order, results repeat bit for bit
+ *   workspace     nimllm_attn_prefill_bwd_workspace_bytes(batch, seq_len, n_head) bytes
+ */
+size_t nimllm_attn_prefill_bwd_workspace_bytes(int batch, int seq_len, int n_head);
+int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float *v, const float *out,
+                            const float *dout, const float *lse, const float *rope_cos,
+                            const float *rope_sin, int pos0, float *dq, float *dk, float *dv,
+                            int batch, int seq_len, int n_head, int n_kv_head, int head_dim,
+                            float scale, void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- the reference's own attention-path launchers, same names and arguments -------
  * Kept so that callers that still use the unfused sequence (backward(), the test
  * programs) link against this library alone.  All launch on the legacy default

@@ -156,6 +156,23 @@ def attn_forward(q, k, v, cos, sin, *, n_head, n_kv_head, head_dim, pos0=0, save
     return out[0] if squeeze else out
 
 
+def attn_backward(q_rot, k_rot, v, out, dout, lse, cos, sin, *, n_head, n_kv_head, head_dim, pos0=0, scale=None):
+    """Backward of the causal attention block (fp32): returns (dq, dk, dv) in the pre-RoPE space.
+    q_rot / k_rot are the rotated activations attn_forward(save_cache=True) left, lse its row
+    log-sum-exp [B, Hq, S]."""
+    if q_rot.dim() == 2:
+        q_rot, k_rot, v, out, dout = (t.unsqueeze(0) for t in (q_rot, k_rot, v, out, dout))
+    B, S = q_rot.shape[0], q_rot.shape[1]
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    dq, dk, dv = torch.empty_like(q_rot), torch.empty_like(k_rot), torch.empty_like(v)
+    need = lib().nimllm_attn_prefill_bwd_workspace_bytes(B, S, n_head)
+    ws = _arena.get(need, q_rot.device)
+    check(lib().nimllm_attn_prefill_bwd(
+        _ptr(q_rot), _ptr(k_rot), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(cos), _ptr(sin), pos0,
+        _ptr(dq), _ptr(dk), _ptr(dv), B, S, n_head, n_kv_head, head_dim, scale, _ptr(ws), need, _stream()))
+    return dq, dk, dv
+
+
 def attn_forward_cached(kv: KvCache, layer, q, k_new, v_new, cos, sin, *, n_head, scale=None, chunk_rows=0):
     """forwardCached()'s attention block for one new token per sequence (newTokens == 1):
     RoPE(q, k_new) at row kv.pos, append, attend rows 0..kv.pos.  q [n_seq, Hq*D],

@@ -1,0 +1,282 @@
+// prefill_bwd.cu -- backward of the causal GQA attention block (fp32), flash-style.
+//
+// Replaces the per-query-head loop of backward() in the reference (src/model.nim:639-685): per
+// head it re-materialises scores and probabilities [S, S], forms dWeights, runs softmax_bwd
+// (src/kernels.cu:305-328), two more S x S products and accumulates dk / dv of the shared KV
+// head with atomics (src/kernels.cu:451-461) -- four S x S fp32 matrices through HBM per head.
+// Here nothing of size S x S leaves the SM: probabilities are recomputed tile by tile from the
+// saved post-RoPE q, k and the forward's log-sum-exp,
+//     p_ij  = exp(scale * q_i.k_j - lse_i)            (j <= i)
+//     dS_ij = p_ij * (dO_i.v_j - dO_i.o_i)
+//     dv_j += sum_i p_ij dO_i     dk_j += scale * sum_i dS_ij q_i     dq_i = scale * sum_j dS_ij k_j
+// and the rotation is undone on dq and dk in the epilogue (gpu_rope_bwd, src/kernels.cu:425-431).
+//
+// Three kernels: delta_i = dO_i.o_i per (sequence, head, row); dk/dv with one CTA per (32 KV rows,
+// KV head) walking the query heads of the group and the query tiles at or below the diagonal --
+// so the sums over heads and rows happen in a fixed order in registers, no atomics, results are
+// deterministic; dq with one CTA per (32 query rows, query head) walking the KV tiles.
+// fp32 FMA on the CUDA cores: this is the <= 1e-4 parity path of the training configuration
+// (S = 128..2048, D = 64), not a tensor-core kernel.
+#include "common.cuh"
+
+namespace nimllm {
+
+namespace {
+
+constexpr int kT = 32;          // tile edge: query rows and KV rows per tile
+constexpr int kThreads = 128;
+
+struct BwdParams {
+    const float *q, *k, *v, *out, *dout, *lse;
+    const float *cos_tab, *sin_tab;
+    float *delta;               // [B, Hq, S]
+    float *dq, *dk, *dv;
+    int B, S, Hq, Hkv, pos0;
+    float scale;
+};
+
+__global__ void __launch_bounds__(128) bwd_delta_kernel(BwdParams p, int D) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);       // over B * S * Hq, head fastest
+    const int lane = threadIdx.x & 31;
+    if (row >= p.B * p.S * p.Hq) return;
+    const int h = row % p.Hq;
+    const int64_t bs = row / p.Hq;                              // b * S + i
+    const float *o = p.out + bs * p.Hq * D + (int64_t)h * D;
+    const float *d = p.dout + bs * p.Hq * D + (int64_t)h * D;
+    float acc = 0.f;
+    for (int c = lane; c < D; c += 32) acc += o[c] * d[c];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) {
+        const int b = (int)(bs / p.S), i = (int)(bs % p.S);
+        p.delta[((int64_t)b * p.Hq + h) * p.S + i] = acc;
+    }
+}
+
+// rows [row0, row0+32) x D of a [B*S, width] matrix (head at column col0) into smem [32][D+1]
+template <int D>
+__device__ __forceinline__ void load_tile(float *dst, const float *src, int64_t seq_base, int row0, int S, int width, int col0) {
+    for (int idx = threadIdx.x; idx < kT * (D / 4); idx += kThreads) {
+        const int r = idx / (D / 4), c4 = (idx % (D / 4)) * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < S) x = *reinterpret_cast<const float4 *>(src + (seq_base + row0 + r) * width + col0 + c4);
+        float *o = dst + r * (D + 1) + c4;
+        o[0] = x.x; o[1] = x.y; o[2] = x.z; o[3] = x.w;
+    }
+}
+
+// P and dS tiles [32 q rows][32 kv cols] from the staged Q, dO (rows) and K, V (cols).
+// Thread t computes row t/4, columns (t%4)*8 .. +7.
+template <int D>
+__device__ __forceinline__ void score_tile(const float *Qs, const float *dOs, const float *Ks, const float *Vs,
+                                           const float *lse_s, const float *delta_s, float *Ps, float *dSs,
+                                           int q0, int k0, int S, float scale) {
+    const int r = threadIdx.x >> 2, cg = (threadIdx.x & 3) * 8;
+    float s[8], dp[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) { s[u] = 0.f; dp[u] = 0.f; }
+    const float *qr = Qs + r * (D + 1), *dor = dOs + r * (D + 1);
+    for (int d = 0; d < D; d++) {
+        const float qv = qr[d], dv = dor[d];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            s[u] = fmaf(qv, Ks[(cg + u) * (D + 1) + d], s[u]);
+            dp[u] = fmaf(dv, Vs[(cg + u) * (D + 1) + d], dp[u]);
+        }
+    }
+    const int qi = q0 + r;
+    const float l = lse_s[r], dl = delta_s[r];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        const int kj = k0 + cg + u;
+        const bool live = qi < S && kj <= qi;
+        const float pv = live ? expf(s[u] * scale - l) : 0.f;
+        Ps[r * (kT + 1) + cg + u] = pv;
+        dSs[r * (kT + 1) + cg + u] = pv * (dp[u] - dl);
+    }
+}
+
+// undo the rotation on a row's values owned by one thread: d = dsel + 4*kk, kk < D/4; the partner
+// of column f < D/2 is f + D/2 = dsel + 4*(kk + D/8)
+template <int D>
+__device__ __forceinline__ void unrotate(float *x, const float *cos_tab, const float *sin_tab, int pos, int dsel) {
+    if (!cos_tab) return;
+#pragma unroll
+    for (int kk = 0; kk < D / 8; kk++) {
+        const int f = dsel + 4 * kk;
+        const float c = cos_tab[(int64_t)pos * (D / 2) + f], s = -sin_tab[(int64_t)pos * (D / 2) + f];
+        const float x0 = x[kk], x1 = x[kk + D / 8];
+        x[kk] = x0 * c - x1 * s;             // k_rope with sign = -1 (src/kernels.cu:399-413)
+        x[kk + D / 8] = x0 * s + x1 * c;
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(BwdParams p) {
+    extern __shared__ float smem[];
+    float *Ks = smem, *Vs = Ks + kT * (D + 1), *Qs = Vs + kT * (D + 1), *dOs = Qs + kT * (D + 1);
+    float *Ps = dOs + kT * (D + 1), *dSs = Ps + kT * (kT + 1);
+    float *lse_s = dSs + kT * (kT + 1), *delta_s = lse_s + kT;
+
+    const int jt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int G = p.Hq / p.Hkv, E = p.Hq * D, Ekv = p.Hkv * D;
+    const int k0 = jt * kT;
+    const int64_t seq_base = (int64_t)b * p.S;
+    const int n_tiles = (p.S + kT - 1) / kT;
+    load_tile<D>(Ks, p.k, seq_base, k0, p.S, Ekv, kvh * D);
+    load_tile<D>(Vs, p.v, seq_base, k0, p.S, Ekv, kvh * D);
+
+    const int c = threadIdx.x >> 2, dsel = threadIdx.x & 3;      // this thread's KV row and column phase
+    float dk[D / 4], dv[D / 4];
+#pragma unroll
+    for (int kk = 0; kk < D / 4; kk++) { dk[kk] = 0.f; dv[kk] = 0.f; }
+
+    for (int h = kvh * G; h < (kvh + 1) * G; h++)
+        for (int it = jt; it < n_tiles; it++) {
+            const int q0 = it * kT;
+            __syncthreads();                                     // previous tile fully consumed
+            load_tile<D>(Qs, p.q, seq_base, q0, p.S, E, h * D);
+            load_tile<D>(dOs, p.dout, seq_base, q0, p.S, E, h * D);
+            if (threadIdx.x < kT) {
+                const int qi = q0 + threadIdx.x;
+                lse_s[threadIdx.x] = qi < p.S ? p.lse[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+                delta_s[threadIdx.x] = qi < p.S ? p.delta[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+            }
+            __syncthreads();
+            score_tile<D>(Qs, dOs, Ks, Vs, lse_s, delta_s, Ps, dSs, q0, k0, p.S, p.scale);
+            __syncthreads();
+            for (int r = 0; r < kT; r++) {
+                const float pv = Ps[r * (kT + 1) + c], ds = dSs[r * (kT + 1) + c];
+#pragma unroll
+                for (int kk = 0; kk < D / 4; kk++) {
+                    dv[kk] = fmaf(pv, dOs[r * (D + 1) + dsel + 4 * kk], dv[kk]);
+                    dk[kk] = fmaf(ds, Qs[r * (D + 1) + dsel + 4 * kk], dk[kk]);
+                }
+            }
+        }
+    const int kj = k0 + c;
+    if (kj < p.S) {
+#pragma unroll
+        for (int kk = 0; kk < D / 4; kk++) dk[kk] *= p.scale;
+        unrotate<D>(dk, p.cos_tab, p.sin_tab, p.pos0 + kj, dsel);
+        float *dko = p.dk + (seq_base + kj) * Ekv + (int64_t)kvh * D, *dvo = p.dv + (seq_base + kj) * Ekv + (int64_t)kvh * D;
+#pragma unroll
+        for (int kk = 0; kk < D / 4; kk++) { dko[dsel + 4 * kk] = dk[kk]; dvo[dsel + 4 * kk] = dv[kk]; }
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads) bwd_dq_kernel(BwdParams p) {
+    extern __shared__ float smem[];
+    float *Ks = smem, *Vs = Ks + kT * (D + 1), *Qs = Vs + kT * (D + 1), *dOs = Qs + kT * (D + 1);
+    float *Ps = dOs + kT * (D + 1), *dSs = Ps + kT * (kT + 1);
+    float *lse_s = dSs + kT * (kT + 1), *delta_s = lse_s + kT;
+
+    const int it = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int G = p.Hq / p.Hkv, E = p.Hq * D, Ekv = p.Hkv * D, kvh = h / G;
+    const int q0 = it * kT;
+    const int64_t seq_base = (int64_t)b * p.S;
+    load_tile<D>(Qs, p.q, seq_base, q0, p.S, E, h * D);
+    load_tile<D>(dOs, p.dout, seq_base, q0, p.S, E, h * D);
+    if (threadIdx.x < kT) {
+        const int qi = q0 + threadIdx.x;
+        lse_s[threadIdx.x] = qi < p.S ? p.lse[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+        delta_s[threadIdx.x] = qi < p.S ? p.delta[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+    }
+    const int r = threadIdx.x >> 2, dsel = threadIdx.x & 3;
+    float dq[D / 4];
+#pragma unroll
+    for (int kk = 0; kk < D / 4; kk++) dq[kk] = 0.f;
+
+    for (int jt = 0; jt <= it; jt++) {
+        const int k0 = jt * kT;
+        __syncthreads();
+        load_tile<D>(Ks, p.k, seq_base, k0, p.S, Ekv, kvh * D);
+        load_tile<D>(Vs, p.v, seq_base, k0, p.S, Ekv, kvh * D);
+        __syncthreads();
+        score_tile<D>(Qs, dOs, Ks, Vs, lse_s, delta_s, Ps, dSs, q0, k0, p.S, p.scale);
+        __syncthreads();
+        for (int cc = 0; cc < kT; cc++) {
+            const float ds = dSs[r * (kT + 1) + cc];
+#pragma unroll
+            for (int kk = 0; kk < D / 4; kk++) dq[kk] = fmaf(ds, Ks[cc * (D + 1) + dsel + 4 * kk], dq[kk]);
+        }
+    }
+    const int qi = q0 + r;
+    if (qi < p.S) {
+#pragma unroll
+        for (int kk = 0; kk < D / 4; kk++) dq[kk] *= p.scale;
+        unrotate<D>(dq, p.cos_tab, p.sin_tab, p.pos0 + qi, dsel);
+        float *o = p.dq + (seq_base + qi) * E + (int64_t)h * D;
+#pragma unroll
+        for (int kk = 0; kk < D / 4; kk++) o[dsel + 4 * kk] = dq[kk];
+    }
+}
+
+template <int D>
+int launch_bwd(const BwdParams &p, cudaStream_t st) {
+    const size_t smem = (size_t)(4 * kT * (D + 1) + 2 * kT * (kT + 1) + 2 * kT) * sizeof(float);
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill_bwd: shared memory opt-in: %s", cudaGetErrorString(e));
+        attr_set[dev] = true;
+    }
+    const int n_tiles = (p.S + kT - 1) / kT;
+    const int rows = p.B * p.S * p.Hq;
+    bwd_delta_kernel<<<(rows + 3) / 4, 128, 0, st>>>(p, D);
+    NIMLLM_CHECK_LAUNCH("attn_prefill_bwd delta");
+    bwd_dkdv_kernel<D><<<dim3(n_tiles, p.Hkv, p.B), kThreads, smem, st>>>(p);
+    NIMLLM_CHECK_LAUNCH("attn_prefill_bwd dk dv");
+    bwd_dq_kernel<D><<<dim3(n_tiles, p.Hq, p.B), kThreads, smem, st>>>(p);
+    NIMLLM_CHECK_LAUNCH("attn_prefill_bwd dq");
+    return NIMLLM_OK;
+}
+
+}  // namespace
+}  // namespace nimllm
+
+using namespace nimllm;
+
+extern "C" {
+
+size_t nimllm_attn_prefill_bwd_workspace_bytes(int batch, int seq_len, int n_head) {
+    if (batch <= 0 || seq_len <= 0 || n_head <= 0) return 0;
+    return (size_t)batch * seq_len * n_head * sizeof(float);
+}
+
+int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float *v, const float *out,
+                            const float *dout, const float *lse, const float *rope_cos, const float *rope_sin,
+                            int pos0, float *dq, float *dk, float *dv, int batch, int seq_len, int n_head,
+                            int n_kv_head, int head_dim, float scale, void *workspace, size_t workspace_bytes,
+                            void *stream) {
+    if (!q_rot || !k_rot || !v || !out || !dout || !lse || !dq || !dk || !dv)
+        return fail(NIMLLM_ERR_ARG, "attn_prefill_bwd: null pointer (q, k, v, out, dout, lse, dq, dk, dv are all required)");
+    if (batch <= 0 || seq_len <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head != 0)
+        return fail(NIMLLM_ERR_ARG, "attn_prefill_bwd: bad shape B=%d S=%d Hq=%d Hkv=%d", batch, seq_len, n_head, n_kv_head);
+    if (head_dim != 32 && head_dim != 64 && head_dim != 128)
+        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill_bwd: head_dim %d (32, 64 and 128 are built)", head_dim);
+    if ((rope_cos == nullptr) != (rope_sin == nullptr))
+        return fail(NIMLLM_ERR_ARG, "attn_prefill_bwd: rope_cos and rope_sin go together");
+    if (batch > 65535 || n_head > 65535) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill_bwd: batch or head count > 65535");
+    const size_t need = nimllm_attn_prefill_bwd_workspace_bytes(batch, seq_len, n_head);
+    if (!workspace || workspace_bytes < need)
+        return fail(NIMLLM_ERR_WORKSPACE, "attn_prefill_bwd: workspace %zu bytes, need %zu", workspace_bytes, need);
+    if (((uintptr_t)q_rot | (uintptr_t)k_rot | (uintptr_t)v | (uintptr_t)dout) & 15)
+        return fail(NIMLLM_ERR_ARG, "attn_prefill_bwd: q, k, v, dout must be 16-byte aligned");
+    BwdParams p;
+    p.q = q_rot; p.k = k_rot; p.v = v; p.out = out; p.dout = dout; p.lse = lse;
+    p.cos_tab = rope_cos; p.sin_tab = rope_sin; p.delta = (float *)workspace;
+    p.dq = dq; p.dk = dk; p.dv = dv;
+    p.B = batch; p.S = seq_len; p.Hq = n_head; p.Hkv = n_kv_head; p.pos0 = pos0;
+    p.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)head_dim);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (head_dim == 32) return launch_bwd<32>(p, st);
+    if (head_dim == 64) return launch_bwd<64>(p, st);
+    return launch_bwd<128>(p, st);
+}
+
+}  // extern "C"

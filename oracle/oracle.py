@@ -205,6 +205,7 @@ def ref_lib() -> C.CDLL:
     if _REF is None:
         R = C.CDLL(os.path.join(_HERE, "_ref", "libnimllm_ref.so"))
         R.ref_attn_forward.argtypes = [f32p] * 6 + [C.c_int] * 5
+        R.ref_attn_backward.argtypes = [f32p] * 9 + [C.c_int] * 4
         R.ref_kvcache_create.restype = C.c_void_p
         R.ref_kvcache_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p]
         R.ref_kvcache_reset.argtypes = [C.c_void_p]
@@ -225,6 +226,19 @@ def ref_lib() -> C.CDLL:
         R.ref_model_prefill_lib.argtypes = [C.c_void_p, i32p, C.c_int, C.c_void_p, f32p]
         _REF = R
     return _REF
+
+
+def ref_attn_backward(q_rot, k_rot, v, dout, cos, sin, Hq, Hkv, D):
+    """backward()'s attention block run through the reference's compiled kernels + cuBLAS."""
+    q_rot = np.ascontiguousarray(q_rot, np.float32); k_rot = np.ascontiguousarray(k_rot, np.float32)
+    v = np.ascontiguousarray(v, np.float32); dout = np.ascontiguousarray(dout, np.float32)
+    S = q_rot.shape[0]
+    dq = np.zeros((S, Hq * D), np.float32); dk = np.zeros((S, Hkv * D), np.float32); dv = np.zeros((S, Hkv * D), np.float32)
+    rc = ref_lib().ref_attn_backward(q_rot, k_rot, v, dout, np.ascontiguousarray(cos[:S]), np.ascontiguousarray(sin[:S]),
+                                     dq, dk, dv, S, Hq, Hkv, D)
+    if rc:
+        raise RuntimeError("reference harness failed")
+    return dq, dk, dv
 
 
 def ref_attn_forward(q, k, v, cos, sin, Hq, Hkv, D, apply_rope=True):

@@ -32,6 +32,14 @@ void gpu_extract_kv_head(const float *src, float *dst, int qHead, int kvRepeat, 
                          int n_kv_dim, int head_dim);
 void gpu_rope_fwd(float *data, const float *cos_tab, const float *sin_tab, int seq_len,
                   int n_embd, int n_head, int head_dim);
+/* backward-path launchers (src/kernels.cu:341-345,390-394,425-431,471-477,159-161) */
+void gpu_softmax_bwd(const float *y, const float *dy, float *dx, int rows, int cols);
+void gpu_insert_head_acc(const float *src, float *dst, int h, int seq_len, int n_embd, int head_dim);
+void gpu_insert_kv_head_acc(const float *src, float *dst, int qHead, int kvRepeat, int seq_len,
+                            int n_kv_dim, int head_dim);
+void gpu_rope_bwd(float *grad, const float *cos_tab, const float *sin_tab, int seq_len, int n_embd,
+                  int n_head, int head_dim);
+void gpu_scale(const float *x, float s, float *y, int n);
 /* non-attention launchers used by the whole-model harness (src/gpu.nim:219-232,282-290) */
 void gpu_embed_fwd(const float *wte, const int *tokens, float *out, int seq_len, int dim);
 void gpu_rmsnorm_affine_fwd(const float *x, const float *gamma, float *y, float *rms_out, int rows, int dim);
@@ -117,6 +125,65 @@ int ref_attn_forward(float *q, float *k, const float *v, const float *cos_tab,
     CK(cudaMemcpy(k, dk, S * Ekv * 4, cudaMemcpyDeviceToHost));
     CK(cudaMemcpy(out, dout, S * E * 4, cudaMemcpyDeviceToHost));
     cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(dc); cudaFree(ds); cudaFree(dout); cudaFree(scr);
+    return 0;
+}
+
+/* src/model.nim:639-685: the attention block of backward(), restated launch by launch with
+ * the reference's own kernels and cublasSgemm_v2.  Host buffers: q_rot [S,E], k_rot, v [S,Ekv]
+ * (as saveCache left them), d_attn_out [S,E]; dq [S,E], dk, dv [S,Ekv] come back with the
+ * rotation undone on dq and dk. */
+int ref_attn_backward(const float *q_rot, const float *k_rot, const float *v, const float *d_attn_out,
+                      const float *cos_tab, const float *sin_tab, float *dq_h, float *dk_h, float *dv_h,
+                      int S, int Hq, int Hkv, int D) {
+    if (ref_init()) return -1;
+    size_t E = (size_t)Hq * D, Ekv = (size_t)Hkv * D, half = D / 2;
+    int G = Hq / Hkv;
+    float scale = 1.0f / sqrtf((float)D);
+    float *q, *k, *vv, *dout, *dc, *ds, *dq, *dk, *dv, *scr;
+    CK(cudaMalloc(&q, S * E * 4)); CK(cudaMalloc(&k, S * Ekv * 4)); CK(cudaMalloc(&vv, S * Ekv * 4));
+    CK(cudaMalloc(&dout, S * E * 4));
+    CK(cudaMalloc(&dc, S * half * 4)); CK(cudaMalloc(&ds, S * half * 4));
+    CK(cudaMalloc(&dq, S * E * 4)); CK(cudaMalloc(&dk, S * Ekv * 4)); CK(cudaMalloc(&dv, S * Ekv * 4));
+    CK(cudaMalloc(&scr, ((size_t)7 * S * D + (size_t)4 * S * S) * 4));
+    CK(cudaMemcpy(q, q_rot, S * E * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(k, k_rot, S * Ekv * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(vv, v, S * Ekv * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(dout, d_attn_out, S * E * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(dc, cos_tab, S * half * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(ds, sin_tab, S * half * 4, cudaMemcpyHostToDevice));
+    /* trackedCreate hands out zeroed memory (src/autograd.nim:37-51) */
+    CK(cudaMemset(dq, 0, S * E * 4)); CK(cudaMemset(dk, 0, S * Ekv * 4)); CK(cudaMemset(dv, 0, S * Ekv * 4));
+    float *doutH = scr, *qH = doutH + (size_t)S * D, *kH = qH + (size_t)S * D, *vH = kH + (size_t)S * D,
+          *dqH = vH + (size_t)S * D, *dkH = dqH + (size_t)S * D, *dvH = dkH + (size_t)S * D,
+          *scores = dvH + (size_t)S * D, *probs = scores + (size_t)S * S, *dW = probs + (size_t)S * S,
+          *dScores = dW + (size_t)S * S;
+    for (int h = 0; h < Hq; h++) {
+        gpu_extract_head(dout, doutH, h, S, (int)E, D);
+        gpu_extract_head(q, qH, h, S, (int)E, D);
+        gpu_extract_kv_head(k, kH, h, G, S, (int)Ekv, D);
+        gpu_extract_kv_head(vv, vH, h, G, S, (int)Ekv, D);
+        ref_sgemm(2, S, S, D, qH, kH, scores);
+        gpu_causal_mask(scores, scale, S);
+        gpu_softmax_fwd(scores, probs, S, S);
+        ref_sgemm(2, S, S, D, doutH, vH, dW);
+        ref_sgemm(4, S, D, S, probs, doutH, dvH);
+        CK(cudaMemset(dScores, 0, (size_t)S * S * 4));
+        gpu_softmax_bwd(probs, dW, dScores, S, S);
+        gpu_scale(dScores, scale, dScores, S * S);
+        ref_sgemm(0, S, D, S, dScores, kH, dqH);
+        ref_sgemm(4, S, D, S, dScores, qH, dkH);
+        gpu_insert_head_acc(dqH, dq, h, S, (int)E, D);
+        gpu_insert_kv_head_acc(dkH, dk, h, G, S, (int)Ekv, D);
+        gpu_insert_kv_head_acc(dvH, dv, h, G, S, (int)Ekv, D);
+    }
+    gpu_rope_bwd(dq, dc, ds, S, (int)E, Hq, D);
+    gpu_rope_bwd(dk, dc, ds, S, (int)Ekv, Hkv, D);
+    CK(cudaDeviceSynchronize());
+    CK(cudaMemcpy(dq_h, dq, S * E * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(dk_h, dk, S * Ekv * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(dv_h, dv, S * Ekv * 4, cudaMemcpyDeviceToHost));
+    cudaFree(q); cudaFree(k); cudaFree(vv); cudaFree(dout); cudaFree(dc); cudaFree(ds);
+    cudaFree(dq); cudaFree(dk); cudaFree(dv); cudaFree(scr);
     return 0;
 }
 
