@@ -636,6 +636,40 @@ struct BalCombineParams {
     int B, Hq, Hkv, G, D, W, U, max_len, wk;
 };
 
+// What a merge thread needs to know about its output row (sequence, query head): which records
+// hold the pieces of the row's (sequence, KV head) pair.  n = 0: empty sequence, n = 1: one warp
+// covered the pair and wrote the row itself.
+struct BalRow {
+    int g, n, w_first, slot_first;
+};
+__device__ __forceinline__ BalRow bal_row(const BalCombineParams &c, int row) {
+    BalRow r;
+    const int b = row / c.Hq, hq = row % c.Hq, kvh = hq / c.G;
+    r.g = hq % c.G;
+    const int n_uniform = (c.max_len + c.U - 1) / c.U;
+    const int cb = c.seq_len ? c.cum[b] : b * n_uniform;
+    const int nb = (c.seq_len ? c.cum[b + 1] : (b + 1) * n_uniform) - cb;
+    const int64_t T = (int64_t)c.Hkv * (c.seq_len ? c.cum[c.B] : c.B * n_uniform);
+    r.n = 0; r.w_first = 0; r.slot_first = 0;
+    if (nb > 0)
+        bal_pair_pieces((int64_t)c.Hkv * cb + (int64_t)kvh * nb, nb, T, bal_active_warps(T, c.wk), r.w_first, r.n, r.slot_first);
+    return r;
+}
+__device__ __forceinline__ const float *bal_rec(const BalCombineParams &c, const BalRow &r, int i) {
+    return c.recs + (((int64_t)(r.w_first + i) * 2 + (i == 0 ? r.slot_first : 0)) * c.G + r.g) * c.W;
+}
+// zeros (and an empty record) for a row of an empty sequence, written by `nthreads` threads
+__device__ __forceinline__ void bal_write_empty(const BalCombineParams &c, int row, int tid, int nthreads) {
+    for (int d = tid; d < c.D; d += nthreads) {
+        if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, 0.f);
+        if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = 0.f;
+    }
+    if (c.partials_out && tid == 0) {
+        float *o = c.partials_out + (int64_t)row * c.W;
+        o[c.D] = -INFINITY; o[c.D + 1] = 0.f; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
+    }
+}
+
 // Variant for batches of many pairs cut into few pieces (measured faster there than the
 // four-warp CTA per row below): one warp per output row; rows of empty sequences become zeros, rows
 // whose pair one warp covered are already final, the others merge the records of the
@@ -644,30 +678,11 @@ __global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombinePa
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= c.B * c.Hq) return;
-    const int b = row / c.Hq, hq = row % c.Hq, kvh = hq / c.G, g = hq % c.G;
-    const int n_uniform = (c.max_len + c.U - 1) / c.U;
-    const int cb = c.seq_len ? c.cum[b] : b * n_uniform;
-    const int nb = (c.seq_len ? c.cum[b + 1] : (b + 1) * n_uniform) - cb;
-    const int64_t T = (int64_t)c.Hkv * (c.seq_len ? c.cum[c.B] : c.B * n_uniform);
-    if (nb == 0) {
-        for (int d = lane; d < c.D; d += 32) {
-            if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, 0.f);
-            if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = 0.f;
-        }
-        if (c.partials_out && lane == 0) {
-            float *o = c.partials_out + (int64_t)row * c.W;
-            o[c.D] = -INFINITY; o[c.D + 1] = 0.f; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
-        }
-        return;
-    }
-    const int wa = bal_active_warps(T, c.wk);
-    const int64_t s = (int64_t)c.Hkv * cb + (int64_t)kvh * nb;
-    int w_first, n, slot_first;
-    bal_pair_pieces(s, nb, T, wa, w_first, n, slot_first);
-    if (n == 1) return;
-    auto rec_of = [&](int i) -> const float * {
-        return c.recs + (((int64_t)(w_first + i) * 2 + (i == 0 ? slot_first : 0)) * c.G + g) * c.W;
-    };
+    const BalRow br = bal_row(c, row);
+    if (br.n == 0) { bal_write_empty(c, row, lane, 32); return; }
+    if (br.n == 1) return;
+    const int n = br.n;
+    auto rec_of = [&](int i) -> const float * { return bal_rec(c, br, i); };
     float M = -INFINITY, wsum = 0.f;
     float acc[8];
 #pragma unroll
@@ -762,30 +777,11 @@ __global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams 
     __shared__ float s_w[4];
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = row / c.Hq, hq = row % c.Hq, kvh = hq / c.G, g = hq % c.G;
-    const int n_uniform = (c.max_len + c.U - 1) / c.U;
-    const int cb = c.seq_len ? c.cum[b] : b * n_uniform;
-    const int nb = (c.seq_len ? c.cum[b + 1] : (b + 1) * n_uniform) - cb;
-    const int64_t T = (int64_t)c.Hkv * (c.seq_len ? c.cum[c.B] : c.B * n_uniform);
-    if (nb == 0) {
-        for (int d = threadIdx.x; d < c.D; d += 128) {
-            if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, 0.f);
-            if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = 0.f;
-        }
-        if (c.partials_out && threadIdx.x == 0) {
-            float *o = c.partials_out + (int64_t)row * c.W;
-            o[c.D] = -INFINITY; o[c.D + 1] = 0.f; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
-        }
-        return;
-    }
-    const int wa = bal_active_warps(T, c.wk);
-    const int64_t s = (int64_t)c.Hkv * cb + (int64_t)kvh * nb;
-    int w_first, n, slot_first;
-    bal_pair_pieces(s, nb, T, wa, w_first, n, slot_first);
-    if (n == 1) return;
-    auto rec_of = [&](int i) -> const float * {
-        return c.recs + (((int64_t)(w_first + i) * 2 + (i == 0 ? slot_first : 0)) * c.G + g) * c.W;
-    };
+    const BalRow br = bal_row(c, row);
+    if (br.n == 0) { bal_write_empty(c, row, threadIdx.x, 128); return; }
+    if (br.n == 1) return;
+    const int n = br.n;
+    auto rec_of = [&](int i) -> const float * { return bal_rec(c, br, i); };
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
