@@ -53,69 +53,103 @@ __global__ void __launch_bounds__(128) bwd_delta_kernel(BwdParams p, int D) {
     }
 }
 
-// rows [row0, row0+32) x D of a [B*S, width] matrix (head at column col0) into smem [32][D+1]
+// Shared-memory tiles are [32][D + 4] floats: rows stay 16-byte aligned for 128-bit loads and
+// consecutive rows start 4 banks apart, so the 8 lanes of a quarter-warp reading one float4 each
+// from consecutive rows (or consecutive float4s of one row) never collide.
+template <int D> constexpr int ld() { return D + 4; }
+
+// rows [row0, row0+32) x D of a [B*S, width] matrix (head at column col0) into a tile
 template <int D>
 __device__ __forceinline__ void load_tile(float *dst, const float *src, int64_t seq_base, int row0, int S, int width, int col0) {
     for (int idx = threadIdx.x; idx < kT * (D / 4); idx += kThreads) {
         const int r = idx / (D / 4), c4 = (idx % (D / 4)) * 4;
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
         if (row0 + r < S) x = *reinterpret_cast<const float4 *>(src + (seq_base + row0 + r) * width + col0 + c4);
-        float *o = dst + r * (D + 1) + c4;
-        o[0] = x.x; o[1] = x.y; o[2] = x.z; o[3] = x.w;
+        *reinterpret_cast<float4 *>(dst + r * ld<D>() + c4) = x;
+    }
+}
+
+// The same tile in two steps, so that the global loads of the next tile are in flight while the
+// current one is being used: fetch into registers (D/16 float4 per thread), stash into the tile.
+template <int D>
+__device__ __forceinline__ void fetch_tile(float4 (&reg)[D / 16], const float *src, int64_t seq_base, int row0, int S, int width, int col0) {
+#pragma unroll
+    for (int k = 0; k < D / 16; k++) {
+        const int idx = threadIdx.x + k * kThreads;
+        const int r = idx / (D / 4), c4 = (idx % (D / 4)) * 4;
+        reg[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < S) reg[k] = *reinterpret_cast<const float4 *>(src + (seq_base + row0 + r) * width + col0 + c4);
+    }
+}
+template <int D>
+__device__ __forceinline__ void stash_tile(float *dst, const float4 (&reg)[D / 16]) {
+#pragma unroll
+    for (int k = 0; k < D / 16; k++) {
+        const int idx = threadIdx.x + k * kThreads;
+        const int r = idx / (D / 4), c4 = (idx % (D / 4)) * 4;
+        *reinterpret_cast<float4 *>(dst + r * ld<D>() + c4) = reg[k];
     }
 }
 
 // P and dS tiles [32 q rows][32 kv cols] from the staged Q, dO (rows) and K, V (cols).
-// Thread t computes row t/4, columns (t%4)*8 .. +7.
+// Thread t computes row t/4, columns (t%4) + 4u, u < 8, four values of d per step.
 template <int D>
 __device__ __forceinline__ void score_tile(const float *Qs, const float *dOs, const float *Ks, const float *Vs,
                                            const float *lse_s, const float *delta_s, float *Ps, float *dSs,
                                            int q0, int k0, int S, float scale) {
-    const int r = threadIdx.x >> 2, cg = (threadIdx.x & 3) * 8;
+    const int r = threadIdx.x >> 2, cg = threadIdx.x & 3;
     float s[8], dp[8];
 #pragma unroll
     for (int u = 0; u < 8; u++) { s[u] = 0.f; dp[u] = 0.f; }
-    const float *qr = Qs + r * (D + 1), *dor = dOs + r * (D + 1);
-    for (int d = 0; d < D; d++) {
-        const float qv = qr[d], dv = dor[d];
+    const float *qr = Qs + r * ld<D>(), *dor = dOs + r * ld<D>();
+#pragma unroll 4
+    for (int d = 0; d < D; d += 4) {
+        const float4 qv = *reinterpret_cast<const float4 *>(qr + d);
+        const float4 dv = *reinterpret_cast<const float4 *>(dor + d);
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            s[u] = fmaf(qv, Ks[(cg + u) * (D + 1) + d], s[u]);
-            dp[u] = fmaf(dv, Vs[(cg + u) * (D + 1) + d], dp[u]);
+            const float4 kv = *reinterpret_cast<const float4 *>(Ks + (cg + 4 * u) * ld<D>() + d);
+            const float4 vv = *reinterpret_cast<const float4 *>(Vs + (cg + 4 * u) * ld<D>() + d);
+            s[u] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, s[u]))));
+            dp[u] = fmaf(dv.x, vv.x, fmaf(dv.y, vv.y, fmaf(dv.z, vv.z, fmaf(dv.w, vv.w, dp[u]))));
         }
     }
     const int qi = q0 + r;
     const float l = lse_s[r], dl = delta_s[r];
 #pragma unroll
     for (int u = 0; u < 8; u++) {
-        const int kj = k0 + cg + u;
+        const int col = cg + 4 * u, kj = k0 + col;
         const bool live = qi < S && kj <= qi;
         const float pv = live ? expf(s[u] * scale - l) : 0.f;
-        Ps[r * (kT + 1) + cg + u] = pv;
-        dSs[r * (kT + 1) + cg + u] = pv * (dp[u] - dl);
+        Ps[r * (kT + 1) + col] = pv;
+        dSs[r * (kT + 1) + col] = pv * (dp[u] - dl);
     }
 }
 
-// undo the rotation on a row's values owned by one thread: d = dsel + 4*kk, kk < D/4; the partner
-// of column f < D/2 is f + D/2 = dsel + 4*(kk + D/8)
+// A thread owns the float4 groups dsel + 4*kq (kq < D/16) of its row: x[4*kq + i] is column
+// 4*(dsel + 4*kq) + i.  The rotation partner of column f < D/2 is f + D/2, i.e. group + D/8 =
+// the same thread's kq + D/32.
 template <int D>
 __device__ __forceinline__ void unrotate(float *x, const float *cos_tab, const float *sin_tab, int pos, int dsel) {
     if (!cos_tab) return;
+    static_assert(D % 32 == 0, "head_dim must be a multiple of 32");
 #pragma unroll
-    for (int kk = 0; kk < D / 8; kk++) {
-        const int f = dsel + 4 * kk;
-        const float c = cos_tab[(int64_t)pos * (D / 2) + f], s = -sin_tab[(int64_t)pos * (D / 2) + f];
-        const float x0 = x[kk], x1 = x[kk + D / 8];
-        x[kk] = x0 * c - x1 * s;             // k_rope with sign = -1 (src/kernels.cu:399-413)
-        x[kk + D / 8] = x0 * s + x1 * c;
-    }
+    for (int kq = 0; kq < D / 32; kq++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int f = 4 * (dsel + 4 * kq) + i;
+            const float c = cos_tab[(int64_t)pos * (D / 2) + f], s = -sin_tab[(int64_t)pos * (D / 2) + f];
+            const float x0 = x[4 * kq + i], x1 = x[4 * (kq + D / 32) + i];
+            x[4 * kq + i] = x0 * c - x1 * s;             // k_rope with sign = -1 (src/kernels.cu:399-413)
+            x[4 * (kq + D / 32) + i] = x0 * s + x1 * c;
+        }
 }
 
 template <int D>
 __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(BwdParams p) {
     extern __shared__ float smem[];
-    float *Ks = smem, *Vs = Ks + kT * (D + 1), *Qs = Vs + kT * (D + 1), *dOs = Qs + kT * (D + 1);
-    float *Ps = dOs + kT * (D + 1), *dSs = Ps + kT * (kT + 1);
+    float *Ks = smem, *Vs = Ks + kT * ld<D>(), *Qs = Vs + kT * ld<D>(), *dOs = Qs + kT * ld<D>();
+    float *Ps = dOs + kT * ld<D>(), *dSs = Ps + kT * (kT + 1);
     float *lse_s = dSs + kT * (kT + 1), *delta_s = lse_s + kT;
 
     const int jt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -131,29 +165,45 @@ __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(BwdParams p) {
 #pragma unroll
     for (int kk = 0; kk < D / 4; kk++) { dk[kk] = 0.f; dv[kk] = 0.f; }
 
-    for (int h = kvh * G; h < (kvh + 1) * G; h++)
-        for (int it = jt; it < n_tiles; it++) {
-            const int q0 = it * kT;
-            __syncthreads();                                     // previous tile fully consumed
-            load_tile<D>(Qs, p.q, seq_base, q0, p.S, E, h * D);
-            load_tile<D>(dOs, p.dout, seq_base, q0, p.S, E, h * D);
-            if (threadIdx.x < kT) {
-                const int qi = q0 + threadIdx.x;
-                lse_s[threadIdx.x] = qi < p.S ? p.lse[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
-                delta_s[threadIdx.x] = qi < p.S ? p.delta[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
-            }
-            __syncthreads();
-            score_tile<D>(Qs, dOs, Ks, Vs, lse_s, delta_s, Ps, dSs, q0, k0, p.S, p.scale);
-            __syncthreads();
-            for (int r = 0; r < kT; r++) {
-                const float pv = Ps[r * (kT + 1) + c], ds = dSs[r * (kT + 1) + c];
+    // (query head, query tile) pairs of this KV tile, in a fixed order; the next pair's rows are
+    // fetched into registers while the current pair is being worked on
+    const int per_h = n_tiles - jt, total = G * per_h;
+    float4 rq[D / 16], rdo[D / 16];
+    float rl = 0.f, rd = 0.f;
+    auto fetch = [&](int n) {
+        const int h = kvh * G + n / per_h, q0 = (jt + n % per_h) * kT;
+        fetch_tile<D>(rq, p.q, seq_base, q0, p.S, E, h * D);
+        fetch_tile<D>(rdo, p.dout, seq_base, q0, p.S, E, h * D);
+        if (threadIdx.x < kT) {
+            const int qi = q0 + threadIdx.x;
+            rl = qi < p.S ? p.lse[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+            rd = qi < p.S ? p.delta[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+        }
+    };
+    fetch(0);
+    for (int n = 0; n < total; n++) {
+        const int q0 = (jt + n % per_h) * kT;
+        __syncthreads();                                         // previous pair fully consumed
+        stash_tile<D>(Qs, rq);
+        stash_tile<D>(dOs, rdo);
+        if (threadIdx.x < kT) { lse_s[threadIdx.x] = rl; delta_s[threadIdx.x] = rd; }
+        __syncthreads();
+        if (n + 1 < total) fetch(n + 1);
+        score_tile<D>(Qs, dOs, Ks, Vs, lse_s, delta_s, Ps, dSs, q0, k0, p.S, p.scale);
+        __syncthreads();
+        for (int r = 0; r < kT; r++) {
+            const float pv = Ps[r * (kT + 1) + c], ds = dSs[r * (kT + 1) + c];
 #pragma unroll
-                for (int kk = 0; kk < D / 4; kk++) {
-                    dv[kk] = fmaf(pv, dOs[r * (D + 1) + dsel + 4 * kk], dv[kk]);
-                    dk[kk] = fmaf(ds, Qs[r * (D + 1) + dsel + 4 * kk], dk[kk]);
-                }
+            for (int kq = 0; kq < D / 16; kq++) {
+                const float4 o4 = *reinterpret_cast<const float4 *>(dOs + r * ld<D>() + 4 * (dsel + 4 * kq));
+                const float4 q4 = *reinterpret_cast<const float4 *>(Qs + r * ld<D>() + 4 * (dsel + 4 * kq));
+                dv[4 * kq + 0] = fmaf(pv, o4.x, dv[4 * kq + 0]); dv[4 * kq + 1] = fmaf(pv, o4.y, dv[4 * kq + 1]);
+                dv[4 * kq + 2] = fmaf(pv, o4.z, dv[4 * kq + 2]); dv[4 * kq + 3] = fmaf(pv, o4.w, dv[4 * kq + 3]);
+                dk[4 * kq + 0] = fmaf(ds, q4.x, dk[4 * kq + 0]); dk[4 * kq + 1] = fmaf(ds, q4.y, dk[4 * kq + 1]);
+                dk[4 * kq + 2] = fmaf(ds, q4.z, dk[4 * kq + 2]); dk[4 * kq + 3] = fmaf(ds, q4.w, dk[4 * kq + 3]);
             }
         }
+    }
     const int kj = k0 + c;
     if (kj < p.S) {
 #pragma unroll
@@ -161,18 +211,22 @@ __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(BwdParams p) {
         unrotate<D>(dk, p.cos_tab, p.sin_tab, p.pos0 + kj, dsel);
         float *dko = p.dk + (seq_base + kj) * Ekv + (int64_t)kvh * D, *dvo = p.dv + (seq_base + kj) * Ekv + (int64_t)kvh * D;
 #pragma unroll
-        for (int kk = 0; kk < D / 4; kk++) { dko[dsel + 4 * kk] = dk[kk]; dvo[dsel + 4 * kk] = dv[kk]; }
+        for (int kq = 0; kq < D / 16; kq++) {
+            *reinterpret_cast<float4 *>(dko + 4 * (dsel + 4 * kq)) = make_float4(dk[4 * kq], dk[4 * kq + 1], dk[4 * kq + 2], dk[4 * kq + 3]);
+            *reinterpret_cast<float4 *>(dvo + 4 * (dsel + 4 * kq)) = make_float4(dv[4 * kq], dv[4 * kq + 1], dv[4 * kq + 2], dv[4 * kq + 3]);
+        }
     }
 }
 
 template <int D>
 __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(BwdParams p) {
     extern __shared__ float smem[];
-    float *Ks = smem, *Vs = Ks + kT * (D + 1), *Qs = Vs + kT * (D + 1), *dOs = Qs + kT * (D + 1);
-    float *Ps = dOs + kT * (D + 1), *dSs = Ps + kT * (kT + 1);
+    float *Ks = smem, *Vs = Ks + kT * ld<D>(), *Qs = Vs + kT * ld<D>(), *dOs = Qs + kT * ld<D>();
+    float *Ps = dOs + kT * ld<D>(), *dSs = Ps + kT * (kT + 1);
     float *lse_s = dSs + kT * (kT + 1), *delta_s = lse_s + kT;
 
-    const int it = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    // the query tiles with the longest walk are launched first
+    const int it = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int G = p.Hq / p.Hkv, E = p.Hq * D, Ekv = p.Hkv * D, kvh = h / G;
     const int q0 = it * kT;
     const int64_t seq_base = (int64_t)b * p.S;
@@ -188,18 +242,29 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(BwdParams p) {
 #pragma unroll
     for (int kk = 0; kk < D / 4; kk++) dq[kk] = 0.f;
 
+    float4 rk[D / 16], rv[D / 16];
+    fetch_tile<D>(rk, p.k, seq_base, 0, p.S, Ekv, kvh * D);
+    fetch_tile<D>(rv, p.v, seq_base, 0, p.S, Ekv, kvh * D);
     for (int jt = 0; jt <= it; jt++) {
         const int k0 = jt * kT;
         __syncthreads();
-        load_tile<D>(Ks, p.k, seq_base, k0, p.S, Ekv, kvh * D);
-        load_tile<D>(Vs, p.v, seq_base, k0, p.S, Ekv, kvh * D);
+        stash_tile<D>(Ks, rk);
+        stash_tile<D>(Vs, rv);
         __syncthreads();
+        if (jt < it) {                                           // next KV tile in flight during this one
+            fetch_tile<D>(rk, p.k, seq_base, k0 + kT, p.S, Ekv, kvh * D);
+            fetch_tile<D>(rv, p.v, seq_base, k0 + kT, p.S, Ekv, kvh * D);
+        }
         score_tile<D>(Qs, dOs, Ks, Vs, lse_s, delta_s, Ps, dSs, q0, k0, p.S, p.scale);
         __syncthreads();
         for (int cc = 0; cc < kT; cc++) {
             const float ds = dSs[r * (kT + 1) + cc];
 #pragma unroll
-            for (int kk = 0; kk < D / 4; kk++) dq[kk] = fmaf(ds, Ks[cc * (D + 1) + dsel + 4 * kk], dq[kk]);
+            for (int kq = 0; kq < D / 16; kq++) {
+                const float4 k4 = *reinterpret_cast<const float4 *>(Ks + cc * ld<D>() + 4 * (dsel + 4 * kq));
+                dq[4 * kq + 0] = fmaf(ds, k4.x, dq[4 * kq + 0]); dq[4 * kq + 1] = fmaf(ds, k4.y, dq[4 * kq + 1]);
+                dq[4 * kq + 2] = fmaf(ds, k4.z, dq[4 * kq + 2]); dq[4 * kq + 3] = fmaf(ds, k4.w, dq[4 * kq + 3]);
+            }
         }
     }
     const int qi = q0 + r;
@@ -209,13 +274,14 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(BwdParams p) {
         unrotate<D>(dq, p.cos_tab, p.sin_tab, p.pos0 + qi, dsel);
         float *o = p.dq + (seq_base + qi) * E + (int64_t)h * D;
 #pragma unroll
-        for (int kk = 0; kk < D / 4; kk++) o[dsel + 4 * kk] = dq[kk];
+        for (int kq = 0; kq < D / 16; kq++)
+            *reinterpret_cast<float4 *>(o + 4 * (dsel + 4 * kq)) = make_float4(dq[4 * kq], dq[4 * kq + 1], dq[4 * kq + 2], dq[4 * kq + 3]);
     }
 }
 
 template <int D>
 int launch_bwd(const BwdParams &p, cudaStream_t st) {
-    const size_t smem = (size_t)(4 * kT * (D + 1) + 2 * kT * (kT + 1) + 2 * kT) * sizeof(float);
+    const size_t smem = (size_t)(4 * kT * ld<D>() + 2 * kT * (kT + 1) + 2 * kT) * sizeof(float);
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
