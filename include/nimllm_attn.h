@@ -211,9 +211,9 @@ int nimllm_attn_prefill(void *q, void *k, const void *v, int dtype, const float 
  *                 leaves them (NULL: no rotation is undone)
  *   dq [B, S, Hq*D], dk, dv [B, S, Hkv*D] are overwritten (the reference accumulates into
  *                 zero-initialised buffers); sums run in a fixed order, results repeat bit for bit
- *   workspace     nimllm_attn_prefill_bwd_workspace_bytes(batch, seq_len, n_head) bytes
+ *   workspace     nimllm_attn_prefill_bwd_workspace_bytes(batch, seq_len, n_head, head_dim) bytes
  */
-size_t nimllm_attn_prefill_bwd_workspace_bytes(int batch, int seq_len, int n_head);
+size_t nimllm_attn_prefill_bwd_workspace_bytes(int batch, int seq_len, int n_head, int head_dim);
 int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float *v, const float *out,
                             const float *dout, const float *lse, const float *rope_cos,
                             const float *rope_sin, int pos0, float *dq, float *dk, float *dv,

@@ -47,7 +47,7 @@ PROTOTYPES = {
     "nimllm_attn_prefill_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "nimllm_attn_prefill": (i32, [vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, i32,
                                   vp, vp, i32, vp, i64, i64, i32, vp, vp, sz, vp]),
-    "nimllm_attn_prefill_bwd_workspace_bytes": (sz, [i32, i32, i32]),
+    "nimllm_attn_prefill_bwd_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "nimllm_attn_prefill_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32,
                                       vp, sz, vp]),
     "gpu_rope_fwd": (None, [vp, vp, vp, i32, i32, i32, i32]),

@@ -165,7 +165,7 @@ def attn_backward(q_rot, k_rot, v, out, dout, lse, cos, sin, *, n_head, n_kv_hea
     B, S = q_rot.shape[0], q_rot.shape[1]
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     dq, dk, dv = torch.empty_like(q_rot), torch.empty_like(k_rot), torch.empty_like(v)
-    need = lib().nimllm_attn_prefill_bwd_workspace_bytes(B, S, n_head)
+    need = lib().nimllm_attn_prefill_bwd_workspace_bytes(B, S, n_head, head_dim)
     ws = _arena.get(need, q_rot.device)
     check(lib().nimllm_attn_prefill_bwd(
         _ptr(q_rot), _ptr(k_rot), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(cos), _ptr(sin), pos0,

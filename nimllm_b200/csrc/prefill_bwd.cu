@@ -30,6 +30,7 @@ struct BwdParams {
     const float *q, *k, *v, *out, *dout, *lse;
     const float *cos_tab, *sin_tab;
     float *delta;               // [B, Hq, S]
+    float *dk_part, *dv_part;   // [G][B*S][Hkv*D] per-query-head partial sums when G > 1, else null
     float *dq, *dk, *dv;
     int B, S, Hq, Hkv, pos0;
     float scale;
@@ -152,8 +153,14 @@ __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(BwdParams p) {
     float *Ps = dOs + kT * ld<D>(), *dSs = Ps + kT * (kT + 1);
     float *lse_s = dSs + kT * (kT + 1), *delta_s = lse_s + kT;
 
-    const int jt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // blockIdx.y is a KV head (one CTA sums over the group's query heads) or, when the partial
+    // buffers are given, a query head (G times the CTAs, a third of the walk each at G = 3; the
+    // partials are added up in head order by bwd_reduce_kernel)
+    const int jt = blockIdx.x, b = blockIdx.z;
     const int G = p.Hq / p.Hkv, E = p.Hq * D, Ekv = p.Hkv * D;
+    const bool split = p.dk_part != nullptr;
+    const int kvh = split ? (int)blockIdx.y / G : (int)blockIdx.y;
+    const int h_first = split ? (int)blockIdx.y : kvh * G, n_heads = split ? 1 : G;
     const int k0 = jt * kT;
     const int64_t seq_base = (int64_t)b * p.S;
     const int n_tiles = (p.S + kT - 1) / kT;
@@ -167,11 +174,11 @@ __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(BwdParams p) {
 
     // (query head, query tile) pairs of this KV tile, in a fixed order; the next pair's rows are
     // fetched into registers while the current pair is being worked on
-    const int per_h = n_tiles - jt, total = G * per_h;
+    const int per_h = n_tiles - jt, total = n_heads * per_h;
     float4 rq[D / 16], rdo[D / 16];
     float rl = 0.f, rd = 0.f;
     auto fetch = [&](int n) {
-        const int h = kvh * G + n / per_h, q0 = (jt + n % per_h) * kT;
+        const int h = h_first + n / per_h, q0 = (jt + n % per_h) * kT;
         fetch_tile<D>(rq, p.q, seq_base, q0, p.S, E, h * D);
         fetch_tile<D>(rdo, p.dout, seq_base, q0, p.S, E, h * D);
         if (threadIdx.x < kT) {
@@ -206,16 +213,50 @@ __global__ void __launch_bounds__(kThreads) bwd_dkdv_kernel(BwdParams p) {
     }
     const int kj = k0 + c;
     if (kj < p.S) {
+        float *dko, *dvo;
+        if (split) {                                             // raw partial sums of this query head
+            const int64_t off = (((int64_t)(h_first % G) * p.B * p.S) + seq_base + kj) * Ekv + (int64_t)kvh * D;
+            dko = p.dk_part + off; dvo = p.dv_part + off;
+        } else {
 #pragma unroll
-        for (int kk = 0; kk < D / 4; kk++) dk[kk] *= p.scale;
-        unrotate<D>(dk, p.cos_tab, p.sin_tab, p.pos0 + kj, dsel);
-        float *dko = p.dk + (seq_base + kj) * Ekv + (int64_t)kvh * D, *dvo = p.dv + (seq_base + kj) * Ekv + (int64_t)kvh * D;
+            for (int kk = 0; kk < D / 4; kk++) dk[kk] *= p.scale;
+            unrotate<D>(dk, p.cos_tab, p.sin_tab, p.pos0 + kj, dsel);
+            dko = p.dk + (seq_base + kj) * Ekv + (int64_t)kvh * D; dvo = p.dv + (seq_base + kj) * Ekv + (int64_t)kvh * D;
+        }
 #pragma unroll
         for (int kq = 0; kq < D / 16; kq++) {
             *reinterpret_cast<float4 *>(dko + 4 * (dsel + 4 * kq)) = make_float4(dk[4 * kq], dk[4 * kq + 1], dk[4 * kq + 2], dk[4 * kq + 3]);
             *reinterpret_cast<float4 *>(dvo + 4 * (dsel + 4 * kq)) = make_float4(dv[4 * kq], dv[4 * kq + 1], dv[4 * kq + 2], dv[4 * kq + 3]);
         }
     }
+}
+
+// dk, dv = sum over the G query heads of a KV head of the partials, in head order; dk is then
+// scaled and un-rotated.  One thread per (row, KV head, rotation pair).
+__global__ void __launch_bounds__(256) bwd_reduce_kernel(BwdParams p, int D) {
+    const int half = D / 2, G = p.Hq / p.Hkv, Ekv = p.Hkv * D;
+    const int64_t total = (int64_t)p.B * p.S * p.Hkv * half;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int f = (int)(idx % half);
+    const int kvh = (int)((idx / half) % p.Hkv);
+    const int64_t row = idx / ((int64_t)half * p.Hkv);             // b * S + position
+    const int64_t o = row * Ekv + (int64_t)kvh * D + f;
+    const int64_t gstride = (int64_t)p.B * p.S * Ekv;
+    float k0 = 0.f, k1 = 0.f, v0 = 0.f, v1 = 0.f;
+    for (int g = 0; g < G; g++) {
+        k0 += p.dk_part[g * gstride + o]; k1 += p.dk_part[g * gstride + o + half];
+        v0 += p.dv_part[g * gstride + o]; v1 += p.dv_part[g * gstride + o + half];
+    }
+    k0 *= p.scale; k1 *= p.scale;
+    if (p.cos_tab) {
+        const int pos = p.pos0 + (int)(row % p.S);
+        const float c = p.cos_tab[(int64_t)pos * half + f], s = -p.sin_tab[(int64_t)pos * half + f];
+        const float a = k0 * c - k1 * s, d = k0 * s + k1 * c;      // k_rope with sign = -1
+        k0 = a; k1 = d;
+    }
+    p.dk[o] = k0; p.dk[o + half] = k1;
+    p.dv[o] = v0; p.dv[o + half] = v1;
 }
 
 template <int D>
@@ -295,8 +336,13 @@ int launch_bwd(const BwdParams &p, cudaStream_t st) {
     const int rows = p.B * p.S * p.Hq;
     bwd_delta_kernel<<<(rows + 3) / 4, 128, 0, st>>>(p, D);
     NIMLLM_CHECK_LAUNCH("attn_prefill_bwd delta");
-    bwd_dkdv_kernel<D><<<dim3(n_tiles, p.Hkv, p.B), kThreads, smem, st>>>(p);
+    bwd_dkdv_kernel<D><<<dim3(n_tiles, p.dk_part ? p.Hq : p.Hkv, p.B), kThreads, smem, st>>>(p);
     NIMLLM_CHECK_LAUNCH("attn_prefill_bwd dk dv");
+    if (p.dk_part) {
+        const int64_t n = (int64_t)p.B * p.S * p.Hkv * (D / 2);
+        bwd_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p, D);
+        NIMLLM_CHECK_LAUNCH("attn_prefill_bwd reduce");
+    }
     bwd_dq_kernel<D><<<dim3(n_tiles, p.Hq, p.B), kThreads, smem, st>>>(p);
     NIMLLM_CHECK_LAUNCH("attn_prefill_bwd dq");
     return NIMLLM_OK;
@@ -309,9 +355,12 @@ using namespace nimllm;
 
 extern "C" {
 
-size_t nimllm_attn_prefill_bwd_workspace_bytes(int batch, int seq_len, int n_head) {
-    if (batch <= 0 || seq_len <= 0 || n_head <= 0) return 0;
-    return (size_t)batch * seq_len * n_head * sizeof(float);
+// delta [B, Hq, S], then (for grouped heads) per-query-head partial dk and dv: 2 * [G][B*S][Hkv*D]
+// = 2 * B*S*Hq*D floats
+size_t nimllm_attn_prefill_bwd_workspace_bytes(int batch, int seq_len, int n_head, int head_dim) {
+    if (batch <= 0 || seq_len <= 0 || n_head <= 0 || head_dim <= 0) return 0;
+    size_t delta = ((size_t)batch * seq_len * n_head * sizeof(float) + 255) / 256 * 256;
+    return delta + 2 * (size_t)batch * seq_len * n_head * head_dim * sizeof(float);
 }
 
 int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float *v, const float *out,
@@ -328,7 +377,7 @@ int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float 
     if ((rope_cos == nullptr) != (rope_sin == nullptr))
         return fail(NIMLLM_ERR_ARG, "attn_prefill_bwd: rope_cos and rope_sin go together");
     if (batch > 65535 || n_head > 65535) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill_bwd: batch or head count > 65535");
-    const size_t need = nimllm_attn_prefill_bwd_workspace_bytes(batch, seq_len, n_head);
+    const size_t need = nimllm_attn_prefill_bwd_workspace_bytes(batch, seq_len, n_head, head_dim);
     if (!workspace || workspace_bytes < need)
         return fail(NIMLLM_ERR_WORKSPACE, "attn_prefill_bwd: workspace %zu bytes, need %zu", workspace_bytes, need);
     if (((uintptr_t)q_rot | (uintptr_t)k_rot | (uintptr_t)v | (uintptr_t)dout) & 15)
@@ -336,6 +385,14 @@ int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float 
     BwdParams p;
     p.q = q_rot; p.k = k_rot; p.v = v; p.out = out; p.dout = dout; p.lse = lse;
     p.cos_tab = rope_cos; p.sin_tab = rope_sin; p.delta = (float *)workspace;
+    {
+        const size_t delta_bytes = ((size_t)batch * seq_len * n_head * sizeof(float) + 255) / 256 * 256;
+        const size_t part = (size_t)batch * seq_len * n_head * head_dim;      // floats per partial buffer
+        float *base = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + delta_bytes);
+        const bool grouped = n_head != n_kv_head;
+        p.dk_part = grouped ? base : nullptr;
+        p.dv_part = grouped ? base + part : nullptr;
+    }
     p.dq = dq; p.dk = dk; p.dv = dv;
     p.B = batch; p.S = seq_len; p.Hq = n_head; p.Hkv = n_kv_head; p.pos0 = pos0;
     p.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)head_dim);
