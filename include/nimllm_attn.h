@@ -120,6 +120,26 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
                        int n_kv_head, int head_dim, float scale, int chunk_rows,
                        void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- decode over a paged KV cache ---------------------------------------------------------
+ * No counterpart in the reference, whose cache is one buffer per (layer, KV head)
+ * (src/model.nim:729-739); this is the block-managed cache its chat loop's multi-turn reuse
+ * asks for (src/chat.nim:57,86-91).  K and V live in pages of page_rows rows:
+ *   k_pages, v_pages  bf16 [n_pages][n_kv_head][page_rows][head_dim]
+ *   page_table        device int32 [batch, max_pages]: rows r*page_rows .. of sequence b are in
+ *                     page page_table[b][r] (entries past the sequence's length are not read)
+ *   page_rows         a power of two >= 32
+ * Everything else as nimllm_attn_decode with chunk_rows = 0 (the library's own split of the
+ * batch); workspace of nimllm_attn_decode_workspace_bytes(batch, n_head, n_kv_head, head_dim,
+ * max_len, 0) bytes.  New rows are appended with nimllm_rope_append: give sequence b the offset
+ *   kv_off[b] = page * n_kv_head*page_rows*head_dim - (pos_b - pos_b % page_rows) * head_dim
+ * (page = page_table[b][pos_b / page_rows]), head_stride = page_rows*head_dim, cache_row0 = 0.
+ */
+int nimllm_attn_decode_paged(const void *q, int q_dtype, const void *k_pages, const void *v_pages,
+                             const int32_t *page_table, int max_pages, int page_rows,
+                             const int32_t *seq_len, int max_len, void *out, int out_dtype,
+                             float *partials_out, int batch, int n_head, int n_kv_head, int head_dim,
+                             float scale, void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- GQA decode for callers that cannot allocate ------------------------------------
  * No counterpart in the reference.  Same computation and arguments as nimllm_attn_decode,
  * minus the workspace: the chunk records of split sequences go to a fixed 8 MiB array that

@@ -34,6 +34,8 @@ PROTOTYPES = {
     "nimllm_attn_decode_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "nimllm_attn_decode": (i32, [vp, i32, vp, vp, i32, vp, i64, i64, vp, i32, vp, i32, vp, i32, i32, i32,
                                  i32, f32, i32, vp, sz, vp]),
+    "nimllm_attn_decode_paged": (i32, [vp, i32, vp, vp, vp, i32, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, f32,
+                                       vp, sz, vp]),
     "nimllm_attn_decode_noalloc_max_bytes": (sz, []),
     "nimllm_attn_decode_noalloc": (i32, [vp, i32, vp, vp, i32, vp, i64, i64, vp, i32, vp, i32, vp, i32, i32, i32,
                                          i32, f32, i32, vp]),

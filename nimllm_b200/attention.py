@@ -123,6 +123,33 @@ def decode_batch(q, k_cache, v_cache, *, n_head, n_kv_head, head_dim, max_len, s
     return (out, rec) if partials else out
 
 
+def decode_paged(q, k_pages, v_pages, page_table, *, n_head, n_kv_head, head_dim, max_len, seq_len=None, scale=None,
+                 out=None, out_dtype=torch.float32, partials=False):
+    """GQA decode over a paged bf16 cache: k_pages / v_pages [n_pages, Hkv, page_rows, D], page_table
+    int32 [B, max_pages].  Returns out [B, Hq*D] (and the (o, m, l) records when partials=True)."""
+    B = q.shape[0]
+    page_rows = k_pages.shape[2]
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    if out is None:
+        out = torch.empty((B, n_head * head_dim), dtype=out_dtype, device=q.device)
+    rec = torch.empty((B * n_head, head_dim + 4), dtype=torch.float32, device=q.device) if partials else None
+    need = lib().nimllm_attn_decode_workspace_bytes(B, n_head, n_kv_head, head_dim, max_len, 0)
+    ws = _arena.get(need, q.device)
+    check(lib().nimllm_attn_decode_paged(
+        _ptr(q), _code(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], page_rows,
+        _ptr(seq_len), max_len, _ptr(out), _code(out), _ptr(rec), B, n_head, n_kv_head, head_dim, scale,
+        _ptr(ws), need, _stream()))
+    return (out, rec) if partials else out
+
+
+def paged_append_offsets(page_table, pos, page_rows, n_kv_head, head_dim):
+    """kv_off for rope_append so that row pos_b of sequence b lands in its page (see the header):
+    int64 [B], computed on the device."""
+    pos = pos.to(torch.int64)
+    page = torch.gather(page_table.to(torch.int64), 1, (pos // page_rows).unsqueeze(1)).squeeze(1)
+    return page * (n_kv_head * page_rows * head_dim) - (pos - pos % page_rows) * head_dim
+
+
 def combine(parts, head_dim, out_dtype=torch.float32, partials=False):
     """Merge (o, m, l) records [n_parts, rows, D+4] -> out [rows, D]."""
     n_parts, rows, W = parts.shape

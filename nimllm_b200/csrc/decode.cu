@@ -41,6 +41,11 @@ struct DecodeParams {
     int max_len, chunk_rows;
     int B, Hq, Hkv, G;
     float scale_log2e;
+    // paged cache (balanced kernel only): page_table [B, max_pages] -> page index; a page is
+    // [Hkv][page_rows][D] elements of K (and of V), page_rows = 1 << page_shift
+    const int32_t *page_table;
+    int max_pages, page_shift;
+    int64_t page_stride;
 };
 
 __device__ __forceinline__ int seq_rows(const DecodeParams &p, int b) {
@@ -493,7 +498,7 @@ __host__ __device__ __forceinline__ void bal_pair_pieces(int64_t s, int nb, int6
     slot_first = bal_first_unit(w_first, T, wa) < s ? 1 : 0;
 }
 
-template <int D, int MINB, int BLK, int NW>
+template <int D, int MINB, int BLK, int NW, bool PAGED>
 __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(DecodeParams p, int *cum_out) {
     constexpr int U = 16 * BLK;
     constexpr int W = D + 4;
@@ -556,9 +561,32 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
 #pragma unroll
         for (int i = 0; i < D / 8; i++) { o[i][0] = 0.f; o[i][1] = 0.f; }
         float m = -INFINITY, l = 0.f;
+        // Paged cache: the lanes hold a window of 32 page-table entries of this sequence, so a
+        // 16-row block finds its page with a shuffle instead of a dependent global load; the
+        // window only moves forward (rows are walked in order).
+        int win_first = 0, pt_reg = 0;
+        auto load_window = [&](int first) {
+            win_first = first;
+            const int e = min(first + lane, p.max_pages - 1);
+            pt_reg = p.page_table[(int64_t)b * p.max_pages + e];
+        };
+        if (PAGED) load_window(r0 >> p.page_shift);
         auto load = [&](KvFrag<D> *f, int row) {
 #pragma unroll
-            for (int x = 0; x < BLK; x++) load_frag<D>(f[x], kb, vb, row + x * 16, r1 - 1, g, t);
+            for (int x = 0; x < BLK; x++) {
+                const int rr = row + x * 16;
+                if (PAGED) {
+                    const int pg = min(rr, r1 - 1) >> p.page_shift;      // a block past the end reads (clamped) rows of the last page
+                    if (pg >= win_first + 32) load_window(pg);
+                    const int entry = __shfl_sync(0xffffffffu, pt_reg, pg - win_first);
+                    const int64_t off = (int64_t)entry * p.page_stride + ((int64_t)kvh << p.page_shift) * D;
+                    const __nv_bfloat16 *kp = reinterpret_cast<const __nv_bfloat16 *>(p.k) + off;
+                    const __nv_bfloat16 *vp = reinterpret_cast<const __nv_bfloat16 *>(p.v) + off;
+                    load_frag<D>(f[x], kp, vp, rr - (pg << p.page_shift), (r1 - 1) - (pg << p.page_shift), g, t);
+                } else {
+                    load_frag<D>(f[x], kb, vb, rr, r1 - 1, g, t);
+                }
+            }
         };
         auto consume = [&](const KvFrag<D> *f, int row) {
 #pragma unroll
@@ -992,6 +1020,34 @@ void launch_generic(const DecodeParams &p, dim3 grid_base, cudaStream_t st) {
     }
 }
 
+// the balanced kernel and its merge launch; p.ws and the prefix array live in `workspace`
+int launch_balanced(DecodeParams &p, const int32_t *seq_len, void *out, int out_dtype, float *partials_out, int batch,
+                    int n_head, int n_kv_head, int head_dim, int max_len, void *workspace, cudaStream_t st) {
+    const BalShape bs = bal_shape(head_dim);
+    int *cum = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(workspace) +
+                                       bal_record_bytes(n_head, n_kv_head, head_dim));
+    const bool paged = p.page_table != nullptr;
+    if (head_dim == 64) {
+        if (paged) decode_mma_balanced_kernel<64, 1, 2, 8, true><<<bs.grid, 256, 0, st>>>(p, cum);
+        else decode_mma_balanced_kernel<64, 1, 2, 8, false><<<bs.grid, 256, 0, st>>>(p, cum);
+    } else {
+        if (paged) decode_mma_balanced_kernel<128, 2, 1, 4, true><<<bs.grid, 128, 0, st>>>(p, cum);
+        else decode_mma_balanced_kernel<128, 2, 1, 4, false><<<bs.grid, 128, 0, st>>>(p, cum);
+    }
+    NIMLLM_CHECK_LAUNCH("attn_decode balanced");
+    BalCombineParams c;
+    c.recs = p.ws; c.cum = cum; c.seq_len = seq_len; c.out = out; c.partials_out = partials_out;
+    c.out_dtype = out_dtype; c.B = batch; c.Hq = n_head; c.Hkv = n_kv_head; c.G = p.G; c.D = head_dim;
+    c.W = rec_stride(head_dim); c.U = bs.unit; c.max_len = max_len; c.wk = bs.grid * bs.nw;
+    // few pieces per pair (a large batch): one warp per row; many pieces: a CTA per row
+    if ((int64_t)c.wk < 4ll * batch * n_kv_head)
+        combine_balanced_warp_kernel<<<(batch * n_head + 3) / 4, 128, 0, st>>>(c);
+    else
+        combine_balanced_kernel<<<batch * n_head, 128, 0, st>>>(c);
+    NIMLLM_CHECK_LAUNCH("attn_decode balanced combine");
+    return NIMLLM_OK;
+}
+
 }  // namespace
 
 }  // namespace nimllm
@@ -1102,27 +1158,11 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
     p.q_dtype = q_dtype; p.out_dtype = out_dtype; p.max_len = max_len; p.chunk_rows = chunk_rows;
     p.B = batch; p.Hq = n_head; p.Hkv = n_kv_head; p.G = n_head / n_kv_head;
     p.scale_log2e = scale * kLog2e;
+    p.page_table = nullptr; p.max_pages = 0; p.page_shift = 0; p.page_stride = 0;
     cudaStream_t st = (cudaStream_t)stream;
 
-    if (balanced) {
-        const BalShape bs = bal_shape(head_dim);
-        int *cum = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(workspace) +
-                                           bal_record_bytes(n_head, n_kv_head, head_dim));
-        if (head_dim == 64) decode_mma_balanced_kernel<64, 1, 2, 8><<<bs.grid, 256, 0, st>>>(p, cum);
-        else decode_mma_balanced_kernel<128, 2, 1, 4><<<bs.grid, 128, 0, st>>>(p, cum);
-        NIMLLM_CHECK_LAUNCH("attn_decode balanced");
-        BalCombineParams c;
-        c.recs = p.ws; c.cum = cum; c.seq_len = seq_len; c.out = out; c.partials_out = partials_out;
-        c.out_dtype = out_dtype; c.B = batch; c.Hq = n_head; c.Hkv = n_kv_head; c.G = p.G; c.D = head_dim;
-        c.W = rec_stride(head_dim); c.U = bs.unit; c.max_len = max_len; c.wk = bs.grid * bs.nw;
-        // few pieces per pair (a large batch): one warp per row; many pieces: a CTA per row
-        if ((int64_t)c.wk < 4ll * batch * n_kv_head)
-            combine_balanced_warp_kernel<<<(batch * n_head + 3) / 4, 128, 0, st>>>(c);
-        else
-            combine_balanced_kernel<<<batch * n_head, 128, 0, st>>>(c);
-        NIMLLM_CHECK_LAUNCH("attn_decode balanced combine");
-        return NIMLLM_OK;
-    }
+    if (balanced) return launch_balanced(p, seq_len, out, out_dtype, partials_out, batch, n_head, n_kv_head, head_dim,
+                                         max_len, workspace, st);
 
     dim3 grid(max_chunks, n_kv_head, batch);
     if (g_force_kernel == 2 && !mma_ok)
@@ -1153,6 +1193,48 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
         NIMLLM_CHECK_LAUNCH("attn_decode combine");
     }
     return NIMLLM_OK;
+}
+
+// ---- decode over a paged cache --------------------------------------------------------------
+// K and V live in fixed-size pages [Hkv][page_rows][D] handed out by the caller's block manager
+// (the multi-turn KV reuse the reference's chat loop wants, src/chat.nim:57,86-91); sequence b's
+// rows r*page_rows .. are in page page_table[b][r].  Same balanced kernel, same records and merge.
+int nimllm_attn_decode_paged(const void *q, int q_dtype, const void *k_pages, const void *v_pages,
+                             const int32_t *page_table, int max_pages, int page_rows, const int32_t *seq_len,
+                             int max_len, void *out, int out_dtype, float *partials_out, int batch, int n_head,
+                             int n_kv_head, int head_dim, float scale, void *workspace, size_t workspace_bytes,
+                             void *stream) {
+    if (!q || !k_pages || !v_pages || !page_table || (!out && !partials_out))
+        return fail(NIMLLM_ERR_ARG, "attn_decode_paged: null q / pages / page table / output pointer");
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head != 0 || max_len <= 0 || max_pages <= 0)
+        return fail(NIMLLM_ERR_ARG, "attn_decode_paged: bad shape B=%d Hq=%d Hkv=%d max_len=%d max_pages=%d", batch,
+                    n_head, n_kv_head, max_len, max_pages);
+    if (!dtype_ok(q_dtype) || !dtype_ok(out_dtype)) return fail(NIMLLM_ERR_ARG, "attn_decode_paged: unknown dtype");
+    if (head_dim != 64 && head_dim != 128)
+        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode_paged: head_dim %d (64 and 128 are built)", head_dim);
+    if (n_head / n_kv_head > 8) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode_paged: Hq/Hkv > 8");
+    int shift = 0;
+    while ((1 << shift) < page_rows) shift++;
+    if (page_rows < 32 || (1 << shift) != page_rows)
+        return fail(NIMLLM_ERR_ARG, "attn_decode_paged: page_rows %d must be a power of two >= 32", page_rows);
+    if ((int64_t)max_pages * page_rows < max_len)
+        return fail(NIMLLM_ERR_ARG, "attn_decode_paged: %d pages of %d rows cannot hold max_len %d", max_pages, page_rows, max_len);
+    const size_t need = bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, seq_len != nullptr);
+    if (need == 0) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode_paged: batch %d is outside what the balanced kernel takes", batch);
+    if (!workspace || workspace_bytes < need)
+        return fail(NIMLLM_ERR_WORKSPACE, "attn_decode_paged: workspace %zu bytes, need %zu", workspace_bytes, need);
+    if ((((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) || ((uintptr_t)workspace & 15))
+        return fail(NIMLLM_ERR_ARG, "attn_decode_paged: pages and workspace must be 16-byte aligned");
+    DecodeParams p;
+    p.q = q; p.k = k_pages; p.v = v_pages; p.kv_off = nullptr; p.seq_stride = 0; p.head_stride = 0;
+    p.seq_len = seq_len; p.out = out; p.partials_out = partials_out; p.ws = (float *)workspace;
+    p.q_dtype = q_dtype; p.out_dtype = out_dtype; p.max_len = max_len; p.chunk_rows = 0;
+    p.B = batch; p.Hq = n_head; p.Hkv = n_kv_head; p.G = n_head / n_kv_head;
+    p.scale_log2e = scale * kLog2e;
+    p.page_table = page_table; p.max_pages = max_pages; p.page_shift = shift;
+    p.page_stride = (int64_t)n_kv_head * page_rows * head_dim;
+    return launch_balanced(p, seq_len, out, out_dtype, partials_out, batch, n_head, n_kv_head, head_dim, max_len,
+                           workspace, (cudaStream_t)stream);
 }
 
 // ---- decode without a caller-provided workspace ------------------------------------------

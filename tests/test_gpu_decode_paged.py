@@ -1,0 +1,107 @@
+"""GPU parity of the paged-cache decode: the same sequences stored contiguously and scattered over
+randomly assigned pages must give bit-identical results (same kernel arithmetic, only the
+addresses differ), and both match the float64 ground truth; appends through the page table land
+in the right rows."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import host
+from nimllm_b200 import _lib, attention as A
+from oracle import oracle as O
+from util import TOL_BF16, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _paged_copy(kc, vc, lens, page_rows, gen):
+    """kc, vc [B, Hkv, cap, D] -> pages [n_pages, Hkv, page_rows, D] in shuffled order + table."""
+    B, Hkv, cap, D = kc.shape
+    per_seq = [int((L + page_rows - 1) // page_rows) for L in lens]
+    max_pages = max(max(per_seq), 1)
+    n_pages = sum(per_seq) + 3                                  # a few pages stay unused
+    order = torch.randperm(n_pages, generator=gen).tolist()
+    kp = torch.full((n_pages, Hkv, page_rows, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    vp = torch.full_like(kp, float("nan"))
+    table = torch.full((B, max_pages), -1, dtype=torch.int32)
+    nxt = 0
+    for b in range(B):
+        for pg in range(per_seq[b]):
+            idx = order[nxt]; nxt += 1
+            table[b, pg] = idx
+            r0 = pg * page_rows
+            r1 = min(r0 + page_rows, cap)
+            kp[idx, :, :r1 - r0] = kc[b, :, r0:r1]
+            vp[idx, :, :r1 - r0] = vc[b, :, r0:r1]
+    table[table < 0] = 0                                        # unread entries must still be valid indices
+    return kp, vp, table.cuda()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(9, 3, 64), (32, 8, 128), (8, 1, 128), (4, 4, 64)])
+@pytest.mark.parametrize("page_rows", [32, 256])
+def test_paged_equals_contiguous_and_ground_truth(Hq, Hkv, D, page_rows):
+    lens = np.array([1, 31, 32, 33, 255, 256, 257, 1000, 0, 4096, 5, 2049], np.int32)
+    B, cap = len(lens), 4096
+    g = torch.Generator(device="cuda").manual_seed(31 + page_rows + D)
+    kc = torch.randn(B, Hkv, cap, D, generator=g, device="cuda").bfloat16()
+    vc = torch.randn(B, Hkv, cap, D, generator=g, device="cuda").bfloat16()
+    q = torch.randn(B, Hq * D, generator=g, device="cuda").bfloat16()
+    sl = torch.from_numpy(lens).cuda()
+    geom = dict(n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=cap, seq_len=sl)
+    _lib.lib().nimllm_attn_debug_force_decode_kernel(3)
+    try:
+        flat, flat_rec = A.decode_batch(q, kc, vc, seq_stride=Hkv * cap * D, head_stride=cap * D, partials=True, **geom)
+    finally:
+        _lib.lib().nimllm_attn_debug_force_decode_kernel(0)
+    kp, vp, table = _paged_copy(kc, vc, lens, page_rows, torch.Generator().manual_seed(5))
+    paged, paged_rec = A.decode_paged(q, kp, vp, table, partials=True, **geom)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(paged), host(flat))
+    np.testing.assert_array_equal(host(paged_rec)[:, :D + 2], host(flat_rec)[:, :D + 2])
+    assert np.isfinite(host(paged)).all()                      # no NaN page was touched
+    bits = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16).reshape(-1)
+    ref = O.decode_batch(host(q), bits(kc), bits(vc), np.arange(B, dtype=np.int64) * Hkv * cap * D,
+                         np.full(B, cap * D, np.int64), lens, Hq, Hkv, D, 1 / np.sqrt(D), acc64=True)
+    assert_close(host(paged), ref, TOL_BF16, "paged decode vs fp64 ground truth")
+
+
+def test_paged_append_then_decode():
+    """A new token per sequence goes through rope_append with page-derived offsets, then the
+    paged decode attends it: equal to doing the same on a contiguous cache."""
+    Hq, Hkv, D, page_rows, cap = 9, 3, 64, 64, 512
+    lens = np.array([63, 64, 65, 200, 0, 511], np.int32)        # rows already cached; the new token is row lens[b]
+    B = len(lens)
+    g = torch.Generator(device="cuda").manual_seed(77)
+    kc = torch.randn(B, Hkv, cap, D, generator=g, device="cuda").bfloat16()
+    vc = torch.randn(B, Hkv, cap, D, generator=g, device="cuda").bfloat16()
+    for b in range(B):                                          # rows at and past the length are not history
+        kc[b, :, lens[b]:] = 0; vc[b, :, lens[b]:] = 0
+    kp, vp, table = _paged_copy(kc, vc, lens + 1, page_rows, torch.Generator().manual_seed(9))
+    kp = torch.nan_to_num(kp); vp = torch.nan_to_num(vp)
+    cos, sin = A.rope_tables(cap, D, 10000.0)
+    pos = torch.from_numpy(lens).cuda()
+    acts = [torch.randn(B, 1, n * D, generator=g, device="cuda") for n in (Hq, Hkv, Hkv)]
+    q1, k1, v1 = (a.clone() for a in acts)
+    A.rope_append(q1, k1, v1, cos, sin, n_head=Hq, n_kv_head=Hkv, head_dim=D, seq_pos=pos, k_cache=kc, v_cache=vc,
+                  seq_stride=Hkv * cap * D, head_stride=cap * D, max_seq=cap)
+    flat = A.decode_batch(q1.view(B, Hq * D), kc, vc, n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=cap, seq_len=pos + 1,
+                          seq_stride=Hkv * cap * D, head_stride=cap * D)
+    q2, k2, v2 = (a.clone() for a in acts)
+    off = A.paged_append_offsets(table, pos, page_rows, Hkv, D)
+    A.rope_append(q2, k2, v2, cos, sin, n_head=Hq, n_kv_head=Hkv, head_dim=D, seq_pos=pos, k_cache=kp, v_cache=vp,
+                  kv_off=off, head_stride=page_rows * D, max_seq=2 ** 30)
+    paged = A.decode_paged(q2.view(B, Hq * D), kp, vp, table, n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=cap,
+                           seq_len=pos + 1)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(paged), host(flat))
+
+
+def test_paged_argument_checks():
+    z = torch.zeros(2, 2 * 64, dtype=torch.bfloat16, device="cuda")
+    pages = torch.zeros(4, 1, 48, 64, dtype=torch.bfloat16, device="cuda")          # 48 rows: not a power of two
+    table = torch.zeros(2, 2, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="page_rows"):
+        A.decode_paged(z, pages, pages, table, n_head=2, n_kv_head=1, head_dim=64, max_len=64)
+    pages = torch.zeros(4, 1, 64, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="cannot hold"):
+        A.decode_paged(z, pages, pages, table, n_head=2, n_kv_head=1, head_dim=64, max_len=1000)
