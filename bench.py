@@ -241,10 +241,29 @@ def run_decode(args, dist, name):
                 xch = None
 
     turn = [0]
+    paged = None
+    if args.page_rows and not sharded:
+        # every replica of the cache re-stored as a pool of pages in random order + one page table
+        P = args.page_rows
+        n_seq_pages = cap // P
+        perm = torch.randperm(B * n_seq_pages, device="cuda")
+        table = torch.empty(B * n_seq_pages, dtype=torch.int32, device="cuda")
+        table[perm] = torch.arange(B * n_seq_pages, dtype=torch.int32, device="cuda")   # page j of the flat order lives at table[j]
+        table = table.view(B, n_seq_pages)
+
+        def to_pages(t):
+            flat = t.view(B, Hkv, n_seq_pages, P, D).permute(0, 2, 1, 3, 4).reshape(B * n_seq_pages, Hkv, P, D)
+            pool = torch.empty_like(flat)
+            pool[table.view(-1).long()] = flat
+            return pool
+        paged = [(to_pages(k_), to_pages(v_)) for k_, v_ in zip(w["kcs"], w["vcs"])]
+        pgeom = dict(n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=max_len, seq_len=seq_len, scale=w["scale"])
 
     def step():
         i = turn[0] = (turn[0] + 1) % len(w["kcs"])
-        if not sharded:
+        if paged is not None:
+            A.decode_paged(w["q"], paged[i][0], paged[i][1], table, out=out, **pgeom)
+        elif not sharded:
             A.decode_batch(w["q"], w["kcs"][i], w["vcs"][i], out=out, **geom)
         elif xch is not None:
             # records go straight into every peer's buffer (NVLink stores + flags), then a bounded
@@ -354,6 +373,8 @@ def run_decode(args, dist, name):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": sampler.summary(),
     }
+    if paged is not None:
+        line["config"]["kv_layout"] = f"pages of {args.page_rows} rows in random order (nimllm_attn_decode_paged); e2e leg uses the contiguous cache"
     if xch is not None:
         line["config"]["peer_exchange_ok"] = xch.ok()
         dist.barrier()
@@ -564,6 +585,8 @@ def main():
     ap.add_argument("--chunk-rows", type=int, default=0)
     ap.add_argument("--prefill-variant", type=int, default=0, choices=[0, 1, 2],
                     help="c4: 0 library default, 1 one CTA per 256 query rows, 2 CTA pairs (tcgen05 cta_group::2)")
+    ap.add_argument("--page-rows", type=int, default=0,
+                    help="c3 / c5 on one GPU: store the cache in shuffled pages of this many rows and time the paged decode")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="c5 on several GPUs: how the shards' partial records meet (peer stores or NCCL all-gather)")
     ap.add_argument("--shape", default="", help="override: c5 -> B,Hq,Hkv,D,L ; c4 -> B,S,Hq,Hkv (profiling only)")
