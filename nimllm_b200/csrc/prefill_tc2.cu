@@ -287,7 +287,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(p_ready_bar);
+                if (lane == 0) { if (rank == 0) mbar_arrive(&sm.p_ready[w]); else mbar_arrive_cluster(p_ready_bar); }
                 continue;
             }
             const bool masked = (j == diag);
@@ -367,7 +367,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(p_ready_bar);
+            if (lane == 0) { if (rank == 0) mbar_arrive(&sm.p_ready[w]); else mbar_arrive_cluster(p_ready_bar); }
         }
 
         if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_full[w], 0, abort_flag));

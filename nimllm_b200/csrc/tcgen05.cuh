@@ -160,8 +160,12 @@ __device__ __forceinline__ uint32_t map_to_cta(const void *p, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
     return r;
 }
+// Arrival on a barrier that may live in the pair's other CTA.  Default (CTA-scope release)
+// semantics: what is handed over is TMEM / async-proxy state ordered by the tcgen05 fences around
+// the barrier, not generic-proxy global memory; a cluster-scope release here was measured to cost
+// several hundred cycles per hand-over.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
