@@ -1,18 +1,22 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path on synthetic data of the named shapes.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c5|c4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload all|c3|c5|c4|c3p] [--impl reference]
 
 One JSON line on stdout (rank 0).  A step is one pass of the hot path over one batch:
 
-  c3 (default)  batched GQA decode, 256 ragged sequences (L ~ U[512, 4096]), 9 q / 3 kv heads,
+  c3            batched GQA decode, 256 ragged sequences (L ~ U[512, 4096]), 9 q / 3 kv heads,
                 D = 64, bf16 KV cache.  Metric: KV GB/s (HBM roofline).  With N GPUs every rank
                 holds its own 256 sequences (weak scaling, no collective on the data path).
+  c3p           the same ONE batch of 256 sequences partitioned over the N GPUs by greedy
+                longest-first on the KV rows (strong scaling, no collective).
   c5            long-context decode, 8 x 131072 rows, 32 q / 8 kv heads, D = 128, bf16; the KV
-                sequence is sharded over the ranks and the (o, m, l) partials are gathered with
-                NCCL and merged (strong scaling).
+                sequence is sharded over the ranks and the (o, m, l) partials are exchanged
+                (peer stores or an NCCL all-gather) and merged (strong scaling).
   c4            causal prefill 4 x 8192, 32 q / 8 kv heads, D = 128, bf16 (tensor roofline); KV
                 heads are split over the ranks, no collective (strong scaling).
+  all (default) the c3 line is the headline; the c4, c5 and c3p measurements of the same run
+                are attached to it under "also" (each with its own value, roofline and clocks).
 
 `value` is timed with CUDA events on the launching stream with inputs resident in HBM;
 `e2e` is the same metric through the host-facing call: every step copies that step's
@@ -38,10 +42,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SEEDS = {"c3": 20253, "c4": 20254, "c5": 20255}
-SHAPE_OVERRIDE = None   # set by --shape; the default shapes are the configurations of BASELINE.json
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, taken from the
-# ncu summaries under profiles/ (None until a capture exists for that workload)
-NCU_TRAFFIC_BYTES = {"c3": 462484992 + 5016320, "c5": 4295632725 + 2294528, "c4": 1860400000 + 226800000}
+SHAPE_OVERRIDE = None   # set by --shape (profiling only); the defaults are the named benchmark shapes
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu
+# capture of that kernel on this workload (a constant: re-capture after changing the kernel)
+NCU_TRAFFIC_BYTES = {"c3": 462484992 + 5016320, "c3p": 462484992 + 5016320, "c5": 4295632725 + 2294528,
+                     "c4": 1860400000 + 226800000}
+WORKLOAD_TEXT = {
+    "c3": "C3 batched GQA decode: 256 ragged sequences per GPU, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
+    "c3p": "C3 batched GQA decode: one batch of 256 ragged sequences partitioned over the GPUs, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
+    "c5": "C5 long-context decode: 8 x 131072 rows, 32q/8kv heads, D=128, bf16 KV, KV sequence sharded over the GPUs",
+}
 
 
 def log(*a):
@@ -177,14 +187,29 @@ def timed_steps(torch, step, steps, warmup, flush=None, dist=None):
 
 
 # ------------------------------------------------------------------------------- c3 / c5
+def c3_lengths(rank):
+    """The 256 sequence lengths of the c3 batch of `rank` (rank 0's batch is THE batch of c3p)."""
+    return np.random.Generator(np.random.Philox(key=SEEDS["c3"] + 1000 * rank)).integers(512, 4097, 256).astype(np.int32)
+
+
 def decode_workload(name, rank, world, device="cuda"):
-    """Shapes and seeded synthetic data of the two decode configurations, built on `device`."""
+    """Shapes and seeded synthetic data of the decode configurations, built on `device`."""
     import torch
     gen = torch.Generator(device=device)
-    if name == "c3":
-        B, Hq, Hkv, D, cap = 256, 9, 3, 64, 4096
-        gen.manual_seed(SEEDS[name] + 1000 * rank)
-        lens = np.random.Generator(np.random.Philox(key=SEEDS[name] + 1000 * rank)).integers(512, 4097, B).astype(np.int32)
+    if name in ("c3", "c3p"):
+        Hq, Hkv, D, cap = 9, 3, 64, 4096
+        if name == "c3":
+            gen.manual_seed(SEEDS[name] + 1000 * rank)
+            lens = c3_lengths(rank)
+        else:
+            # ONE batch of 256 sequences; this rank holds the sequences the greedy longest-first
+            # partition by KV rows gives it (nimllm_b200.sharding.partition_sequences)
+            from nimllm_b200 import sharding
+            all_lens = c3_lengths(0)
+            mine = sharding.partition_sequences(all_lens, world)[rank]
+            lens = all_lens[mine]
+            gen.manual_seed(SEEDS["c3"] + 77 + rank)
+        B = len(lens)
         rows = cap
     else:
         B, Hq, Hkv, D, L = 8, 32, 8, 128, 131072
@@ -199,22 +224,62 @@ def decode_workload(name, rank, world, device="cuda"):
     for t in (kc, vc):              # fill in slices: randn in fp32 then round, without a 2x fp32 copy
         for b in range(B):
             t[b] = torch.randn(Hkv, cap, D, generator=gen, device=device).bfloat16()
-    # c3 moves 453 MB per step, 3.6x the 126 MB L2: the timed loop rotates over `copies` replicas
-    # of the cache so that a step never finds lines of its own data left by the step before
-    # (1.36 GB are touched between two uses of a replica).  No flush kernel is used: a flush that
-    # WRITES leaves L2 full of dirty lines whose write-back is charged to the next step.
-    copies = 3 if name == "c3" and device != "cpu" else 1
-    kcs = [kc] + [kc.clone() for _ in range(copies - 1)]
-    vcs = [vc] + [vc.clone() for _ in range(copies - 1)]
-    qgen = torch.Generator(device=device).manual_seed(SEEDS[name] + 7)   # q is the same on every rank of c5
-    q = torch.randn(B, Hq * D, generator=qgen if name == "c5" else gen, device=device).bfloat16()
     kv_bytes = int(lens.astype(np.int64).sum()) * 2 * Hkv * D * 2
     qo_bytes = B * Hq * D * (2 + 4)
+    # c3 moves 453 MB per step, 3.6x the 126 MB L2: the timed loop rotates over `copies` replicas
+    # of the cache so that a step never finds lines of its own data left by the step before
+    # (>= 1.2 GB are touched between two uses of a replica; a partition of the batch is smaller, so
+    # it gets more replicas).  No flush kernel is used: a flush that WRITES leaves L2 full of dirty
+    # lines whose write-back is charged to the next step.
+    copies = 1
+    if name in ("c3", "c3p") and device != "cpu":
+        copies = max(3, int(math.ceil(1.2e9 / max(kv_bytes, 1))))
+    kcs = [kc] + [kc.clone() for _ in range(copies - 1)]
+    vcs = [vc] + [vc.clone() for _ in range(copies - 1)]
+    qgen = torch.Generator(device=device).manual_seed(SEEDS[name if name != "c3p" else "c3"] + 7)   # q is the same on every rank of c5
+    q = torch.randn(B, Hq * D, generator=qgen if name == "c5" else gen, device=device).bfloat16()
     return dict(B=B, Hq=Hq, Hkv=Hkv, D=D, cap=cap, lens=lens, kc=kc, vc=vc, kcs=kcs, vcs=vcs, q=q, rows=rows,
-                bytes=kv_bytes + qo_bytes, scale=1.0 / math.sqrt(D))
+                bytes=kv_bytes + qo_bytes, scale=1.0 / math.sqrt(D), copies=copies)
 
 
-def run_decode(args, dist, name):
+def sustained_loop(torch, step, ms_per_step, dist, seconds=2.0, unit_steps=1, capture=True):
+    """The same step launched back to back for about `seconds` of device time (captured as a CUDA
+    graph of `unit_steps` steps so that the host's launch rate is not what is measured), timed
+    with one pair of events; returns (ms per step, steps) as the max over ranks."""
+    n_units = max(2, int(math.ceil(seconds * 1e3 / max(ms_per_step, 1e-3) / unit_steps)))
+    n_units = min(n_units, 200000)
+    try:
+        if not capture:
+            raise RuntimeError("already a graph")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(unit_steps):
+                step()
+        run = g.replay
+    except Exception as e:
+        if capture:  # pragma: no cover
+            log(f"sustained loop: graph capture failed ({e}); launching eagerly")
+        def run():
+            for _ in range(unit_steps):
+                step()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    a.record()
+    for _ in range(n_units):
+        run()
+    b.record()
+    dist.barrier()
+    ms = dist.max(a.elapsed_time(b)) / (n_units * unit_steps)
+    return ms, n_units * unit_steps
+
+
+def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
     import torch
     from nimllm_b200 import attention as A
     from nimllm_b200 import _lib
@@ -268,17 +333,17 @@ def run_decode(args, dist, name):
         elif xch is not None:
             # records go straight into every peer's buffer (NVLink stores + flags), then a bounded
             # wait and the merge: no collective library on the data path
-            _, rec = A.decode_batch(w["q"], w["kc"], w["vc"], out=out, partials=True, **geom)
-            xch.combine(rec, merged)
+            xch.decode_combine(w["q"], w["kc"], w["vc"], merged, **geom)
         else:
             _, rec = A.decode_batch(w["q"], w["kc"], w["vc"], out=out, partials=True, **geom)
             dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
             A.combine(gathered, D)
 
     graphed = False
+    eager_step = step
     if sharded:
-        # the sharded step is three dependent launches (decode, NCCL all-gather of 133 KB, merge);
-        # replaying them as one CUDA graph takes the host's launch latency off the critical path
+        # the sharded step is a few dependent launches; replaying them as one CUDA graph takes the
+        # host's launch latency off the critical path
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -290,7 +355,7 @@ def run_decode(args, dist, name):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 step()
-            eager_step, step = step, graph.replay
+            step = graph.replay
             graphed = True
         except Exception as e:  # pragma: no cover
             log(f"CUDA graph capture of the sharded step failed ({e}); timing eager launches")
@@ -298,104 +363,127 @@ def run_decode(args, dist, name):
     sampler = ClockSampler(dist.local)
     with sampler:
         ms = timed_steps(torch, step, args.steps, args.warmup, flush, dist)
+        # sustained: about two seconds of back-to-back steps (one rotation over the replicas per graph)
+        sus_ms, sus_steps = sustained_loop(torch, eager_step if not graphed else step, sum(ms) / len(ms), dist,
+                                           seconds=args.sustain, unit_steps=1 if graphed else len(w["kcs"]),
+                                           capture=not graphed) \
+            if args.sustain > 0 and (not sharded or graphed) else (None, 0)
     t_local = sum(ms) / 1e3
     t_max = dist.max(t_local)
     total_bytes = dist.sum(float(w["bytes"])) if not sharded else float(w["bytes"]) * dist.world
     value = total_bytes / t_max * args.steps / 1e9
+    best_ms = dist.max(min(ms))
 
-    # ---- end to end through the host-facing call: H2D activations, RoPE + append + decode, D2H
     E, Ekv = Hq * D, Hkv * D
-    # the step's activations q | k | v sit back to back in one pinned buffer: one host-to-device copy
-    hin = torch.randn(B * (E + 2 * Ekv)).pin_memory()
-    hout = torch.empty(B, E).pin_memory()
-    din = torch.empty(B * (E + 2 * Ekv), device="cuda")
-    dq, dk, dv = din[:B * E].view(B, E), din[B * E:B * (E + Ekv)].view(B, Ekv), din[B * (E + Ekv):].view(B, Ekv)
-    # the new token overwrites the last attended row, so the batch keeps its lengths from step to
-    # step; in c5 that is global row 131071, which only the last KV-sequence shard stores
-    if name == "c5":
-        cos, sin = A.rope_tables(131072, D, 500000.0)
-        seq_pos = torch.full((B,), 131071, dtype=torch.int32, device="cuda")
-        row0 = dist.rank * w["rows"]
-    else:
-        cos, sin = A.rope_tables(max_len + 1, D, 10000.0)
-        seq_pos = (seq_len - 1).to(torch.int32)
-        row0 = 0
-
-    def e2e_step():
-        i = turn[0] = (turn[0] + 1) % len(w["kcs"])
-        kci, vci = w["kcs"][i], w["vcs"][i]
-        din.copy_(hin, non_blocking=True)
-        A.rope_append(dq.view(B, 1, E), dk.view(B, 1, Ekv), dv.view(B, 1, Ekv), cos, sin, n_head=Hq, n_kv_head=Hkv,
-                      head_dim=D, seq_pos=seq_pos, k_cache=kci, v_cache=vci, seq_stride=Hkv * cap * D,
-                      head_stride=cap * D, cache_row0=row0, max_seq=cap)
-        if not sharded:
-            A.decode_batch(dq, kci, vci, out=out, **geom)
-            hout.copy_(out, non_blocking=True)
-        elif xch is not None:
-            _, rec = A.decode_batch(dq, w["kc"], w["vc"], out=out, partials=True, **geom)
-            hout.copy_(xch.combine(rec, merged).view(B, E), non_blocking=True)
+    e2e = None
+    if with_e2e:
+        # ---- end to end through the host-facing call: H2D activations, RoPE + append + decode, D2H
+        # the step's activations q | k | v sit back to back in one pinned buffer: one host-to-device copy
+        hin = torch.randn(B * (E + 2 * Ekv)).pin_memory()
+        hout = torch.empty(B, E).pin_memory()
+        din = torch.empty(B * (E + 2 * Ekv), device="cuda")
+        dq, dk, dv = din[:B * E].view(B, E), din[B * E:B * (E + Ekv)].view(B, Ekv), din[B * (E + Ekv):].view(B, Ekv)
+        # the new token overwrites the last attended row, so the batch keeps its lengths from step to
+        # step; in c5 that is global row 131071, which only the last KV-sequence shard stores
+        if name == "c5":
+            cos, sin = A.rope_tables(w["rows"] * dist.world, D, 500000.0)
+            seq_pos = torch.full((B,), w["rows"] * dist.world - 1, dtype=torch.int32, device="cuda")
+            row0 = dist.rank * w["rows"]
         else:
-            _, rec = A.decode_batch(dq, w["kc"], w["vc"], out=out, partials=True, **geom)
-            dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
-            hout.copy_(A.combine(gathered, D).view(B, E), non_blocking=True)
+            cos, sin = A.rope_tables(max_len + 1, D, 10000.0)
+            seq_pos = (seq_len - 1).to(torch.int32)
+            row0 = 0
 
-    e2e_ms = timed_steps(torch, e2e_step, args.steps, args.warmup, flush, dist)
-    e2e_t = dist.max(sum(e2e_ms) / 1e3)
-    e2e_value = total_bytes / e2e_t * args.steps / 1e9
-    # restore nothing: the overwritten rows stay valid bf16 data
+        def e2e_step():
+            i = turn[0] = (turn[0] + 1) % len(w["kcs"])
+            kci, vci = w["kcs"][i], w["vcs"][i]
+            din.copy_(hin, non_blocking=True)
+            A.rope_append(dq.view(B, 1, E), dk.view(B, 1, Ekv), dv.view(B, 1, Ekv), cos, sin, n_head=Hq, n_kv_head=Hkv,
+                          head_dim=D, seq_pos=seq_pos, k_cache=kci, v_cache=vci, seq_stride=Hkv * cap * D,
+                          head_stride=cap * D, cache_row0=row0, max_seq=cap)
+            if not sharded:
+                A.decode_batch(dq, kci, vci, out=out, **geom)
+                hout.copy_(out, non_blocking=True)
+            elif xch is not None:
+                hout.copy_(xch.decode_combine(dq, w["kc"], w["vc"], merged, **geom).view(B, E), non_blocking=True)
+            else:
+                _, rec = A.decode_batch(dq, w["kc"], w["vc"], out=out, partials=True, **geom)
+                dist.dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
+                hout.copy_(A.combine(gathered, D).view(B, E), non_blocking=True)
+
+        e2e_ms = timed_steps(torch, e2e_step, args.steps, args.warmup, flush, dist)
+        e2e_t = dist.max(sum(e2e_ms) / 1e3)
+        e2e = {"value": round(total_bytes / e2e_t * args.steps / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": B * (E + 2 * Ekv) * 4, "d2h_bytes_per_step": B * E * 4,
+               "ms_per_step": round(e2e_t / args.steps * 1e3, 5)}
+        # restore nothing: the overwritten rows stay valid bf16 data
 
     pk = peaks()
-    launches_per_step = 1 + (1 if lib_needs_combine(_lib, B, Hq, Hkv, D, max_len, args.chunk_rows) else 0) + (1 if sharded else 0)
+    needs_merge = lib_needs_combine(_lib, B, Hq, Hkv, D, max_len, args.chunk_rows)
+    launches_per_step = 1 + (1 if needs_merge else 0) + (1 if sharded else 0)
     per_rank_ms = sum(ms) / len(ms)
     achieved = float(w["bytes"]) / (per_rank_ms / 1e3) / 1e9
+    if sharded:
+        parallelism = ("kv-sequence shards, (o,m,l) records stored into the peers' buffers over NVLink by the local merge "
+                       "kernel + flags + merge" if xch is not None else
+                       "kv-sequence shards + NCCL all-gather of (o,m,l) + merge") + \
+                      (", step replayed as a CUDA graph" if graphed else "")
+    elif name == "c3p":
+        parallelism = f"one batch of 256 sequences split over {dist.world} GPU(s) by greedy longest-first on KV rows, no collective"
+    else:
+        parallelism = f"independent sequences x{dist.world}, no collective"
+    n_tokens = {"c3": B * dist.world, "c3p": 256, "c5": B}[name]
     line = {
         "metric": "decode_attn_kv_gbps", "value": round(value, 2), "unit": "GB/s", "n_gpus": dist.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_max / args.steps * 1e3, 5),
-        "higher_is_better": True, "scaling": "strong" if name == "c5" else "weak", "vs_baseline": None,
+        "ms_best_step": round(best_ms, 5),
+        "higher_is_better": True, "scaling": "weak" if name == "c3" else "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": {"c3": "C3 batched GQA decode: 256 ragged sequences per GPU, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
-                                "c5": "C5 long-context decode: 8 x 131072 rows, 32q/8kv heads, D=128, bf16 KV, KV sequence sharded over the GPUs"}[name],
+        "config": {"workload": WORKLOAD_TEXT[name],
                    "batch_per_gpu": B, "kv_rows_total": int(w["lens"].astype(np.int64).sum()),
-                   "parallelism": (("kv-sequence shards, (o,m,l) records stored into the peers' buffers over NVLink + flags + merge"
-                                    if xch is not None else "kv-sequence shards + NCCL all-gather of (o,m,l) + merge") +
-                                   (", step replayed as a CUDA graph" if graphed else "") if sharded else
-                                   f"independent sequences x{dist.world}, no collective"),
-                   "l2": ("inputs larger than L2: the timed loop rotates over 3 replicas of the 453 MB batch"
-                          if name == "c3" else "inputs larger than L2: 4.3 GB (or its shard) streamed once per step") +
+                   "parallelism": parallelism,
+                   "l2": (f"inputs larger than L2: the timed loop rotates over {w['copies']} replicas of this GPU's batch"
+                          if name != "c5" else "inputs larger than L2: 4.3 GB (or its shard) streamed once per step") +
                          "; no flush kernel (a writing flush leaves dirty lines whose write-back lands in the next step)",
-                   "tokens_per_s": round(B * (1 if name == "c5" else dist.world) / (t_max / args.steps), 1)},
+                   "tokens_per_s": round(n_tokens / (t_max / args.steps), 1)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": pk["hbm"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm"], 4), "traffic": NCU_TRAFFIC_BYTES[name],
+                     "frac": round(achieved / pk["hbm"], 4),
+                     "traffic": NCU_TRAFFIC_BYTES[name] if dist.world == 1 else None,
                      "peak_source": pk["source"], "algorithmic_bytes_per_step": int(w["bytes"]),
-                     "kernel": "decode_mma_balanced_kernel + its merge launch per step, CUDA events on the launching stream; traffic of the decode kernel from profiles/decode_mma_c3.md"},
-        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": B * (E + 2 * Ekv) * 4,
-                "d2h_bytes_per_step": B * E * 4, "ms_per_step": round(e2e_t / args.steps * 1e3, 5)},
+                     "kernel": "decode_mma_balanced_kernel + its merge launch per step (this GPU's share), CUDA events on "
+                               "the launching stream; traffic = dram bytes of the decode kernel from one ncu capture of this workload on one GPU"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": sampler.summary(),
     }
+    if sus_ms is not None:
+        line["sustained"] = {"ms_per_step": round(sus_ms, 5), "steps": sus_steps,
+                             "value": round(total_bytes / (sus_ms / 1e3) / 1e9, 2), "unit": "GB/s",
+                             "frac": round(float(w["bytes"]) / (sus_ms / 1e3) / 1e9 / pk["hbm"], 4),
+                             "how": "back-to-back steps for about two seconds, replayed as a CUDA graph, one event pair"}
+    if e2e is not None:
+        line["e2e"] = e2e
     if paged is not None:
         line["config"]["kv_layout"] = f"pages of {args.page_rows} rows in random order (nimllm_attn_decode_paged); e2e leg uses the contiguous cache"
     if xch is not None:
         line["config"]["peer_exchange_ok"] = xch.ok()
         dist.barrier()
         xch.close()
-    if dist.rank == 0 and dist.world == 1:
+    if with_cpu and dist.rank == 0 and dist.world == 1:
         line["cpu_baseline"] = cpu_baseline_decode(w, reps=3)
     return line
 
 
 # ------------------------------------------------------------------------------------ c4
-def run_prefill(args, dist):
+def run_prefill(args, dist, with_e2e=True, with_cpu=True):
     """C4: causal prefill 4 x 8192, 32 q / 8 kv heads, D = 128, bf16, RoPE base 500000.  The
     KV heads (with their query heads) are split over the ranks; no collective."""
     import torch
     from nimllm_b200 import attention as A
-    if getattr(args, "prefill_variant", 0):
-        from nimllm_b200 import _lib as _l
-        _l.lib().nimllm_attn_debug_prefill_variant(args.prefill_variant)
     B, S, Hq, Hkv, D = 4, 8192, 32, 8, 128
-    if SHAPE_OVERRIDE:                                  # --shape B,S,Hq,Hkv: small case for ncu captures
+    if SHAPE_OVERRIDE:                                  # --shape B,S,Hq,Hkv[,D]: small case for ncu captures
         B, S, Hq, Hkv = SHAPE_OVERRIDE[:4]
+        if len(SHAPE_OVERRIDE) > 4:
+            D = SHAPE_OVERRIDE[4]
     if Hkv % dist.world:
         raise SystemExit("c4 splits 8 KV heads: --gpus must divide 8")
     hq, hkv = Hq // dist.world, Hkv // dist.world
@@ -417,44 +505,55 @@ def run_prefill(args, dist):
     sampler = ClockSampler(dist.local)
     with sampler:
         ms = timed_steps(torch, step, args.steps, args.warmup, flush, dist)
+        sus_ms, sus_steps = sustained_loop(torch, step, sum(ms) / len(ms), dist, seconds=args.sustain, capture=False) \
+            if args.sustain > 0 else (None, 0)
     t_max = dist.max(sum(ms) / 1e3)
+    best_ms = dist.max(min(ms))
     value = flops_rank * dist.world * args.steps / t_max / 1e12
-
-    # end to end: pinned host q/k/v -> device, attention, result back to pinned host
-    hq_, hk_, hv_ = (torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v))
-    hq_.copy_(q); hk_.copy_(k); hv_.copy_(v)
-    hout = torch.empty(q.shape, dtype=q.dtype).pin_memory()
-
-    def e2e_step():
-        q.copy_(hq_, non_blocking=True); k.copy_(hk_, non_blocking=True); v.copy_(hv_, non_blocking=True)
-        out = A.attn_forward(q, k, v, cos, sin, n_head=hq, n_kv_head=hkv, head_dim=D, save_cache=False, scale=scale)
-        hout.copy_(out, non_blocking=True)
-
-    e_steps = max(3, min(args.steps, 5))
-    e2e_ms = timed_steps(torch, e2e_step, e_steps, 3, flush, dist)
-    e2e_t = dist.max(sum(e2e_ms) / 1e3)
     pk = peaks()
     achieved = flops_rank / (sum(ms) / len(ms) / 1e3) / 1e12
+    full = (B, S, Hq, Hkv, D) == (4, 8192, 32, 8, 128)
     line = {
         "metric": "prefill_attn_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": dist.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_max / args.steps * 1e3, 4),
+        "ms_best_step": round(best_ms, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"C4 causal prefill: {B} x {S} tokens, {Hq}q/{Hkv}kv heads, D=128, bf16, RoPE base 500000",
+        "config": {"workload": f"C4 causal prefill: {B} x {S} tokens, {Hq}q/{Hkv}kv heads, D={D}, bf16, RoPE base 500000",
                    "parallelism": f"KV heads split over {dist.world} GPU(s), no collective",
                    "l2": "inputs larger than L2 (0.8 GB of q, k, v, out per step); no flush kernel",
                    "tokens_per_s": round(B * S / (t_max / args.steps), 1)},
         "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": pk["bf16"], "unit": "TFLOP/s",
                      "frac": round(achieved / pk["bf16"], 4), "frac_of_sustained": round(achieved / pk["bf16_sustained"], 4),
-                     "traffic": NCU_TRAFFIC_BYTES["c4"], "peak_source": pk["source"],
+                     "traffic": NCU_TRAFFIC_BYTES["c4"] if (full and dist.world == 1) else None, "peak_source": pk["source"],
                      "algorithmic_flops_per_step": flops_rank,
-                     "kernel": "prefill_tc_kernel (+ rope_append_kernel pre-pass on K) per step; traffic from profiles/prefill_tc_c4.md"},
-        "e2e": {"value": round(flops_rank * dist.world * e_steps / e2e_t / 1e12, 2), "unit": "TFLOP/s",
-                "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": q.numel() * 2,
-                "ms_per_step": round(e2e_t / e_steps * 1e3, 4), "steps": e_steps},
+                     "kernel": "prefill_tc_kernel (+ rope_append_kernel pre-pass on K) per step, CUDA events on the launching "
+                               "stream; traffic = dram bytes of the prefill kernel from one ncu launch list of this workload"},
         "gpu_launches": 2 * args.steps,
         "clocks": sampler.summary(),
     }
-    if dist.rank == 0 and dist.world == 1:
+    if sus_ms is not None:
+        line["sustained"] = {"ms_per_step": round(sus_ms, 4), "steps": sus_steps,
+                             "value": round(flops_rank * dist.world / (sus_ms / 1e3) / 1e12, 2), "unit": "TFLOP/s",
+                             "frac_of_sustained_peak": round(flops_rank / (sus_ms / 1e3) / 1e12 / pk["bf16_sustained"], 4),
+                             "how": "back-to-back steps for about two seconds, one event pair"}
+    if with_e2e:
+        # end to end: pinned host q/k/v -> device, attention, result back to pinned host
+        hq_, hk_, hv_ = (torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v))
+        hq_.copy_(q); hk_.copy_(k); hv_.copy_(v)
+        hout = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+
+        def e2e_step():
+            q.copy_(hq_, non_blocking=True); k.copy_(hk_, non_blocking=True); v.copy_(hv_, non_blocking=True)
+            out = A.attn_forward(q, k, v, cos, sin, n_head=hq, n_kv_head=hkv, head_dim=D, save_cache=False, scale=scale)
+            hout.copy_(out, non_blocking=True)
+
+        e_steps = max(3, min(args.steps, 5))
+        e2e_ms = timed_steps(torch, e2e_step, e_steps, 3, flush, dist)
+        e2e_t = dist.max(sum(e2e_ms) / 1e3)
+        line["e2e"] = {"value": round(flops_rank * dist.world * e_steps / e2e_t / 1e12, 2), "unit": "TFLOP/s",
+                       "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": q.numel() * 2,
+                       "ms_per_step": round(e2e_t / e_steps * 1e3, 4), "steps": e_steps}
+    if with_cpu and dist.rank == 0 and dist.world == 1 and S >= 4096 and hq >= 8 and D == 128:
         line["cpu_baseline"] = cpu_baseline_prefill(q, k, v, hq, hkv, D, scale)
     return line
 
@@ -514,7 +613,7 @@ def run_reference_decode(args, dist, name):
     from oracle import oracle as O
     O.lib().oracle_set_threads(os.cpu_count() or 1)      # torchrun exports OMP_NUM_THREADS=1
     if name != "c3":
-        return {"impl": "reference", "unavailable": "reference arm is implemented for the c3 workload"}
+        return {"impl": "reference", "unavailable": "reference arm is implemented for the c3 workload (the headline)"}
     w = decode_workload(name, 0, 1, "cuda" if torch.cuda.is_available() else "cpu")
     B, Hq, Hkv, D, cap = w["B"], w["Hq"], w["Hkv"], w["D"], w["cap"]
     kb = w["kc"].cpu().view(torch.int16).numpy().view(np.uint16).reshape(-1)
@@ -535,7 +634,7 @@ def run_reference_decode(args, dist, name):
         "n_gpus": dist.world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(t / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "C3 batched GQA decode: 256 ragged sequences, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
+        "config": {"workload": WORKLOAD_TEXT["c3"],
                    "note": "the reference has no CPU forward; this is the C restatement of its attention loop "
                            "(src/model.nim:822-840) with OpenMP over sequence x head; the numerator is the "
                            "workload's algorithmic bytes (bf16 KV), so ratios of values are ratios of speed"},
@@ -581,15 +680,14 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=["c3", "c5", "c4"])
+    ap.add_argument("--workload", default="all", choices=["all", "c3", "c3p", "c5", "c4"])
+    ap.add_argument("--sustain", type=float, default=2.0, help="seconds of the back-to-back sustained loop per workload (0: skip)")
     ap.add_argument("--chunk-rows", type=int, default=0)
-    ap.add_argument("--prefill-variant", type=int, default=0, choices=[0, 1, 2],
-                    help="c4: 0 library default, 1 one CTA per 256 query rows, 2 CTA pairs (tcgen05 cta_group::2)")
     ap.add_argument("--page-rows", type=int, default=0,
                     help="c3 / c5 on one GPU: store the cache in shuffled pages of this many rows and time the paged decode")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="c5 on several GPUs: how the shards' partial records meet (peer stores or NCCL all-gather)")
-    ap.add_argument("--shape", default="", help="override: c5 -> B,Hq,Hkv,D,L ; c4 -> B,S,Hq,Hkv (profiling only)")
+    ap.add_argument("--shape", default="", help="override: c5 -> B,Hq,Hkv,D,L ; c4 -> B,S,Hq,Hkv[,D] (profiling only)")
     args = ap.parse_args()
     global SHAPE_OVERRIDE
     if args.shape:
@@ -607,8 +705,8 @@ def main():
         if torch.cuda.is_available():
             torch.cuda.set_device(0)
         args.steps = min(args.steps, 20)       # each CPU step is a full batch: bound the run
-        args.warmup = min(args.warmup, 3)
-        line = run_reference_decode(args, _Solo, args.workload)
+        args.warmup = min(args.warmup, 10)
+        line = run_reference_decode(args, _Solo, "c3" if args.workload == "all" else args.workload)
         print(json.dumps(line), file=real_stdout, flush=True)
         return 0
 
@@ -618,10 +716,29 @@ def main():
     if not os.path.exists(_lib.LIB_PATH) and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         build.build()
     dist = Dist(args.gpus)
-    if args.workload in ("c3", "c5"):
+    solo = dist.world == 1
+    if args.workload in ("c3", "c3p", "c5"):
         line = run_decode(args, dist, args.workload)
-    else:
+    elif args.workload == "c4":
         line = run_prefill(args, dist)
+    else:
+        # headline: c3 exactly as `--workload c3` prints it; the other configurations of the same
+        # run ride along under "also" (end-to-end legs only on one GPU; the CPU baseline only for
+        # the headline)
+        line = run_decode(args, dist, "c3")
+        also = {}
+        for key, fn in (("c4", lambda: run_prefill(args, dist, with_e2e=solo, with_cpu=False) if 8 % dist.world == 0 else None),
+                        ("c5", lambda: run_decode(args, dist, "c5", with_e2e=solo, with_cpu=False)),
+                        ("c3_partitioned", lambda: run_decode(args, dist, "c3p", with_e2e=False, with_cpu=False))):
+            torch.cuda.empty_cache()
+            try:
+                rec = fn()
+            except Exception as e:      # a sub-record must never take the headline down with it
+                rec = {"error": f"{type(e).__name__}: {e}"[:300]}
+                log(f"also.{key} failed: {rec['error']}")
+            if rec is not None:
+                also[key] = rec
+        line["also"] = also
     if dist.rank == 0:
         print(json.dumps(line), file=real_stdout, flush=True)
     dist.close()

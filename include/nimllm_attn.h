@@ -130,15 +130,28 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
  *   page_rows         a power of two >= 32
  * Everything else as nimllm_attn_decode with chunk_rows = 0 (the library's own split of the
  * batch); workspace of nimllm_attn_decode_workspace_bytes(batch, n_head, n_kv_head, head_dim,
- * max_len, 0) bytes.  New rows are appended with nimllm_rope_append: give sequence b the offset
- *   kv_off[b] = page * n_kv_head*page_rows*head_dim - (pos_b - pos_b % page_rows) * head_dim
- * (page = page_table[b][pos_b / page_rows]), head_stride = page_rows*head_dim, cache_row0 = 0.
+ * max_len, 0) bytes.  New rows are appended with nimllm_rope_append_paged below.
  */
 int nimllm_attn_decode_paged(const void *q, int q_dtype, const void *k_pages, const void *v_pages,
                              const int32_t *page_table, int max_pages, int page_rows,
                              const int32_t *seq_len, int max_len, void *out, int out_dtype,
                              float *partials_out, int batch, int n_head, int n_kv_head, int head_dim,
                              float scale, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- fused RoPE + cast + append into a paged KV cache --------------------------------------
+ * No counterpart in the reference (see above).  nimllm_rope_append with the cache given as
+ * pages: the row at position p of sequence b goes to row p % page_rows of page
+ * page_table[b][p / page_rows], so an append of several tokens may cross page boundaries.
+ * Positions at or past max_pages * page_rows, table entries < 0 and pages >= n_pages (the size
+ * of the pool) are not stored -- nothing is ever written outside the pool.
+ *   k_pages, v_pages  cache_dtype [n_pages][n_kv_head][page_rows][head_dim]
+ *   page_rows         a power of two (>= 32 for nimllm_attn_decode_paged)
+ * q, k_new, v_new, the tables, seq_pos / pos0, write_back_k as in nimllm_rope_append. */
+int nimllm_rope_append_paged(void *q, int n_head, void *k_new, const void *v_new, int act_dtype,
+                             int write_back_k, const float *rope_cos, const float *rope_sin,
+                             const int32_t *seq_pos, int pos0, void *k_pages, void *v_pages, int cache_dtype,
+                             const int32_t *page_table, int max_pages, int page_rows, int n_pages, int batch,
+                             int n, int n_kv_head, int head_dim, void *stream);
 
 /* ---- GQA decode for callers that cannot allocate ------------------------------------
  * No counterpart in the reference.  Same computation and arguments as nimllm_attn_decode,
@@ -149,8 +162,14 @@ int nimllm_attn_decode_paged(const void *q, int q_dtype, const void *k_pages, co
  * (src/autograd.nim:16-65), so a decode step that arrives when the arena is exhausted, or a
  * caller that must not touch cudaMalloc because it synchronises the device, can still run.
  * The function itself never allocates or frees.
- *   - A call whose records do not fit (nimllm_attn_decode_workspace_bytes(...) larger than
- *     nimllm_attn_decode_noalloc_max_bytes()) is refused with NIMLLM_ERR_WORKSPACE.
+ *   - A call is refused with NIMLLM_ERR_WORKSPACE only when its records fit the array under
+ *     neither kernel.  With chunk_rows = 0, a bf16 cache and Hq/Hkv <= 8 the library's own split
+ *     of the batch keeps a fixed number of records that depends on the head shape alone
+ *     (about 2 MB at 9q/3kv heads of 64, 5 MB at 32q/8kv heads of 128, 10 MB -- too much -- at
+ *     Hq/Hkv = 8 with heads of 128).  If that does not fit, or chunk_rows > 0, the chunk grid
+ *     runs and needs ceil(max_len / chunk_rows) * batch * n_head * (head_dim + 4) * 4 bytes
+ *     (nothing when no sequence is split; with chunk_rows = 0 the library picks the chunk length).
+ *     nimllm_attn_decode_noalloc_max_bytes() is the size of the array (8 MiB).
  *   - The first call on each device looks the array's device address up
  *     (cudaGetSymbolAddress); make that first call outside any stream capture.
  *   - All calls on a device share the array, and it keeps what the last call left there
@@ -176,7 +195,7 @@ int nimllm_attn_combine(const float *parts, int n_parts, int rows, int head_dim,
  * No counterpart in the reference (single GPU).  One process per GPU of a box; every rank's
  * decode has produced records [rows, D+4] (partials_out above) for ITS rows of the KV sequence.
  * nimllm_attn_combine_peers stores them into every peer's exchange buffer over NVLink (plain
- * peer stores, then a per-rank flag), waits -- at most about a second, then *status_dev = 1 --
+ * peer stores, then a per-rank flag), waits -- up to the wait limit, then *status_dev = 1 --
  * for all peers' records, and merges them: the all-gather and the merge of
  * nimllm_attn_combine in two small launches with no collective library on the path.
  * Set-up: create a buffer per rank, pass every rank's 64-byte export handle to every other rank
@@ -186,10 +205,29 @@ typedef struct nimllm_peer_exchange nimllm_peer_exchange;
 nimllm_peer_exchange *nimllm_peer_exchange_create(int rank, int world, int rows_max, int head_dim);
 int nimllm_peer_exchange_export(nimllm_peer_exchange *x, void *handle_out_64_bytes);
 int nimllm_peer_exchange_import(nimllm_peer_exchange *x, int peer_rank, const void *handle_64_bytes);
+/* a peer that lives in the same process on the same device (several ranks driven by one process,
+ * tests on one GPU): its buffer is used directly, without a handle */
+int nimllm_peer_exchange_import_local(nimllm_peer_exchange *x, int peer_rank, nimllm_peer_exchange *peer);
 int nimllm_peer_exchange_ready(nimllm_peer_exchange *x);
+/* how long the wait for the peers' records may last before it gives up and sets *status_dev = 1
+ * (default 1000 ms); a rank that stopped calling leaves the others with that status, not a hang */
+int nimllm_peer_exchange_set_wait_limit(nimllm_peer_exchange *x, int milliseconds);
 void nimllm_peer_exchange_destroy(nimllm_peer_exchange *x);
 int nimllm_attn_combine_peers(nimllm_peer_exchange *x, const float *rec_local, int rows, void *out, int out_dtype,
                               int *status_dev, void *stream);
+
+/* The same exchange fused into the shard's decode (bf16 cache, Hq/Hkv <= 8, head_dim 64 or 128):
+ * nimllm_attn_decode_push runs this rank's decode over its rows of the KV sequence (arguments as
+ * nimllm_attn_decode with chunk_rows = 0) and its merge launch stores every finished record straight
+ * into every peer's buffer -- no separate copy of the records, no extra launch; nimllm_attn_wait_combine
+ * then waits (bounded) for all ranks' records of this call and merges them into out [batch*n_head, D].
+ * Every rank calls the pair once per step, in the same order; both launches may be captured in a graph. */
+size_t nimllm_attn_decode_push_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim, int max_len);
+int nimllm_attn_decode_push(nimllm_peer_exchange *x, const void *q, int q_dtype, const void *k_cache,
+                            const void *v_cache, const int64_t *kv_off, int64_t seq_stride, int64_t head_stride,
+                            const int32_t *seq_len, int max_len, int batch, int n_head, int n_kv_head, int head_dim,
+                            float scale, void *workspace, size_t workspace_bytes, void *stream);
+int nimllm_attn_wait_combine(nimllm_peer_exchange *x, int rows, void *out, int out_dtype, int *status_dev, void *stream);
 
 /* ---- causal prefill ----------------------------------------------------------------
  * Replaces the attention block of forward(), src/model.nim:469-475,494-508: RoPE on

@@ -31,6 +31,8 @@ PROTOTYPES = {
     "nimllm_kvcache_head_stride": (i64, [vp]),
     "nimllm_rope_append": (i32, [vp, i32, vp, vp, i32, i32, vp, vp, vp, i32, vp, vp, i32, vp, i64, i64,
                                  i32, i32, i32, i32, i32, i32, vp]),
+    "nimllm_rope_append_paged": (i32, [vp, i32, vp, vp, i32, i32, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32,
+                                       i32, i32, i32, i32, vp]),
     "nimllm_attn_decode_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "nimllm_attn_decode": (i32, [vp, i32, vp, vp, i32, vp, i64, i64, vp, i32, vp, i32, vp, i32, i32, i32,
                                  i32, f32, i32, vp, sz, vp]),
@@ -43,9 +45,14 @@ PROTOTYPES = {
     "nimllm_peer_exchange_create": (vp, [i32, i32, i32, i32]),
     "nimllm_peer_exchange_export": (i32, [vp, vp]),
     "nimllm_peer_exchange_import": (i32, [vp, i32, vp]),
+    "nimllm_peer_exchange_import_local": (i32, [vp, i32, vp]),
+    "nimllm_peer_exchange_set_wait_limit": (i32, [vp, i32]),
     "nimllm_peer_exchange_ready": (i32, [vp]),
     "nimllm_peer_exchange_destroy": (None, [vp]),
     "nimllm_attn_combine_peers": (i32, [vp, vp, i32, vp, i32, vp, vp]),
+    "nimllm_attn_decode_push_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
+    "nimllm_attn_decode_push": (i32, [vp, vp, i32, vp, vp, vp, i64, i64, vp, i32, i32, i32, i32, i32, f32, vp, sz, vp]),
+    "nimllm_attn_wait_combine": (i32, [vp, i32, vp, i32, vp, vp]),
     "nimllm_attn_prefill_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "nimllm_attn_prefill": (i32, [vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, i32,
                                   vp, vp, i32, vp, i64, i64, i32, vp, vp, sz, vp]),
@@ -65,7 +72,6 @@ PROTOTYPES = {
 # testing hooks exported by the library but not part of include/nimllm_attn.h
 _EXTRA = {
     "nimllm_attn_debug_force_decode_kernel": (None, [i32]),
-    "nimllm_attn_debug_prefill_dump": (None, [vp]),
     "nimllm_attn_debug_balanced_plan": (i32, [vp, i32, i32, i32, i32, vp, i32, vp]),
     "nimllm_attn_debug_prefill_variant": (None, [i32]),
 }

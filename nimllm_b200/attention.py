@@ -142,12 +142,15 @@ def decode_paged(q, k_pages, v_pages, page_table, *, n_head, n_kv_head, head_dim
     return (out, rec) if partials else out
 
 
-def paged_append_offsets(page_table, pos, page_rows, n_kv_head, head_dim):
-    """kv_off for rope_append so that row pos_b of sequence b lands in its page (see the header):
-    int64 [B], computed on the device."""
-    pos = pos.to(torch.int64)
-    page = torch.gather(page_table.to(torch.int64), 1, (pos // page_rows).unsqueeze(1)).squeeze(1)
-    return page * (n_kv_head * page_rows * head_dim) - (pos - pos % page_rows) * head_dim
+def rope_append_paged(q, k_new, v_new, cos, sin, k_pages, v_pages, page_table, *, n_head, n_kv_head, head_dim,
+                      pos0=0, seq_pos=None, write_back_k=True):
+    """rope_append into a paged cache: k_pages / v_pages [n_pages, Hkv, page_rows, D], page_table int32
+    [B, max_pages]; every new row finds its own page, so n > 1 may cross page boundaries."""
+    B, n = k_new.shape[0], k_new.shape[1]
+    check(lib().nimllm_rope_append_paged(
+        _ptr(q), n_head, _ptr(k_new), _ptr(v_new), _code(k_new), int(write_back_k), _ptr(cos), _ptr(sin),
+        _ptr(seq_pos), pos0, _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(page_table), page_table.shape[1],
+        k_pages.shape[2], k_pages.shape[0], B, n, n_kv_head, head_dim, _stream()))
 
 
 def combine(parts, head_dim, out_dtype=torch.float32, partials=False):

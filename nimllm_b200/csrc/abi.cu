@@ -137,10 +137,40 @@ int nimllm_rope_append(void *q, int n_head, void *k_new, const void *v_new, int 
     if (n_kv_head > 0 && (!k_new || !v_new)) return fail(NIMLLM_ERR_ARG, "rope_append: null k_new / v_new");
     if (k_cache && (head_stride % 8 != 0 || seq_stride % 8 != 0 || max_seq <= 0))
         return fail(NIMLLM_ERR_ARG, "rope_append: cache strides must be multiples of 8 elements and max_seq > 0");
+    if (((uintptr_t)q | (uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)k_cache | (uintptr_t)v_cache |
+         (uintptr_t)rope_cos | (uintptr_t)rope_sin) & 15)
+        return fail(NIMLLM_ERR_ARG, "rope_append: q, k_new, v_new, the caches and the tables must be 16-byte aligned");
     if (batch == 0 || n == 0) return NIMLLM_OK;
     return launch_rope_append(q, q ? n_head : 0, k_new, v_new, act_dtype, write_back_k, rope_cos, rope_sin,
                               seq_pos, pos0, k_cache, v_cache, cache_dtype, kv_off, seq_stride, head_stride,
                               cache_row0, max_seq, batch, n, n_kv_head, head_dim, (cudaStream_t)stream);
+}
+
+// Same launch with the page of every new row resolved inside the kernel.
+int nimllm_rope_append_paged(void *q, int n_head, void *k_new, const void *v_new, int act_dtype,
+                             int write_back_k, const float *rope_cos, const float *rope_sin,
+                             const int32_t *seq_pos, int pos0, void *k_pages, void *v_pages, int cache_dtype,
+                             const int32_t *page_table, int max_pages, int page_rows, int n_pages, int batch,
+                             int n, int n_kv_head, int head_dim, void *stream) {
+    if (batch < 0 || n < 0 || n_kv_head <= 0 || n_head < 0 || head_dim <= 0 || head_dim % 8 != 0)
+        return fail(NIMLLM_ERR_ARG, "rope_append_paged: bad shape B=%d n=%d Hq=%d Hkv=%d D=%d", batch, n, n_head,
+                    n_kv_head, head_dim);
+    if (!dtype_ok(act_dtype) || !dtype_ok(cache_dtype)) return fail(NIMLLM_ERR_ARG, "rope_append_paged: unknown dtype");
+    if ((rope_cos == nullptr) != (rope_sin == nullptr))
+        return fail(NIMLLM_ERR_ARG, "rope_append_paged: give both RoPE tables or neither");
+    if (!k_new || !v_new || !k_pages || !v_pages || !page_table)
+        return fail(NIMLLM_ERR_ARG, "rope_append_paged: null k_new / v_new / pages / page table");
+    int shift = 0;
+    while ((1 << shift) < page_rows) shift++;
+    if (page_rows < 1 || (1 << shift) != page_rows || max_pages <= 0 || n_pages <= 0)
+        return fail(NIMLLM_ERR_ARG, "rope_append_paged: page_rows %d must be a power of two, max_pages and n_pages > 0",
+                    page_rows);
+    if (((uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)q) & 15)
+        return fail(NIMLLM_ERR_ARG, "rope_append_paged: q, k_new, v_new and the pages must be 16-byte aligned");
+    if (batch == 0 || n == 0) return NIMLLM_OK;
+    return launch_rope_append(q, q ? n_head : 0, k_new, v_new, act_dtype, write_back_k, rope_cos, rope_sin, seq_pos,
+                              pos0, k_pages, v_pages, cache_dtype, nullptr, 0, 0, 0, 0, batch, n, n_kv_head, head_dim,
+                              (cudaStream_t)stream, page_table, max_pages, shift, n_pages);
 }
 
 size_t nimllm_attn_prefill_workspace_bytes(int batch, int seq_len, int n_head, int n_kv_head,
@@ -163,6 +193,8 @@ int nimllm_attn_prefill(void *q, void *k, const void *v, int dtype, const float 
     if ((rope_cos == nullptr) != (rope_sin == nullptr))
         return fail(NIMLLM_ERR_ARG, "attn_prefill: give both RoPE tables or neither");
     if (batch == 0 || seq_len == 0) return NIMLLM_OK;
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
+        return fail(NIMLLM_ERR_ARG, "attn_prefill: q, k, v, out must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
 
     if (dtype == NIMLLM_F32) {

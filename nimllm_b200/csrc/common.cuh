@@ -74,6 +74,50 @@ __device__ __forceinline__ void store_from_f32(void *base, int dtype, int64_t i,
     else reinterpret_cast<__nv_bfloat16 *>(base)[i] = __float2bfloat16_rn(x);
 }
 
+// ---- programmatic dependent launch: a kernel launched with the programmatic-serialization
+// attribute may start while its predecessor still runs; it must not touch the predecessor's
+// results before grid_dependency_wait().  launch_dependents() lets the successor's CTAs be
+// scheduled early.  Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- where a kernel stores finished (o, m, l) records for the other ranks of a KV-sequence-
+// sharded decode (peer.cu owns the buffers).  Buffer of a rank: 2 slots of [world][rows_max][W]
+// floats, then kPeerMaxWorld flag words, then {CTA ticket, call counter}.
+constexpr int kPeerMaxWorld = 16;
+struct PeerPush {
+    float *const *peers;     // device table: base of every rank's buffer (own entry included)
+    int rank, world, rows_max, W;
+    size_t slot_floats;      // world * rows_max * W
+};
+__device__ __forceinline__ unsigned int *peer_ctl(const PeerPush &px, int r) {
+    return reinterpret_cast<unsigned int *>(px.peers[r] + 2 * px.slot_floats);
+}
+// call counter of this launch; the counter lives in device memory and is advanced by the last
+// CTA of the pushing launch, so a captured CUDA graph can replay the step
+__device__ __forceinline__ unsigned int peer_push_epoch(const PeerPush &px) { return peer_ctl(px, px.rank)[kPeerMaxWorld + 1] + 1u; }
+// this rank's records in rank r's buffer (double-slotted by the counter's parity, so a fast
+// rank's next call cannot overwrite records a slow rank is still merging)
+__device__ __forceinline__ float *peer_push_slot(const PeerPush &px, int r, unsigned int epoch) {
+    return px.peers[r] + (size_t)(epoch & 1u) * px.slot_floats + (size_t)px.rank * px.rows_max * px.W;
+}
+// called by every thread of every CTA after its stores: the last CTA to get here advances the
+// counter and raises this rank's flag on every peer (plain stores + system-scope release)
+__device__ __forceinline__ void peer_push_publish(const PeerPush &px, unsigned int epoch) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int *ctl = peer_ctl(px, px.rank) + kPeerMaxWorld;
+        if (atomicAdd(&ctl[0], 1u) == gridDim.x - 1) {
+            ctl[0] = 0u;
+            ctl[1] = epoch;
+            __threadfence_system();
+            for (int r = 0; r < px.world; r++)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_ctl(px, r) + px.rank), "r"(epoch) : "memory");
+        }
+    }
+}
+
 inline size_t dtype_size(int dtype) { return dtype == NIMLLM_F32 ? 4 : 2; }
 inline bool dtype_ok(int dtype) { return dtype == NIMLLM_F32 || dtype == NIMLLM_BF16; }
 
@@ -85,7 +129,8 @@ int launch_rope_append(void *q, int Hq, void *k_new, const void *v_new, int act_
                        const int32_t *seq_pos, int pos0, void *k_cache, void *v_cache,
                        int cache_dtype, const int64_t *kv_off, int64_t seq_stride,
                        int64_t head_stride, int cache_row0, int max_seq, int B, int n, int Hkv,
-                       int D, cudaStream_t st);
+                       int D, cudaStream_t st, const int32_t *page_table = nullptr, int max_pages = 0,
+                       int page_shift = 0, int n_pages = 0);
 
 int launch_prefill_f32(const float *q, const float *k, const float *v, float *out, float *lse,
                        int B, int S, int Hq, int Hkv, int D, float scale, int causal,
@@ -104,4 +149,11 @@ int launch_prefill_tc2(void *q, const void *k, const void *v, void *out, float *
                        size_t workspace_bytes, cudaStream_t st);
 extern int g_prefill_variant;
 
+}  // namespace nimllm
+
+struct nimllm_peer_exchange;
+namespace nimllm {
+PeerPush peer_push_of(const nimllm_peer_exchange *x);
+int peer_rows_max(const nimllm_peer_exchange *x);
+int peer_head_dim(const nimllm_peer_exchange *x);
 }  // namespace nimllm

@@ -20,6 +20,8 @@
 //   decode_generic_kernel  fp32 or bf16 cache, fp32 FMA on the CUDA cores: the <= 1e-4
 //                          parity path for the reference's fp32 cache, and the fallback
 //                          for group sizes the mma kernel does not take.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace nimllm {
@@ -508,6 +510,9 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n_uniform = (p.max_len + U - 1) / U;
+    // the merge kernel that follows is a programmatic dependent: its CTAs may take their places
+    // now and wait there for this grid to finish, instead of being launched after it
+    launch_dependents();
 
     if (p.seq_len) {
         // exclusive prefix of the unit counts of the sequences (one KV head's worth)
@@ -662,6 +667,40 @@ struct BalCombineParams {
     float *partials_out;
     int out_dtype;
     int B, Hq, Hkv, G, D, W, U, max_len, wk;
+    // KV-sequence shards: every finished record also goes to this rank's slot in every peer's
+    // exchange buffer (plain stores over NVLink), and the last CTA raises the rank's flag there
+    int do_push;
+    PeerPush push;
+};
+
+// one finished record row -> the local outputs and, when pushing, every peer
+struct RowSink {
+    const BalCombineParams &c;
+    int row;
+    unsigned int epoch;
+    __device__ __forceinline__ void value(int d, float val) const {
+        if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, val);
+        if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = val;
+        if (c.do_push)
+            for (int r = 0; r < c.push.world; r++) peer_push_slot(c.push, r, epoch)[(int64_t)row * c.W + d] = val;
+    }
+    __device__ __forceinline__ void stats(float m, float l) const {
+        const float4 t = make_float4(m, l, 0.f, 0.f);
+        if (c.partials_out) *reinterpret_cast<float4 *>(c.partials_out + (int64_t)row * c.W + c.D) = t;
+        if (c.do_push)
+            for (int r = 0; r < c.push.world; r++)
+                *reinterpret_cast<float4 *>(peer_push_slot(c.push, r, epoch) + (int64_t)row * c.W + c.D) = t;
+    }
+    // a row the decode kernel finished by itself: only the peers still need it
+    __device__ __forceinline__ void forward(int tid, int nthreads) const {
+        if (!c.do_push) return;
+        const float4 *src = reinterpret_cast<const float4 *>(c.partials_out + (int64_t)row * c.W);
+        for (int i = tid; i < c.W / 4; i += nthreads) {
+            const float4 t = __ldcg(src + i);
+            for (int r = 0; r < c.push.world; r++)
+                reinterpret_cast<float4 *>(peer_push_slot(c.push, r, epoch) + (int64_t)row * c.W)[i] = t;
+        }
+    }
 };
 
 // What a merge thread needs to know about its output row (sequence, query head): which records
@@ -687,28 +726,20 @@ __device__ __forceinline__ const float *bal_rec(const BalCombineParams &c, const
     return c.recs + (((int64_t)(r.w_first + i) * 2 + (i == 0 ? r.slot_first : 0)) * c.G + r.g) * c.W;
 }
 // zeros (and an empty record) for a row of an empty sequence, written by `nthreads` threads
-__device__ __forceinline__ void bal_write_empty(const BalCombineParams &c, int row, int tid, int nthreads) {
-    for (int d = tid; d < c.D; d += nthreads) {
-        if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, 0.f);
-        if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = 0.f;
-    }
-    if (c.partials_out && tid == 0) {
-        float *o = c.partials_out + (int64_t)row * c.W;
-        o[c.D] = -INFINITY; o[c.D + 1] = 0.f; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
-    }
+__device__ __forceinline__ void bal_write_empty(const RowSink &sink, int tid, int nthreads) {
+    for (int d = tid; d < sink.c.D; d += nthreads) sink.value(d, 0.f);
+    if (tid == 0) sink.stats(-INFINITY, 0.f);
 }
 
 // Variant for batches of many pairs cut into few pieces (measured faster there than the
 // four-warp CTA per row below): one warp per output row; rows of empty sequences become zeros, rows
 // whose pair one warp covered are already final, the others merge the records of the
 // consecutive warps that hold their pieces.
-__global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombineParams c) {
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= c.B * c.Hq) return;
+__device__ __forceinline__ void combine_row_warp(const BalCombineParams &c, int row, int lane, unsigned int epoch) {
+    const RowSink sink{c, row, epoch};
     const BalRow br = bal_row(c, row);
-    if (br.n == 0) { bal_write_empty(c, row, lane, 32); return; }
-    if (br.n == 1) return;
+    if (br.n == 0) { bal_write_empty(sink, lane, 32); return; }
+    if (br.n == 1) { sink.forward(lane, 32); return; }
     const int n = br.n;
     auto rec_of = [&](int i) -> const float * { return bal_rec(c, br, i); };
     float M = -INFINITY, wsum = 0.f;
@@ -783,16 +814,16 @@ __global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombinePa
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         const int d = lane + 32 * j;
-        if (d < c.D) {
-            const float val = acc[j] * inv;
-            if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, val);
-            if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = val;
-        }
+        if (d < c.D) sink.value(d, acc[j] * inv);
     }
-    if (c.partials_out && lane == 0) {
-        float *o = c.partials_out + (int64_t)row * c.W;
-        o[c.D] = M; o[c.D + 1] = wsum; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
-    }
+    if (lane == 0) sink.stats(M, wsum);
+}
+__global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombineParams c) {
+    grid_dependency_wait();              // the decode kernel's records and prefix array are complete
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const unsigned int epoch = c.do_push ? peer_push_epoch(c.push) : 0u;
+    if (row < c.B * c.Hq) combine_row_warp(c, row, threadIdx.x & 31, epoch);
+    if (c.do_push) peer_push_publish(c.push, epoch);
 }
 
 // One CTA of four warps per output row (sequence, query head): rows of empty sequences become
@@ -800,14 +831,13 @@ __global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombinePa
 // consecutive warps that hold their pieces.  Warp k takes pieces k, k+4, ... and loads them
 // before the row maximum is known, so the usual row (up to 16 pieces) waits for memory once for
 // its indices and once for its records; the four partial sums meet in shared memory.
-__global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams c) {
-    __shared__ float s_acc[4][256];
-    __shared__ float s_w[4];
-    const int row = blockIdx.x;
+__device__ __forceinline__ void combine_row_cta(const BalCombineParams &c, int row, unsigned int epoch,
+                                                float (*s_acc)[256], float *s_w) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const BalRow br = bal_row(c, row);
-    if (br.n == 0) { bal_write_empty(c, row, threadIdx.x, 128); return; }
-    if (br.n == 1) return;
+    const RowSink sink{c, row, epoch};
+    const BalRow br = bal_row(c, row);                    // the same for every thread of the CTA
+    if (br.n == 0) { bal_write_empty(sink, threadIdx.x, 128); return; }
+    if (br.n == 1) { sink.forward(threadIdx.x, 128); return; }
     const int n = br.n;
     auto rec_of = [&](int i) -> const float * { return bal_rec(c, br, i); };
     float acc[8];
@@ -854,15 +884,17 @@ __global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams 
     __syncthreads();
     wsum = (s_w[0] + s_w[1]) + (s_w[2] + s_w[3]);
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-    for (int d = threadIdx.x; d < c.D; d += 128) {
-        const float val = ((s_acc[0][d] + s_acc[1][d]) + (s_acc[2][d] + s_acc[3][d])) * inv;
-        if (c.out) store_from_f32(c.out, c.out_dtype, (int64_t)row * c.D + d, val);
-        if (c.partials_out) c.partials_out[(int64_t)row * c.W + d] = val;
-    }
-    if (c.partials_out && threadIdx.x == 0) {
-        float *o = c.partials_out + (int64_t)row * c.W;
-        o[c.D] = M; o[c.D + 1] = wsum; o[c.D + 2] = 0.f; o[c.D + 3] = 0.f;
-    }
+    for (int d = threadIdx.x; d < c.D; d += 128)
+        sink.value(d, ((s_acc[0][d] + s_acc[1][d]) + (s_acc[2][d] + s_acc[3][d])) * inv);
+    if (threadIdx.x == 0) sink.stats(M, wsum);
+}
+__global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams c) {
+    __shared__ float s_acc[4][256];
+    __shared__ float s_w[4];
+    grid_dependency_wait();              // the decode kernel's records and prefix array are complete
+    const unsigned int epoch = c.do_push ? peer_push_epoch(c.push) : 0u;
+    combine_row_cta(c, blockIdx.x, epoch, s_acc, s_w);
+    if (c.do_push) peer_push_publish(c.push, epoch);
 }
 
 // ------------------------------------------------------------------ combine kernel
@@ -1022,7 +1054,8 @@ void launch_generic(const DecodeParams &p, dim3 grid_base, cudaStream_t st) {
 
 // the balanced kernel and its merge launch; p.ws and the prefix array live in `workspace`
 int launch_balanced(DecodeParams &p, const int32_t *seq_len, void *out, int out_dtype, float *partials_out, int batch,
-                    int n_head, int n_kv_head, int head_dim, int max_len, void *workspace, cudaStream_t st) {
+                    int n_head, int n_kv_head, int head_dim, int max_len, void *workspace, cudaStream_t st,
+                    const PeerPush *push = nullptr) {
     const BalShape bs = bal_shape(head_dim);
     int *cum = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(workspace) +
                                        bal_record_bytes(n_head, n_kv_head, head_dim));
@@ -1039,12 +1072,26 @@ int launch_balanced(DecodeParams &p, const int32_t *seq_len, void *out, int out_
     c.recs = p.ws; c.cum = cum; c.seq_len = seq_len; c.out = out; c.partials_out = partials_out;
     c.out_dtype = out_dtype; c.B = batch; c.Hq = n_head; c.Hkv = n_kv_head; c.G = p.G; c.D = head_dim;
     c.W = rec_stride(head_dim); c.U = bs.unit; c.max_len = max_len; c.wk = bs.grid * bs.nw;
-    // few pieces per pair (a large batch): one warp per row; many pieces: a CTA per row
-    if ((int64_t)c.wk < 4ll * batch * n_kv_head)
-        combine_balanced_warp_kernel<<<(batch * n_head + 3) / 4, 128, 0, st>>>(c);
-    else
-        combine_balanced_kernel<<<batch * n_head, 128, 0, st>>>(c);
-    NIMLLM_CHECK_LAUNCH("attn_decode balanced combine");
+    c.do_push = push ? 1 : 0;
+    if (push) c.push = *push; else c.push = PeerPush{nullptr, 0, 0, 0, 0, 0};
+    // The merge launch is a programmatic dependent of the decode kernel (its CTAs are placed while
+    // the decode still runs and wait for it on the device).  Few pieces per pair (a large batch):
+    // one warp per row; many pieces: a CTA per row.
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e;
+    if ((int64_t)c.wk < 4ll * batch * n_kv_head) {
+        cfg.gridDim = dim3((batch * n_head + 3) / 4);
+        e = cudaLaunchKernelEx(&cfg, combine_balanced_warp_kernel, c);
+    } else {
+        cfg.gridDim = dim3(batch * n_head);
+        e = cudaLaunchKernelEx(&cfg, combine_balanced_kernel, c);
+    }
+    if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_decode balanced combine: %s", cudaGetErrorString(e));
     return NIMLLM_OK;
 }
 
@@ -1237,6 +1284,51 @@ int nimllm_attn_decode_paged(const void *q, int q_dtype, const void *k_pages, co
                            workspace, (cudaStream_t)stream);
 }
 
+// ---- this rank's part of a KV-sequence-sharded decode ---------------------------------------
+// The shard decode with the exchange fused into its merge launch: the merge kernel holds every
+// finished (o, m, l) record in registers and stores it straight into every peer's exchange
+// buffer; its last CTA raises the rank's flag.  nimllm_attn_wait_combine finishes the step.
+size_t nimllm_attn_decode_push_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim, int max_len) {
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || max_len <= 0 || n_head % n_kv_head != 0) return 0;
+    const size_t bal = bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, true);
+    if (bal == 0) return 0;
+    // + the rows the decode kernel finishes by itself, kept where the merge kernel forwards them from
+    return (bal + 255) / 256 * 256 + (size_t)batch * n_head * rec_stride(head_dim) * sizeof(float);
+}
+
+int nimllm_attn_decode_push(nimllm_peer_exchange *x, const void *q, int q_dtype, const void *k_cache,
+                            const void *v_cache, const int64_t *kv_off, int64_t seq_stride, int64_t head_stride,
+                            const int32_t *seq_len, int max_len, int batch, int n_head, int n_kv_head, int head_dim,
+                            float scale, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!x || !q || !k_cache || !v_cache) return fail(NIMLLM_ERR_ARG, "attn_decode_push: null exchange / q / cache");
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head != 0 || max_len <= 0)
+        return fail(NIMLLM_ERR_ARG, "attn_decode_push: bad shape B=%d Hq=%d Hkv=%d max_len=%d", batch, n_head, n_kv_head, max_len);
+    if (!dtype_ok(q_dtype)) return fail(NIMLLM_ERR_ARG, "attn_decode_push: unknown dtype");
+    if (head_dim != peer_head_dim(x) || batch * n_head > peer_rows_max(x))
+        return fail(NIMLLM_ERR_ARG, "attn_decode_push: the exchange was created for head_dim %d and %d rows", peer_head_dim(x),
+                    peer_rows_max(x));
+    const size_t need = nimllm_attn_decode_push_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len);
+    if (need == 0)
+        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode_push: needs head_dim 64 or 128 and Hq/Hkv <= 8 (use nimllm_attn_decode "
+                                            "with partials_out and nimllm_attn_combine_peers otherwise)");
+    if (!workspace || workspace_bytes < need)
+        return fail(NIMLLM_ERR_WORKSPACE, "attn_decode_push: workspace %zu bytes, need %zu", workspace_bytes, need);
+    if ((((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) || ((uintptr_t)workspace & 255))
+        return fail(NIMLLM_ERR_ARG, "attn_decode_push: caches 16-byte, workspace 256-byte aligned");
+    const size_t bal = bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, true);
+    float *rows_done = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + (bal + 255) / 256 * 256);
+    DecodeParams p;
+    p.q = q; p.k = k_cache; p.v = v_cache; p.kv_off = kv_off; p.seq_stride = seq_stride; p.head_stride = head_stride;
+    p.seq_len = seq_len; p.out = nullptr; p.partials_out = rows_done; p.ws = (float *)workspace;
+    p.q_dtype = q_dtype; p.out_dtype = NIMLLM_F32; p.max_len = max_len; p.chunk_rows = 0;
+    p.B = batch; p.Hq = n_head; p.Hkv = n_kv_head; p.G = n_head / n_kv_head;
+    p.scale_log2e = scale * kLog2e;
+    p.page_table = nullptr; p.max_pages = 0; p.page_shift = 0; p.page_stride = 0;
+    const PeerPush px = peer_push_of(x);
+    return launch_balanced(p, seq_len, nullptr, NIMLLM_F32, rows_done, batch, n_head, n_kv_head, head_dim, max_len, workspace,
+                           (cudaStream_t)stream, &px);
+}
+
 // ---- decode without a caller-provided workspace ------------------------------------------
 // The chunk records of a split decode normally live in the caller's workspace.  This variant
 // keeps them in a fixed array inside the library instead, for callers that have nowhere to
@@ -1251,32 +1343,42 @@ int nimllm_attn_decode_noalloc(const void *q, int q_dtype, const void *k_cache, 
                                int64_t head_stride, const int32_t *seq_len, int max_len, void *out,
                                int out_dtype, float *partials_out, int batch, int n_head,
                                int n_kv_head, int head_dim, float scale, int chunk_rows, void *stream) {
+    // shapes first: the size arithmetic below must not run on nonsense
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head != 0 || max_len <= 0 || chunk_rows < 0 ||
+        (head_dim != 64 && head_dim != 128))
+        return fail(NIMLLM_ERR_ARG, "attn_decode_noalloc: bad shape B=%d Hq=%d Hkv=%d D=%d max_len=%d chunk_rows=%d",
+                    batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
     // In host code the array's name is only a handle; the device address has to be asked for,
-    // once per device, with that device current.  No lock: racing first calls would store the
-    // same address.
-    static void *scratch_ptr[64] = {nullptr};
+    // once per device, with that device current.  Racing first calls store the same address.
+    static std::atomic<void *> scratch_ptr[64];
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64)
         return fail(NIMLLM_ERR_CUDA, "attn_decode_noalloc: no usable current device (%s)", cudaGetErrorString(e));
-    if (!scratch_ptr[dev]) {
-        void *ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, g_builtin_scratch);
-        if (e != cudaSuccess || !ptr)
+    void *scratch = scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
+        e = cudaGetSymbolAddress(&scratch, g_builtin_scratch);
+        if (e != cudaSuccess || !scratch)
             return fail(NIMLLM_ERR_CUDA, "attn_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
                         cudaGetErrorString(e));
-        scratch_ptr[dev] = ptr;
+        scratch_ptr[dev].store(scratch, std::memory_order_release);
     }
-    // what the chunk grid needs; the balanced kernel is used when its records fit as well
-    const size_t need = split_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
-    if (need > kBuiltinScratchBytes)
+    // The call runs if the records of one of the two kernels fit: the library's own split of the
+    // batch (chunk_rows = 0, bf16 cache, Hq/Hkv <= 8) needs a fixed amount that depends on the
+    // head shape only; otherwise the chunk grid needs one record per (chunk, sequence, head).
+    // nimllm_attn_decode makes the same choice from the same two numbers.
+    const bool bal_possible = chunk_rows == 0 && cache_dtype == NIMLLM_BF16 && n_head / n_kv_head <= 8;
+    const size_t bal = bal_possible ? bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, seq_len != nullptr) : 0;
+    const size_t split = split_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
+    const bool bal_fits = bal > 0 && bal <= kBuiltinScratchBytes;
+    if (!bal_fits && split > kBuiltinScratchBytes)
         return fail(NIMLLM_ERR_WORKSPACE,
-                    "attn_decode_noalloc: this call needs %zu bytes of chunk records but the built-in scratch holds "
-                    "%zu; use nimllm_attn_decode with a workspace, or a larger chunk_rows",
-                    need, kBuiltinScratchBytes);
+                    "attn_decode_noalloc: this call needs %zu bytes of chunk records (%zu for the library's own split) "
+                    "but the built-in scratch holds %zu; use nimllm_attn_decode with a workspace, or a larger chunk_rows",
+                    split, bal, kBuiltinScratchBytes);
     return nimllm_attn_decode(q, q_dtype, k_cache, v_cache, cache_dtype, kv_off, seq_stride, head_stride, seq_len,
                               max_len, out, out_dtype, partials_out, batch, n_head, n_kv_head, head_dim, scale,
-                              chunk_rows, scratch_ptr[dev], kBuiltinScratchBytes, stream);
+                              chunk_rows, scratch, kBuiltinScratchBytes, stream);
 }
 
 int nimllm_attn_combine(const float *parts, int n_parts, int rows, int head_dim, int rec_stride_,

@@ -25,18 +25,12 @@ struct nimllm_peer_exchange {
     void *peer_base[16];         // mapped base of every rank's buffer (own entry = local)
     bool imported[16];
     float **peer_table_dev;      // device copy of peer_base
+    unsigned long long wait_limit_ns;   // how long wait_combine_kernel polls before it gives up
 };
 
 namespace nimllm {
 namespace {
 
-constexpr int kMaxWorld = 16;
-
-__host__ __device__ inline size_t flags_offset_floats(size_t slot_floats) { return 2 * slot_floats; }
-
-__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
     unsigned int v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -46,42 +40,32 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
 // records [rows, W] of this rank -> slot `rank` of every peer's buffer; the last CTA to finish
 // publishes the call counter in every peer's flag word for this rank
 //
-// The call counter lives in device memory (word kMaxWorld + 1 after the flags) and is advanced by
+// The call counter lives in device memory (word kPeerMaxWorld + 1 after the flags) and is advanced by
 // the push kernel itself, so a captured CUDA graph can replay the pair of launches.
-__global__ void __launch_bounds__(256) push_kernel(const float *__restrict__ rec, float *const *__restrict__ peers, int rank,
-                                                   int world, int rows, int rows_max, int W, size_t slot_floats) {
-    unsigned int *ctl = reinterpret_cast<unsigned int *>(peers[rank] + flags_offset_floats(slot_floats)) + kMaxWorld;
-    const unsigned int epoch = ctl[1] + 1u;        // stable until the last CTA of this launch writes it back
-    const int slot = (int)(epoch & 1u);
-    const int n4 = rows * W / 4;
+__global__ void __launch_bounds__(256) push_kernel(const float *__restrict__ rec, PeerPush px, int rows) {
+    const unsigned int epoch = peer_push_epoch(px);   // stable until the last CTA of this launch writes it back
+    const int n4 = rows * px.W / 4;
     const float4 *src = reinterpret_cast<const float4 *>(rec);
-    for (int r = 0; r < world; r++) {
-        float4 *dst = reinterpret_cast<float4 *>(peers[r] + (size_t)slot * slot_floats + (size_t)rank * rows_max * W);
+    for (int r = 0; r < px.world; r++) {
+        float4 *dst = reinterpret_cast<float4 *>(peer_push_slot(px, r, epoch));
         for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) dst[i] = src[i];
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        if (atomicAdd(&ctl[0], 1u) == gridDim.x - 1) {
-            ctl[0] = 0u;
-            ctl[1] = epoch;
-            __threadfence_system();
-            for (int r = 0; r < world; r++)
-                st_release_sys(reinterpret_cast<unsigned int *>(peers[r] + flags_offset_floats(slot_floats)) + rank, epoch);
-        }
-    }
+    peer_push_publish(px, epoch);
 }
 
 // one warp per output row: wait for every rank's flag, then log-sum-exp merge of the world
 // records of the row (same arithmetic as combine_kernel in decode.cu)
 __global__ void __launch_bounds__(128) wait_combine_kernel(const float *buf, int world, int rows, int rows_max,
                                                            int D, int W, size_t slot_floats, void *out, int out_dtype,
-                                                           int *status) {
+                                                           int *status, unsigned long long limit_ns) {
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    // launched as a programmatic dependent of the kernel that pushes: everything above is free to
+    // run early, the pusher's writes (the call counter below) are visible after this point
+    grid_dependency_wait();
     if (row >= rows) return;
-    const unsigned int *flags = reinterpret_cast<const unsigned int *>(buf + flags_offset_floats(slot_floats));
-    const unsigned int epoch = __ldcg(flags + kMaxWorld + 1);   // written by this rank's push kernel, which has completed
+    const unsigned int *flags = reinterpret_cast<const unsigned int *>(buf + 2 * slot_floats);
+    const unsigned int epoch = __ldcg(flags + kPeerMaxWorld + 1);   // written by this rank's push kernel, which has completed
     const int slot = (int)(epoch & 1u);
     bool ok = true;
     if (lane < world) {
@@ -95,7 +79,7 @@ __global__ void __launch_bounds__(128) wait_combine_kernel(const float *buf, int
                 unsigned long long now;
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
                 if (t0 == 0) t0 = now;
-                else if (now - t0 > 1000000000ull) { ok = false; break; }
+                else if (now - t0 > limit_ns) { ok = false; break; }
             }
         }
     }
@@ -143,22 +127,23 @@ using namespace nimllm;
 extern "C" {
 
 nimllm_peer_exchange *nimllm_peer_exchange_create(int rank, int world, int rows_max, int head_dim) {
-    if (rank < 0 || world < 1 || world > kMaxWorld || rank >= world || rows_max <= 0 || head_dim <= 0 || head_dim % 4) {
+    if (rank < 0 || world < 1 || world > kPeerMaxWorld || rank >= world || rows_max <= 0 || head_dim <= 0 || head_dim % 4) {
         set_error("peer_exchange_create: bad arguments");
         return nullptr;
     }
     nimllm_peer_exchange *x = new nimllm_peer_exchange();
     x->rank = rank; x->world = world; x->rows_max = rows_max; x->W = rec_stride(head_dim);
     x->slot_floats = (size_t)world * rows_max * x->W;
-    x->bytes = (2 * x->slot_floats + 2 * kMaxWorld) * sizeof(float);
+    x->bytes = (2 * x->slot_floats + 2 * kPeerMaxWorld) * sizeof(float);
     cudaGetDevice(&x->device);
     if (cudaMalloc((void **)&x->local, x->bytes) != cudaSuccess || cudaMemset(x->local, 0, x->bytes) != cudaSuccess ||
-        cudaMalloc((void **)&x->peer_table_dev, kMaxWorld * sizeof(float *)) != cudaSuccess) {
+        cudaMalloc((void **)&x->peer_table_dev, kPeerMaxWorld * sizeof(float *)) != cudaSuccess) {
         set_error("peer_exchange_create: cudaMalloc failed");
         delete x;
         return nullptr;
     }
-    for (int r = 0; r < kMaxWorld; r++) { x->peer_base[r] = nullptr; x->imported[r] = false; }
+    x->wait_limit_ns = 1000000000ull;
+    for (int r = 0; r < kPeerMaxWorld; r++) { x->peer_base[r] = nullptr; x->imported[r] = false; }
     x->peer_base[rank] = x->local;
     cudaDeviceSynchronize();
     return x;
@@ -189,12 +174,31 @@ int nimllm_peer_exchange_import(nimllm_peer_exchange *x, int peer_rank, const vo
     return NIMLLM_OK;
 }
 
+/* a peer that lives in THIS process on the same device (tests, or several ranks driven by one
+ * process): its buffer is used directly, no IPC handle */
+int nimllm_peer_exchange_import_local(nimllm_peer_exchange *x, int peer_rank, nimllm_peer_exchange *peer) {
+    if (!x || !peer || peer_rank < 0 || peer_rank >= x->world || peer->rank != peer_rank || peer->world != x->world ||
+        peer->rows_max != x->rows_max || peer->W != x->W)
+        return fail(NIMLLM_ERR_ARG, "peer_exchange_import_local: the two buffers do not describe the same exchange");
+    if (peer_rank == x->rank) return NIMLLM_OK;
+    x->peer_base[peer_rank] = peer->local;
+    x->imported[peer_rank] = false;           // nothing to close
+    return NIMLLM_OK;
+}
+
+/* how long a wait for the peers' records may last before it gives up (default 1000 ms) */
+int nimllm_peer_exchange_set_wait_limit(nimllm_peer_exchange *x, int milliseconds) {
+    if (!x || milliseconds <= 0) return fail(NIMLLM_ERR_ARG, "peer_exchange_set_wait_limit: bad argument");
+    x->wait_limit_ns = (unsigned long long)milliseconds * 1000000ull;
+    return NIMLLM_OK;
+}
+
 /* after every peer has been imported */
 int nimllm_peer_exchange_ready(nimllm_peer_exchange *x) {
     if (!x) return fail(NIMLLM_ERR_ARG, "peer_exchange_ready: null handle");
     for (int r = 0; r < x->world; r++)
         if (!x->peer_base[r]) return fail(NIMLLM_ERR_ARG, "peer_exchange_ready: rank %d was not imported", r);
-    cudaError_t e = cudaMemcpy(x->peer_table_dev, x->peer_base, kMaxWorld * sizeof(float *), cudaMemcpyHostToDevice);
+    cudaError_t e = cudaMemcpy(x->peer_table_dev, x->peer_base, kPeerMaxWorld * sizeof(float *), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "peer_exchange_ready: %s", cudaGetErrorString(e));
     return NIMLLM_OK;
 }
@@ -209,24 +213,53 @@ void nimllm_peer_exchange_destroy(nimllm_peer_exchange *x) {
     delete x;
 }
 
+}  // extern "C"
+
+namespace nimllm {
+PeerPush peer_push_of(const nimllm_peer_exchange *x) {
+    PeerPush px;
+    px.peers = x->peer_table_dev; px.rank = x->rank; px.world = x->world; px.rows_max = x->rows_max; px.W = x->W;
+    px.slot_floats = x->slot_floats;
+    return px;
+}
+int peer_rows_max(const nimllm_peer_exchange *x) { return x->rows_max; }
+int peer_head_dim(const nimllm_peer_exchange *x) { return x->W - 4; }
+}  // namespace nimllm
+
+extern "C" {
+
+/* bounded wait for every rank's records of this call, then the merge: out [rows, D] */
+int nimllm_attn_wait_combine(nimllm_peer_exchange *x, int rows, void *out, int out_dtype, int *status_dev, void *stream) {
+    if (!x || !out || !status_dev) return fail(NIMLLM_ERR_ARG, "attn_wait_combine: null argument");
+    if (rows <= 0 || rows > x->rows_max) return fail(NIMLLM_ERR_ARG, "attn_wait_combine: rows %d outside 1..%d", rows, x->rows_max);
+    if (!dtype_ok(out_dtype)) return fail(NIMLLM_ERR_ARG, "attn_wait_combine: unknown dtype");
+    const int D = x->W - 4;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((rows + 3) / 4); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0; cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, wait_combine_kernel, (const float *)x->local, x->world, rows, x->rows_max, D, x->W,
+                                       x->slot_floats, out, out_dtype, status_dev, x->wait_limit_ns);
+    if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_wait_combine: %s", cudaGetErrorString(e));
+    return NIMLLM_OK;
+}
+
 /* records [rows, D+4] of this rank in, merged output [rows, D] out; status_dev (device int,
- * caller-zeroed) becomes 1 if a peer's records did not arrive within about a second */
+ * caller-zeroed) becomes 1 if a peer's records did not arrive within the wait limit */
 int nimllm_attn_combine_peers(nimllm_peer_exchange *x, const float *rec_local, int rows, void *out, int out_dtype,
                               int *status_dev, void *stream) {
     if (!x || !rec_local || !out || !status_dev) return fail(NIMLLM_ERR_ARG, "attn_combine_peers: null argument");
     if (rows <= 0 || rows > x->rows_max) return fail(NIMLLM_ERR_ARG, "attn_combine_peers: rows %d outside 1..%d", rows, x->rows_max);
     if (!dtype_ok(out_dtype)) return fail(NIMLLM_ERR_ARG, "attn_combine_peers: unknown dtype");
+    if ((uintptr_t)rec_local & 15) return fail(NIMLLM_ERR_ARG, "attn_combine_peers: records must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    const int D = x->W - 4;
     int blocks = (rows * x->W / 4 + 255) / 256;
     if (blocks > 32) blocks = 32;
-    push_kernel<<<blocks, 256, 0, st>>>(rec_local, x->peer_table_dev, x->rank, x->world, rows, x->rows_max, x->W,
-                                        x->slot_floats);
+    push_kernel<<<blocks, 256, 0, st>>>(rec_local, peer_push_of(x), rows);
     NIMLLM_CHECK_LAUNCH("attn_combine_peers push");
-    wait_combine_kernel<<<(rows + 3) / 4, 128, 0, st>>>(x->local, x->world, rows, x->rows_max, D, x->W, x->slot_floats, out,
-                                                        out_dtype, status_dev);
-    NIMLLM_CHECK_LAUNCH("attn_combine_peers merge");
-    return NIMLLM_OK;
+    return nimllm_attn_wait_combine(x, rows, out, out_dtype, status_dev, stream);
 }
 
 }  // extern "C"

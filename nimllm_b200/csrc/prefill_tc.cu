@@ -8,34 +8,34 @@
 // One CTA owns 256 consecutive query rows of one (sequence, query head) as two 128-row
 // tiles and walks the KV sequence in 128-row tiles up to the causal diagonal.
 //
-//   warp 8      TMA producer: K_j / V_j tiles into one 5-slot shared-memory ring walked in the
-//               order K_0 V_0 K_1 V_1 ... (cp.async.bulk.tensor, 128-byte swizzle, mbarrier
-//               transaction counts; a slot is released by tcgen05.commit when the MMAs that
-//               read it have completed).  Q tiles by TMA as well when no RoPE is asked for.
-//   warp 9      MMA issuer (one lane): S_w = Q_w K_j^T (both operands from shared memory) and
-//               O_w += P_w V_j (P from TMEM, V MN-major from shared memory) as tcgen05.mma
-//               (cta_group::1, kind::f16, M = N = 128, K = 16, fp32 accumulators in TMEM).  S
-//               and O of both query tiles take the 512 TMEM columns: S0 S1 O0 O1.
+//   warp 8      TMA producer: K_j tiles into a 3-slot ring, V_j tiles into a 2-slot ring
+//               (cp.async.bulk.tensor, 128-byte swizzle, mbarrier transaction counts; a slot is
+//               released by tcgen05.commit when the MMAs that read it have completed).  Q tiles by
+//               TMA as well when no RoPE is asked for.
+//   warp 9      MMA issuer, converged, one elected lane executes the tcgen05 instructions:
+//               S = Q_w K_j^T (both operands from shared memory) and O_w += P_w V_j (P from TMEM,
+//               V MN-major from shared memory), cta_group::1, kind::f16, M = N = 128, K = 16, fp32
+//               accumulators in TMEM.
 //   warps 0-3 / 4-7   softmax group of query tile 0 / 1, one thread per query row (= one TMEM
 //               lane).  Per KV tile: ONE TMEM round trip brings the 128 scores of the row into
 //               registers (setmaxnreg moves registers from warps 8-11 to these), row max, P =
-//               exp2(S*c - m) rounded to bf16 and stored back over the first 64 columns of S,
-//               where the PV MMA reads it as its A operand.  O is rescaled only when a row
-//               maximum grows by more than 2^8 (the exact softmax is restored by the final
-//               division by the running sum); the epilogue normalises, rounds and writes O.
+//               exp2(S*c - m) rounded to bf16 into the tile's own P columns, where the PV MMA
+//               reads it as its A operand.  O is rescaled only when a row maximum grows by more
+//               than 2^8 (the exact softmax is restored by the final division by the running
+//               sum); the epilogue normalises, rounds and writes O.
 //
-// While one group computes its softmax the tensor pipe works on the other tile's PV and next S.
+// TMEM (512 columns): S | P0 P1 | O0 | O1.  The two query tiles SHARE the one S accumulator: a
+// score tile only has to live until its softmax group has pulled it into registers, and the two
+// groups take turns.  Because P has columns of its own, Q_w K_{j+1}^T is computed while the
+// softmax of tile j still runs, and P_w V_j while the softmax of tile j+1 runs: a group goes from
+// one tile's softmax straight into the next one's, and no MMA sits on that chain.  Order of the
+// issuer: S fills alternate between the tiles (each waits only for the previous fill to have been
+// read out), every end of a softmax triggers that tile's PV and the other tile's next fill.
+//
 // RoPE: K arrives already rotated (the pre-pass that also fills the KV cache rotates it in
 // place, as the reference does and stores); Q is rotated by this kernel's prologue while it is
 // staged into the swizzled shared-memory tile (coalesced, 8 lanes per row), and written back
 // only when the caller keeps it (save_cache).
-//
-// Measured on B200 at 4 x 8192 x 32/8 heads (see profiles/): with the softmax handshakes
-// removed the TMA + MMA pipeline alone sustains ~1.2 PFLOP/s -- each CTA re-reads K/V for only
-// 256 query rows and both QK^T operands come from shared memory -- which bounds this one-CTA
-// design; splitting the exponentials between the special-function unit and an FMA polynomial,
-// packed bf16x2 exp2, deeper K/V rings and a KV-head-major CTA order were all measured and did
-// not help, because the softmax arithmetic is not on the critical path.
 //
 // Every wait on an mbarrier is bounded: after ~2 s without progress the CTA raises an abort
 // flag, all roles leave their loops, TMEM is released and a status word is set.
@@ -43,28 +43,29 @@
 
 namespace nimllm {
 
-float *g_prefill_dbg = nullptr;  // testing hook: device buffer of 33152 floats, or null
-
 namespace {
 
 using namespace tc;
 
 constexpr int kBM = 128;           // query rows per tile (= TMEM lanes)
 constexpr int kBN = 128;           // KV rows per tile
-constexpr int kSlots = 5;           // K/V ring: K_0 V_0 K_1 V_1 ... walk the slots in order
+constexpr int kKSlots = 3;          // ring of K tiles
+constexpr int kVSlots = 2;          // ring of V tiles
 // head_dim kD is a template parameter (128 or 64): a [128 x kD] bf16 tile is kD/64 swizzled 64-column
 // boxes of 16 KiB
 template <int kD> constexpr int tile_bytes() { return kBN * kD * 2; }
 constexpr int kThreads = 384;                // 8 softmax warps + one warpgroup holding producer, MMA issuer, 2 idle
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 256;   // S (shared by both tiles) | P0 P1 | O0 O1
 constexpr float kRescaleThreshold = 8.0f;    // log2 units: O is rescaled when a row maximum grows by more
 
 template <int kD> struct Smem {
     // tiles first: 1024-byte alignment is required by the 128-byte swizzle atoms
     uint8_t q[2][tile_bytes<kD>()];
-    uint8_t kv[kSlots][tile_bytes<kD>()];
-    uint64_t q_full, kv_full[kSlots], kv_empty[kSlots];
-    uint64_t s_full[2], p_ready[2], o_full[2], drain;
+    uint8_t k[kKSlots][tile_bytes<kD>()];
+    uint8_t v[kVSlots][tile_bytes<kD>()];
+    uint64_t q_full, k_full[kKSlots], k_empty[kKSlots], v_full[kVSlots], v_empty[kVSlots];
+    uint64_t s_full[2], s_free, p_ready[2], pv_done[2], o_full[2], drain;
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -75,7 +76,6 @@ struct PrefillParams {
     float *lse;              // [B, Hq, S] or null
     const float *cos_tab, *sin_tab;  // rows pos0.. used when rotate_q
     int *status;             // device status word: 0 ok, 1 a bounded wait gave up
-    float *dbg;              // optional debug dump (tests only)
     int B, S, Hq, Hkv, pos0;
     int rotate_q;            // 1: stage Q through registers with RoPE; 0: Q is loaded by TMA
     int write_back_q;        // with rotate_q: also store the rotated Q to global
@@ -115,10 +115,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, p.rotate_q ? 8 : 1);
-        for (int s = 0; s < kSlots; s++) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 1); }
+        for (int s = 0; s < kKSlots; s++) { mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1); }
+        for (int s = 0; s < kVSlots; s++) { mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1); }
         for (int w = 0; w < 2; w++) {
-            mbar_init(&sm.s_full[w], 1); mbar_init(&sm.p_ready[w], 4); mbar_init(&sm.o_full[w], 1);
+            mbar_init(&sm.s_full[w], 1); mbar_init(&sm.p_ready[w], 4); mbar_init(&sm.pv_done[w], 1);
+            mbar_init(&sm.o_full[w], 1);
         }
+        mbar_init(&sm.s_free, 4);
         mbar_init(&sm.drain, 1);
         sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -147,82 +150,100 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     if (active1) tma_load_2d(sm.q[1] + bx * kBoxBytes, &q_map, qx + bx * 64, y0 + kBM, &sm.q_full);
                 }
             }
-            // ring position u = 2j for K_j, 2j + 1 for V_j; slot u % kSlots, phase (u / kSlots) & 1
-            for (int u = 0; u < 2 * nmax; u++) {
-                const int slot = u % kSlots, ph = (u / kSlots) & 1;
-                const int y = b * p.S + (u >> 1) * kBN;
-                const CUtensorMap *map = (u & 1) ? &v_map : &k_map;
-                if (!mbar_wait(&sm.kv_empty[slot], ph ^ 1, abort_flag)) break;
-                mbar_expect_tx(&sm.kv_full[slot], kTileBytes);
+            // K_j goes to slot j % kKSlots (phase (j / kKSlots) & 1), V_j to slot j % kVSlots; loads
+            // are issued in the order the issuer first needs them: K_0 K_1 V_0 K_2 V_1 K_3 ...
+            auto load = [&](uint8_t *dst, const CUtensorMap *map, int j, uint64_t *full) {
+                mbar_expect_tx(full, kTileBytes);
                 for (int bx = 0; bx < kBoxes; bx++)
-                    tma_load_2d(sm.kv[slot] + bx * kBoxBytes, map, kx + bx * 64, y, &sm.kv_full[slot]);
+                    tma_load_2d(dst + bx * kBoxBytes, map, kx + bx * 64, b * p.S + j * kBN, full);
+            };
+            bool ok = true;
+            for (int j = 0; ok && j <= nmax; j++) {
+                if (j < nmax) {
+                    if (!(ok = mbar_wait(&sm.k_empty[j % kKSlots], ((j / kKSlots) & 1) ^ 1, abort_flag))) break;
+                    load(sm.k[j % kKSlots], &k_map, j, &sm.k_full[j % kKSlots]);
+                }
+                if (j >= 1) {
+                    const int jv = j - 1;
+                    if (!(ok = mbar_wait(&sm.v_empty[jv % kVSlots], ((jv / kVSlots) & 1) ^ 1, abort_flag))) break;
+                    load(sm.v[jv % kVSlots], &v_map, jv, &sm.v_full[jv % kVSlots]);
+                }
             }
         }
     } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
+        // The warp stays converged: descriptors are warp-uniform values (no per-lane copies to
+        // move into uniform registers), the tcgen05 instructions execute in one elected lane.
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        if (lane == 0) {
+        {
+            const uint32_t leader = elect_one();
             constexpr uint32_t idesc_qk = instr_desc(kBM, kBN, 0, 0);   // A, B K-major
             constexpr uint32_t idesc_pv = instr_desc(kBM, kD, 0, 1);    // A from TMEM, B (V) MN-major
-            const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
-            const uint32_t s_tmem[2] = {tmem + 0, tmem + 128};
-            const uint32_t o_tmem[2] = {tmem + 256, tmem + 384};
+            // descriptor words: start address >> 4 | leading byte offset >> 4 << 16 in the low word,
+            // stride byte offset 1024 B, version 1 and the 128-byte swizzle in the high word
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            constexpr uint32_t kLboK = 1u << 16;                         // K-major operands: 16 B
+            constexpr uint32_t kLboV = (uint32_t)(kBoxBytes >> 4) << 16; // MN-major V: 64-column boxes 16 KiB apart
+            const uint32_t q_lo[2] = {((smem_u32(sm.q[0]) >> 4) & 0x3FFFu) | kLboK, ((smem_u32(sm.q[1]) >> 4) & 0x3FFFu) | kLboK};
+            const uint32_t k_base = smem_u32(sm.k[0]), v_base = smem_u32(sm.v[0]);
+            const uint32_t s_tmem = tmem + kColS;
+            const uint32_t p_tmem[2] = {tmem + kColP, tmem + kColP + 64};
+            const uint32_t o_tmem[2] = {tmem + kColO, tmem + kColO + 128};
             const int n_w[2] = {n0, n1};
             bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
             tc_fence_after();
+            int fills = 0;                                  // S fills issued so far (both tiles)
 
-            // S_w = Q_w K^T : 8 steps of 16 along D; both operands K-major, 128-byte swizzle,
-            // 1024 bytes between 8-row groups; a step advances 32 bytes inside the 128-byte row
-            auto issue_qk = [&](int w, int slot) {
-                const uint32_t ka = smem_u32(sm.kv[slot]);
+            // S = Q_w K_j^T : kD/16 steps of 16 along D; both operands K-major, 128-byte swizzle,
+            // 1024 bytes between 8-row groups; a step advances 32 bytes inside the 128-byte row.
+            // The fill has to wait until the previous one has been read out of TMEM.
+            auto fill = [&](int w, int j) {
+                if (!ok) return;
+                if (fills > 0 && !(ok = mbar_wait(&sm.s_free, (fills - 1) & 1, abort_flag))) return;
+                if (!(ok = mbar_wait(&sm.k_full[j % kKSlots], (j / kKSlots) & 1, abort_flag))) return;
+                tc_fence_after();
+                const uint32_t k_lo = (((k_base + (uint32_t)(j % kKSlots) * kTileBytes) >> 4) & 0x3FFFu) | kLboK;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ks++) {
-                    const uint32_t off = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
-                    mma_ss(s_tmem[w], smem_desc(q_addr[w] + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_qk, ks > 0);
+                    const uint32_t c = (uint32_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+                    mma_ss_if(leader, s_tmem, make_desc(q_lo[w] + c, kDescHi), make_desc(k_lo + c, kDescHi), idesc_qk, ks > 0);
                 }
-                tc_commit(&sm.s_full[w]);
+                tc_commit_if(leader, &sm.s_full[w]);
+                fills++;
+                // K_j is done with once the last tile that attends it has its scores: tile 1 when
+                // it is active (it always attends at least as many KV tiles), else tile 0
+                if (w == 1 || j >= n_w[1]) tc_commit_if(leader, &sm.k_empty[j % kKSlots]);
             };
-            // O_w += P_w V : 8 steps of 16 KV rows; P (bf16 pairs, 8 columns per step) from TMEM,
-            // V MN-major: 16 rows = 2048 bytes per step, 64-column boxes 16 KiB apart
-            auto issue_pv = [&](int w, int slot, int j) {
-                const uint32_t va = smem_u32(sm.kv[slot]);
+            // O_w += P_w V_j : 8 steps of 16 KV rows; P (bf16 pairs, 8 columns per step) from TMEM,
+            // V MN-major: 16 rows = 2048 bytes per step
+            auto pv = [&](int w, int j) {
+                if (!ok) return;
+                if (!(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) return;
+                if (!(ok = mbar_wait(&sm.v_full[j % kVSlots], (j / kVSlots) & 1, abort_flag))) return;
+                tc_fence_after();
+                const uint32_t v_lo = (((v_base + (uint32_t)(j % kVSlots) * kTileBytes) >> 4) & 0x3FFFu) | kLboV;
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ks++)
-                    mma_ts(o_tmem[w], s_tmem[w] + ks * 8, smem_desc(va + ks * 2048, kBoxBytes, 1024), idesc_pv,
-                           (j > 0 || ks > 0) ? 1u : 0u);
-                if (j == n_w[w] - 1) tc_commit(&sm.o_full[w]);
+                    mma_ts_if(leader, o_tmem[w], p_tmem[w] + ks * 8, make_desc(v_lo + ks * 128, kDescHi), idesc_pv,
+                              (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit_if(leader, &sm.pv_done[w]);       // P_w may be overwritten, O_w may be rescaled
+                if (j == n_w[w] - 1) tc_commit_if(leader, &sm.o_full[w]);
             };
 
-            auto wait_full = [&](int u) { return mbar_wait(&sm.kv_full[u % kSlots], (u / kSlots) & 1, abort_flag); };
-            auto release = [&](int u) { tc_commit(&sm.kv_empty[u % kSlots]); };   // arrives when the MMAs so far are done
-
-            if (ok && nmax > 0) ok = wait_full(0);
-            if (ok && nmax > 0) {
-                tc_fence_after();
-                if (n0 > 0) issue_qk(0, 0);
-                if (n1 > 0) issue_qk(1, 0);
-                release(0);
+            if (0 < n0) fill(0, 0);
+            if (0 < n1) fill(1, 0);
+            if (1 < n0) fill(0, 1);
+            for (int i = 0; ok && i < nmax; i++) {
+                // tile 0 finished the softmax of KV tile i (and took S_0(i+1) out of TMEM)
+                if (i < n0) pv(0, i);
+                if (i + 1 < n1) fill(1, i + 1);
+                // tile 1 finished the softmax of KV tile i (and took S_1(i+1) out of TMEM)
+                if (i < n1) pv(1, i);
+                if (ok) tc_commit_if(leader, &sm.v_empty[i % kVSlots]);
+                if (i + 2 < n0) fill(0, i + 2);
             }
-            for (int j = 0; ok && j < nmax; j++) {
-                const int uv = 2 * j + 1, ukn = 2 * j + 2;      // ring positions of V_j and K_{j+1}
-                const bool next = j + 1 < nmax;
-                if (!(ok = wait_full(uv))) break;
-                if (next && !(ok = wait_full(ukn))) break;
-#pragma unroll
-                for (int w = 0; w < 2; w++) {
-                    if (j < n_w[w]) {
-                        if (!(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) break;
-                        tc_fence_after();
-                        issue_pv(w, uv % kSlots, j);
-                    }
-                    if (w == 1) release(uv);
-                    if (j + 1 < n_w[w]) issue_qk(w, ukn % kSlots);
-                }
-                if (!ok) break;
-                if (next) release(ukn);
-            }
-            // every MMA issued by this thread has completed once this commit arrives
-            tc_commit(&sm.drain);
+            // every MMA issued by this warp has completed once this commit arrives
+            tc_commit_if(leader, &sm.drain);
             mbar_wait(&sm.drain, 0, abort_flag);
         }
     } else if (warp < 8) {
@@ -232,8 +253,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         const int r = (warp & 3) * 32 + lane;          // row inside the tile = TMEM lane
         const int qrow = row_base + w * kBM + r;       // query position inside the sequence
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t s_addr = lane_base + (w ? 128u : 0u);
-        const uint32_t o_addr = lane_base + (w ? 384u : 256u);
+        const uint32_t s_addr = lane_base + kColS;
+        const uint32_t p_addr = lane_base + kColP + (w ? 64u : 0u);
+        const uint32_t o_addr = lane_base + kColO + (w ? 128u : 0u);
         const int n = w ? n1 : n0;
         const int diag = 2 * t + w;                    // KV tile holding this tile's diagonal
         const float c = p.scale_log2e;
@@ -318,8 +340,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             tmem_ld32(s_addr + 64, v + 64);
             tmem_ld32(s_addr + 96, v + 96);
             tc_wait_ld();
-            if (p.dbg && blockIdx.x == 0 && w == 0 && j == 0)
-                for (int i = 0; i < 128; i++) p.dbg[r * 128 + i] = __uint_as_float(v[i]);
+            // the scores are in registers: the other tile's next scores may take their place
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.s_free);
 
             // row maximum of the raw scores, four independent chains
             float mx;
@@ -354,8 +378,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 grow = true;
             }
             if (__any_sync(0xffffffffu, grow)) {
-                // rare: bring O down to the new reference maximum.  S_j is complete, so every
-                // earlier MMA (the last PV of this tile included) has finished with O.
+                // rare: bring O down to the new reference maximum, once the PV products of the
+                // tile before (issued while this softmax was starting) have landed in O
+                if (!(ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[w], (j - 1) & 1, abort_flag)))) break;
+                tc_fence_after();
 #pragma unroll 1
                 for (int ch = 0; ch < kD / 32; ch++) {
                     uint32_t o[32];
@@ -385,11 +411,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 pk[i >> 1] = pack_bf16(e[0], e[1]);
                 pk[(i >> 1) + 1] = pack_bf16(e[2], e[3]);
             }
-            tmem_st32(s_addr, pk);
-            tmem_st32(s_addr + 32, pk + 32);
             l += (sum0 + sum1) + (sum2 + sum3);
+            // P_w(j-1) must have been consumed (its PV was issued when the previous softmax ended)
+            if (j > 0) {
+                if (!(ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[w], (j - 1) & 1, abort_flag)))) break;
+                tc_fence_after();
+            }
+            tmem_st32(p_addr, pk);
+            tmem_st32(p_addr + 32, pk + 32);
             tc_wait_st();
-            if (p.dbg && blockIdx.x == 0 && w == 0 && j == 0) p.dbg[32768 + 256 + r] = mx;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_ready[w]);     // one arrival per warp
@@ -406,8 +436,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 uint32_t v[32];
                 tmem_ld32(o_addr + ch * 32, v);
                 tc_wait_ld();
-                if (p.dbg && blockIdx.x == 0 && w == 0)
-                    for (int i = 0; i < 32; i++) p.dbg[16384 + r * 128 + ch * 32 + i] = __uint_as_float(v[i]);
                 if (qrow < p.S) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -422,7 +450,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             }
             if (p.lse && qrow < p.S)
                 p.lse[((int64_t)b * p.Hq + h) * p.S + qrow] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
-            if (p.dbg && blockIdx.x == 0 && w == 0) { p.dbg[32768 + r] = l; p.dbg[32768 + 128 + r] = m_ref; }
         }
     }
 
@@ -502,7 +529,7 @@ int launch_prefill_tc_d(void *q, const void *k, const void *v, void *out, float 
     PrefillParams p;
     p.q = (__nv_bfloat16 *)q; p.out = (__nv_bfloat16 *)out; p.lse = lse;
     p.cos_tab = cos_tab; p.sin_tab = sin_tab;
-    p.status = (int *)workspace; p.dbg = kD == 128 ? g_prefill_dbg : nullptr;
+    p.status = (int *)workspace;
     p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.pos0 = pos0;
     p.rotate_q = cos_tab ? 1 : 0;
     p.write_back_q = write_back_q;
@@ -534,5 +561,3 @@ int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *l
 }
 
 }  // namespace nimllm
-
-extern "C" void nimllm_attn_debug_prefill_dump(float *device_buffer) { nimllm::g_prefill_dbg = device_buffer; }

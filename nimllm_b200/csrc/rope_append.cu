@@ -24,6 +24,10 @@ struct RopeAppendParams {
     int pos0, cache_row0, max_seq;
     int B, n, Hq, Hkv, D;
     int write_back_k;
+    // paged cache (page_table != null): page_table [B, max_pages] -> page of page_rows rows,
+    // pages [n_pages][Hkv][page_rows][D]; kv_off / strides / cache_row0 are not used then
+    const int32_t *page_table;
+    int max_pages, page_shift, n_pages;
 };
 
 template <typename T> __device__ __forceinline__ void load4(const T *p, float *f);
@@ -92,7 +96,21 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeAppendParams p) {
                 store4<ActT>(x + half, x1);
             }
         }
-        if (!is_q && p.k_cache) {
+        if (!is_q && p.k_cache && p.page_table) {
+            // every row finds its own page: an append may cross page boundaries; rows past the
+            // table, unassigned entries (< 0) and pages outside the pool are not stored
+            const int pr = pos >> p.page_shift;
+            if (pos >= 0 && pr < p.max_pages) {
+                const int pg = p.page_table[(int64_t)b * p.max_pages + pr];
+                if (pg >= 0 && pg < p.n_pages) {
+                    const int64_t base = (((int64_t)pg * p.Hkv + head) << p.page_shift) * p.D +
+                                         (int64_t)(pos & ((1 << p.page_shift) - 1)) * p.D + f;
+                    CacheT *dst = reinterpret_cast<CacheT *>(is_k ? p.k_cache : p.v_cache) + base;
+                    store4<CacheT>(dst, x0);
+                    store4<CacheT>(dst + half, x1);
+                }
+            }
+        } else if (!is_q && p.k_cache) {
             int row = pos - p.cache_row0;
             if (row >= 0 && row < p.max_seq) {
                 int64_t base = (p.kv_off ? p.kv_off[b] : (int64_t)b * p.seq_stride) +
@@ -112,8 +130,10 @@ int launch_rope_append(void *q, int Hq, void *k_new, const void *v_new, int act_
                        const int32_t *seq_pos, int pos0, void *k_cache, void *v_cache,
                        int cache_dtype, const int64_t *kv_off, int64_t seq_stride,
                        int64_t head_stride, int cache_row0, int max_seq, int B, int n, int Hkv,
-                       int D, cudaStream_t st) {
+                       int D, cudaStream_t st, const int32_t *page_table, int max_pages, int page_shift,
+                       int n_pages) {
     RopeAppendParams p;
+    p.page_table = page_table; p.max_pages = max_pages; p.page_shift = page_shift; p.n_pages = n_pages;
     p.q = q; p.k_new = k_new; p.v_new = v_new;
     p.cos_tab = cos_tab; p.sin_tab = sin_tab; p.seq_pos = seq_pos;
     p.k_cache = k_cache; p.v_cache = v_cache; p.kv_off = kv_off;

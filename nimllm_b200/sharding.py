@@ -62,21 +62,33 @@ def gather_partials(rec, group=None):
 
 
 class PeerExchange:
-    """Per-rank exchange buffer for KV-sequence-shard partials, wired to the other ranks of the
-    box through CUDA IPC handles passed over the (host-side) process group.  combine() is the
-    data path: peer stores + flags + bounded wait + merge, no collective."""
+    """Per-rank exchange buffer for KV-sequence-shard partials.  With a process group the ranks of
+    the box are wired together through CUDA IPC handles passed over the (host-side) group; with
+    `local_peers` (a list of PeerExchange objects of this process, used by single-GPU tests and by
+    one process driving several ranks) the peers' buffers are used directly.  combine() and
+    decode_combine() are the data path: peer stores + flags + bounded wait + merge, no collective."""
 
-    def __init__(self, rows_max: int, head_dim: int, group=None):
+    def __init__(self, rows_max: int, head_dim: int, group=None, rank=None, world=None, wait_limit_ms=None):
         import ctypes as C
         import torch
-        import torch.distributed as dist
         from ._lib import check, lib
         self._lib, self._check = lib(), check
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.head_dim = head_dim
+        self._out = None
+        solo = rank is not None
+        if solo:
+            self.rank, self.world = rank, world
+        else:
+            import torch.distributed as dist
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.handle = self._lib.nimllm_peer_exchange_create(self.rank, self.world, rows_max, head_dim)
         if not self.handle:
             raise RuntimeError(self._lib.nimllm_attn_last_error().decode())
+        if wait_limit_ms is not None:
+            check(self._lib.nimllm_peer_exchange_set_wait_limit(self.handle, int(wait_limit_ms)))
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        if solo:
+            return                                  # the caller wires the peers with connect_local()
         mine = C.create_string_buffer(64)
         check(self._lib.nimllm_peer_exchange_export(self.handle, mine))
         handles = [None] * self.world
@@ -95,7 +107,14 @@ class PeerExchange:
         if any(errs):
             self.close()
             raise RuntimeError("peer exchange setup failed: " + "; ".join(f"rank {r}: {e}" for r, e in enumerate(errs) if e))
-        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    @staticmethod
+    def connect_local(exchanges):
+        """Wire exchange objects that live in this process (one per rank, same device) to each other."""
+        for x in exchanges:
+            for y in exchanges:
+                x._check(x._lib.nimllm_peer_exchange_import_local(x.handle, y.rank, y.handle))
+            x._check(x._lib.nimllm_peer_exchange_ready(x.handle))
 
     def combine(self, rec, out=None):
         """rec [rows, D+4] fp32 (this rank's records) -> merged [rows, D] fp32."""
@@ -106,6 +125,37 @@ class PeerExchange:
         self._check(self._lib.nimllm_attn_combine_peers(self.handle, rec.data_ptr(), rows, out.data_ptr(), 0,
                                                         self.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
         return out
+
+    def decode_push(self, q, k_cache, v_cache, *, n_head, n_kv_head, head_dim, max_len, seq_len=None, kv_off=None,
+                    seq_stride=0, head_stride=0, scale=None, chunk_rows=0):
+        """This rank's shard decode; its merge launch stores the records into every peer's buffer."""
+        import math
+        import torch
+        from . import attention as A
+        B = q.shape[0]
+        scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+        need = self._lib.nimllm_attn_decode_push_workspace_bytes(B, n_head, n_kv_head, head_dim, max_len)
+        ws = A._arena.get(max(need, 1), q.device)
+        self._check(self._lib.nimllm_attn_decode_push(
+            self.handle, q.data_ptr(), A._code(q), k_cache.data_ptr(), v_cache.data_ptr(),
+            kv_off.data_ptr() if kv_off is not None else None, seq_stride, head_stride,
+            seq_len.data_ptr() if seq_len is not None else None, max_len, B, n_head, n_kv_head, head_dim, scale,
+            ws.data_ptr(), need, torch.cuda.current_stream().cuda_stream))
+        return B * n_head
+
+    def wait_combine(self, rows, out=None):
+        """Bounded wait for every rank's records of this call, then the merge -> [rows, D] fp32."""
+        import torch
+        if out is None:
+            out = torch.empty((rows, self.head_dim), dtype=torch.float32, device="cuda")
+        self._check(self._lib.nimllm_attn_wait_combine(self.handle, rows, out.data_ptr(), 0, self.status.data_ptr(),
+                                                       torch.cuda.current_stream().cuda_stream))
+        return out
+
+    def decode_combine(self, q, k_cache, v_cache, out=None, **geom):
+        """The whole sharded step of this rank: decode + merge-and-push, wait + merge.  q [B, Hq*D],
+        the rank's rows of the cache; geom as attention.decode_batch takes it.  Returns [B*Hq, D]."""
+        return self.wait_combine(self.decode_push(q, k_cache, v_cache, **geom), out)
 
     def ok(self) -> bool:
         """False if a wait for a peer's records ever ran out (synchronises)."""

@@ -141,20 +141,3 @@ def test_balanced_decode_plan_covers_every_unit_once():
         if total:
             per_warp = np.bincount(segs[:, 0], weights=(segs[:, 4] - segs[:, 3]))
             assert per_warp.max() - per_warp[per_warp > 0].min() <= 1     # equal spans
-
-
-def test_paged_append_offsets_point_at_the_page_row():
-    """kv_off + head*head_stride + pos*D (what rope_append computes with cache_row0 = 0) must be
-    the element of row pos % page_rows of the sequence's page for that row."""
-    import torch
-    from nimllm_b200.attention import paged_append_offsets
-    Hkv, D, P = 3, 64, 32
-    table = torch.tensor([[5, 2, 9], [0, 7, 1]], dtype=torch.int32)
-    pos = torch.tensor([70, 31], dtype=torch.int32)
-    off = paged_append_offsets(table, pos, P, Hkv, D)
-    for b in range(2):
-        page = int(table[b, int(pos[b]) // P])
-        for head in range(Hkv):
-            got = int(off[b]) + head * P * D + int(pos[b]) * D
-            want = page * Hkv * P * D + head * P * D + (int(pos[b]) % P) * D
-            assert got == want

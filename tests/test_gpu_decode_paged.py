@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import host
+from gpu_util import bf16_bits, host
 from nimllm_b200 import _lib, attention as A
 from oracle import oracle as O
 from util import TOL_BF16, assert_close
@@ -66,8 +66,8 @@ def test_paged_equals_contiguous_and_ground_truth(Hq, Hkv, D, page_rows):
 
 
 def test_paged_append_then_decode():
-    """A new token per sequence goes through rope_append with page-derived offsets, then the
-    paged decode attends it: equal to doing the same on a contiguous cache."""
+    """A new token per sequence goes through the paged append, then the paged decode attends it:
+    equal to doing the same on a contiguous cache."""
     Hq, Hkv, D, page_rows, cap = 9, 3, 64, 64, 512
     lens = np.array([63, 64, 65, 200, 0, 511], np.int32)        # rows already cached; the new token is row lens[b]
     B = len(lens)
@@ -87,13 +87,57 @@ def test_paged_append_then_decode():
     flat = A.decode_batch(q1.view(B, Hq * D), kc, vc, n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=cap, seq_len=pos + 1,
                           seq_stride=Hkv * cap * D, head_stride=cap * D)
     q2, k2, v2 = (a.clone() for a in acts)
-    off = A.paged_append_offsets(table, pos, page_rows, Hkv, D)
-    A.rope_append(q2, k2, v2, cos, sin, n_head=Hq, n_kv_head=Hkv, head_dim=D, seq_pos=pos, k_cache=kp, v_cache=vp,
-                  kv_off=off, head_stride=page_rows * D, max_seq=2 ** 30)
+    A.rope_append_paged(q2, k2, v2, cos, sin, kp, vp, table, n_head=Hq, n_kv_head=Hkv, head_dim=D, seq_pos=pos)
     paged = A.decode_paged(q2.view(B, Hq * D), kp, vp, table, n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=cap,
                            seq_len=pos + 1)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(host(paged), host(flat))
+
+
+def test_paged_append_of_several_tokens_crosses_pages_and_stays_in_the_pool():
+    """Appends of n = 70 tokens starting near page ends: every row must land in its own page (the
+    pool afterwards equals a paged copy of the contiguous cache), rows past the table and rows
+    whose table entry is unassigned (-1) or outside the pool are dropped, guard pages stay intact."""
+    Hq, Hkv, D, page_rows, cap, n = 4, 2, 64, 32, 256, 70
+    pos0 = np.array([0, 30, 63, 150, 200], np.int32)            # 200 + 70 > 256: the tail is past the table
+    B = len(pos0)
+    g = torch.Generator(device="cuda").manual_seed(78)
+    kc = torch.zeros(B, Hkv, cap, D, device="cuda").bfloat16()
+    vc = torch.zeros_like(kc)
+    max_pages = cap // page_rows
+    n_pool = B * max_pages + 2                                   # two guard pages nobody owns
+    perm = torch.randperm(B * max_pages, generator=torch.Generator().manual_seed(10)).to(torch.int32)
+    table = perm.view(B, max_pages).cuda()
+    table[3, 6] = -1                                             # rows 192..223 of sequence 3: unassigned
+    table[1, 2] = n_pool + 5                                     # rows 64..95 of sequence 1: outside the pool
+    kp = torch.zeros(n_pool, Hkv, page_rows, D, device="cuda").bfloat16()
+    vp = torch.zeros_like(kp)
+    kp[-2:] = 7.0; vp[-2:] = 7.0
+    cos, sin = A.rope_tables(cap + n, D, 10000.0)
+    pos = torch.from_numpy(pos0).cuda()
+    acts = [torch.randn(B, n, h * D, generator=g, device="cuda").bfloat16() for h in (Hq, Hkv, Hkv)]
+    q1, k1, v1 = (a.clone() for a in acts)
+    A.rope_append(q1, k1, v1, cos, sin, n_head=Hq, n_kv_head=Hkv, head_dim=D, seq_pos=pos, k_cache=kc, v_cache=vc,
+                  seq_stride=Hkv * cap * D, head_stride=cap * D, max_seq=cap)
+    q2, k2, v2 = (a.clone() for a in acts)
+    A.rope_append_paged(q2, k2, v2, cos, sin, kp, vp, table, n_head=Hq, n_kv_head=Hkv, head_dim=D, seq_pos=pos)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(bf16_bits(q1), bf16_bits(q2))
+    np.testing.assert_array_equal(bf16_bits(k1), bf16_bits(k2))
+    tab = table.cpu().numpy()
+    for b in range(B):
+        for r in range(max_pages):
+            pg = int(tab[b, r])
+            want_k = kc[b, :, r * page_rows:(r + 1) * page_rows]
+            want_v = vc[b, :, r * page_rows:(r + 1) * page_rows]
+            if pg < 0 or pg >= n_pool:
+                continue                                          # dropped rows: nothing to compare, nothing written
+            np.testing.assert_array_equal(bf16_bits(kp[pg]), bf16_bits(want_k))
+            np.testing.assert_array_equal(bf16_bits(vp[pg]), bf16_bits(want_v))
+    assert (kp[-2:] == 7.0).all() and (vp[-2:] == 7.0).all()
+    # the page whose table entry was redirected received nothing either
+    orphan = int(perm.view(B, max_pages)[1, 2])
+    assert not kp[orphan].any() and not vp[orphan].any()
 
 
 def test_paged_argument_checks():
