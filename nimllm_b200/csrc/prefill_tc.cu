@@ -136,7 +136,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const uint32_t tmem = sm.tmem_base;
 
     // Registers follow the work: the softmax warpgroups hold a whole row of S (128 values) plus
-    // the packed P, the third warpgroup only issues copies and MMAs.  168 per thread at launch.
+    // the packed P, the third warpgroup only issues copies and MMAs.  168 per thread at launch;
+    // setmaxnreg.inc can only take what the CTA's own warps gave back with setmaxnreg.dec, and it
+    // blocks (for ever) when that is not enough: 4 warps x (168 - 72) = 8 warps x (216 - 168).
     if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
@@ -184,63 +186,95 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
             constexpr uint32_t kLboK = 1u << 16;                         // K-major operands: 16 B
             constexpr uint32_t kLboV = (uint32_t)(kBoxBytes >> 4) << 16; // MN-major V: 64-column boxes 16 KiB apart
-            const uint32_t q_lo[2] = {((smem_u32(sm.q[0]) >> 4) & 0x3FFFu) | kLboK, ((smem_u32(sm.q[1]) >> 4) & 0x3FFFu) | kLboK};
+            const uint32_t q_lo0 = ((smem_u32(sm.q[0]) >> 4) & 0x3FFFu) | kLboK, q_lo1 = ((smem_u32(sm.q[1]) >> 4) & 0x3FFFu) | kLboK;
             const uint32_t k_base = smem_u32(sm.k[0]), v_base = smem_u32(sm.v[0]);
             const uint32_t s_tmem = tmem + kColS;
-            const uint32_t p_tmem[2] = {tmem + kColP, tmem + kColP + 64};
-            const uint32_t o_tmem[2] = {tmem + kColO, tmem + kColO + 128};
-            const int n_w[2] = {n0, n1};
             bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
             tc_fence_after();
-            int fills = 0;                                  // S fills issued so far (both tiles)
-
             // S = Q_w K_j^T : kD/16 steps of 16 along D; both operands K-major, 128-byte swizzle,
-            // 1024 bytes between 8-row groups; a step advances 32 bytes inside the 128-byte row.
-            // The fill has to wait until the previous one has been read out of TMEM.
-            auto fill = [&](int w, int j) {
-                if (!ok) return;
-                if (fills > 0 && !(ok = mbar_wait(&sm.s_free, (fills - 1) & 1, abort_flag))) return;
-                if (!(ok = mbar_wait(&sm.k_full[j % kKSlots], (j / kKSlots) & 1, abort_flag))) return;
+            // 1024 bytes between 8-row groups; a step advances 32 bytes inside the 128-byte row
+            auto issue_fill = [&](int w, int j) {
                 tc_fence_after();
                 const uint32_t k_lo = (((k_base + (uint32_t)(j % kKSlots) * kTileBytes) >> 4) & 0x3FFFu) | kLboK;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ks++) {
                     const uint32_t c = (uint32_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
-                    mma_ss_if(leader, s_tmem, make_desc(q_lo[w] + c, kDescHi), make_desc(k_lo + c, kDescHi), idesc_qk, ks > 0);
+                    mma_ss_if(leader, s_tmem, make_desc((w ? q_lo1 : q_lo0) + c, kDescHi), make_desc(k_lo + c, kDescHi), idesc_qk, ks > 0);
                 }
-                tc_commit_if(leader, &sm.s_full[w]);
-                fills++;
+                tc_commit_if(leader, w ? &sm.s_full[1] : &sm.s_full[0]);
                 // K_j is done with once the last tile that attends it has its scores: tile 1 when
                 // it is active (it always attends at least as many KV tiles), else tile 0
-                if (w == 1 || j >= n_w[1]) tc_commit_if(leader, &sm.k_empty[j % kKSlots]);
+                if (w == 1 || j >= n1) tc_commit_if(leader, &sm.k_empty[j % kKSlots]);
             };
             // O_w += P_w V_j : 8 steps of 16 KV rows; P (bf16 pairs, 8 columns per step) from TMEM,
             // V MN-major: 16 rows = 2048 bytes per step
-            auto pv = [&](int w, int j) {
-                if (!ok) return;
-                if (!(ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag))) return;
-                if (!(ok = mbar_wait(&sm.v_full[j % kVSlots], (j / kVSlots) & 1, abort_flag))) return;
+            auto issue_pv = [&](int w, int j) {
                 tc_fence_after();
                 const uint32_t v_lo = (((v_base + (uint32_t)(j % kVSlots) * kTileBytes) >> 4) & 0x3FFFu) | kLboV;
 #pragma unroll
                 for (int ks = 0; ks < kBN / 16; ks++)
-                    mma_ts_if(leader, o_tmem[w], p_tmem[w] + ks * 8, make_desc(v_lo + ks * 128, kDescHi), idesc_pv,
-                              (j > 0 || ks > 0) ? 1u : 0u);
-                tc_commit_if(leader, &sm.pv_done[w]);       // P_w may be overwritten, O_w may be rescaled
-                if (j == n_w[w] - 1) tc_commit_if(leader, &sm.o_full[w]);
+                    mma_ts_if(leader, tmem + kColO + (w ? 128u : 0u), tmem + kColP + (w ? 64u : 0u) + ks * 8,
+                              make_desc(v_lo + ks * 128, kDescHi), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit_if(leader, w ? &sm.pv_done[1] : &sm.pv_done[0]);   // P_w may be overwritten, O_w may be rescaled
+                if (j == (w ? n1 : n0) - 1) tc_commit_if(leader, w ? &sm.o_full[1] : &sm.o_full[0]);
             };
 
-            if (0 < n0) fill(0, 0);
-            if (0 < n1) fill(1, 0);
-            if (1 < n0) fill(0, 1);
-            for (int i = 0; ok && i < nmax; i++) {
-                // tile 0 finished the softmax of KV tile i (and took S_0(i+1) out of TMEM)
-                if (i < n0) pv(0, i);
-                if (i + 1 < n1) fill(1, i + 1);
-                // tile 1 finished the softmax of KV tile i (and took S_1(i+1) out of TMEM)
-                if (i < n1) pv(1, i);
-                if (ok) tc_commit_if(leader, &sm.v_empty[i % kVSlots]);
-                if (i + 2 < n0) fill(0, i + 2);
+            // Work still to issue: the S fills in their fixed order (tile 0 and tile 1 alternate,
+            // each waits for the previous fill to have been read out of TMEM) and, per tile, the PV
+            // of every finished softmax.  A look at a barrier costs this warp a few hundred cycles
+            // while the tensor cores stream operands out of shared memory, so it never waits on one
+            // item: every round it looks (non-blocking, all six looks in flight together) at what
+            // the pending items need and issues everything that is ready -- the fill first, because
+            // a softmax group will wait for it, while the PV products are not needed before the
+            // same tile's next P is stored.  (Measured: waiting on the items in a fixed order, fewer
+            // looks per round, and sleeping on the fill's barrier between rounds were all slower.)
+            int q_fills = 0, jf0 = 0, jf1 = 0, jp0 = 0, jp1 = 0, j_rel = 0;
+            int k_known = -1, v_known = -1;                 // tiles known to have landed in shared memory
+            uint32_t idle = 0;
+            uint64_t t_idle = 0;
+            while (ok && (jf0 < n0 || jf1 < n1 || jp0 < n0 || jp1 < n1)) {
+                int wf = -1;
+                if (jf0 < n0 && jf1 < n1) wf = jf0 <= jf1 ? 0 : 1;
+                else if (jf0 < n0) wf = 0;
+                else if (jf1 < n1) wf = 1;
+                const int jf = wf == 1 ? jf1 : jf0;         // step of the next fill (when there is one)
+                // (a look at a barrier that does not apply this round is harmless)
+                const int jk = min(jf, nmax - 1), jv0 = min(jp0, nmax - 1), jv1 = min(jp1, nmax - 1);
+                const uint32_t bars[6] = {smem_u32(&sm.s_free), smem_u32(&sm.k_full[jk % kKSlots]), smem_u32(&sm.p_ready[0]),
+                                          smem_u32(&sm.v_full[jv0 % kVSlots]), smem_u32(&sm.p_ready[1]),
+                                          smem_u32(&sm.v_full[jv1 % kVSlots])};
+                const uint32_t pars[6] = {(uint32_t)(q_fills - 1) & 1u, (uint32_t)(jk / kKSlots) & 1u, (uint32_t)jp0 & 1u,
+                                          (uint32_t)(jv0 / kVSlots) & 1u, (uint32_t)jp1 & 1u, (uint32_t)(jv1 / kVSlots) & 1u};
+                const uint32_t seen = mbar_test6(bars, pars);
+                const bool t_sf = seen & 1u, t_k = seen & 2u, t_p0 = seen & 4u, t_v0 = seen & 8u, t_p1 = seen & 16u, t_v1 = seen & 32u;
+                uint32_t bits = 0;
+                if (wf >= 0 && (q_fills == 0 || t_sf) && (jf <= k_known || t_k)) bits |= 1u;
+                if (jp0 < n0 && t_p0 && (jp0 <= v_known || t_v0)) bits |= 2u;
+                if (jp1 < n1 && t_p1 && (jp1 <= v_known || t_v1)) bits |= 4u;
+                bits = __shfl_sync(0xffffffffu, bits, 0);   // one answer for the whole warp
+                if (bits & 1u) {
+                    issue_fill(wf, jf);
+                    k_known = max(k_known, jf);
+                    if (wf) jf1++; else jf0++;
+                    q_fills++;
+                }
+                if (bits & 2u) { issue_pv(0, jp0); v_known = max(v_known, jp0); jp0++; }
+                if (bits & 4u) { issue_pv(1, jp1); v_known = max(v_known, jp1); jp1++; }
+                if (bits & 6u) {
+                    // V_j goes back to the producer once both tiles' products with it are issued
+                    while (j_rel < nmax && (jp0 > j_rel || j_rel >= n0) && (jp1 > j_rel || j_rel >= n1)) {
+                        tc_commit_if(leader, &sm.v_empty[j_rel % kVSlots]);
+                        j_rel++;
+                    }
+                }
+                if (bits) { idle = 0; continue; }
+                // nothing ready: bounded
+                if ((++idle & 63u) == 0u) {
+                    if (*abort_flag) { ok = false; break; }
+                    const uint64_t now = globaltimer_ns();
+                    if (idle == 64u) t_idle = now;
+                    else if (now - t_idle > 2000000000ull) { *abort_flag = 1; ok = false; break; }
+                }
             }
             // every MMA issued by this warp has completed once this commit arrives
             tc_commit_if(leader, &sm.drain);
@@ -398,8 +432,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const float neg_m = -m_ref;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
             uint32_t pk[64];
+            bool p_free = (j == 0);
 #pragma unroll
             for (int i = 0; i < 128; i += 4) {
+                // half-way: has the PV of the tile before finished with the P columns?  (asked here,
+                // so that the answer is back when the stores below need it)
+                if (i == 64 && j > 0) p_free = mbar_test(&sm.pv_done[w], (j - 1) & 1);
                 float x[4], e[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
@@ -414,7 +452,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             l += (sum0 + sum1) + (sum2 + sum3);
             // P_w(j-1) must have been consumed (its PV was issued when the previous softmax ended)
             if (j > 0) {
-                if (!(ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[w], (j - 1) & 1, abort_flag)))) break;
+                if (!__all_sync(0xffffffffu, p_free) &&
+                    !(ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[w], (j - 1) & 1, abort_flag)))) break;
                 tc_fence_after();
             }
             tmem_st32(p_addr, pk);

@@ -46,6 +46,30 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Six non-blocking looks issued back to back (one shared-memory round trip for all of them
+// instead of six in a row); bit i of the result = phase `par[i]` of barrier `bar[i]` completed.
+__device__ __forceinline__ uint32_t mbar_test6(const uint32_t (&bar)[6], const uint32_t (&par)[6]) {
+    uint32_t mask;
+    asm volatile(
+        "{\n\t.reg .pred p0, p1, p2, p3, p4, p5;\n\t.reg .u32 t;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p0, [%1], %7;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p1, [%2], %8;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p2, [%3], %9;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p3, [%4], %10;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p4, [%5], %11;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p5, [%6], %12;\n\t"
+        "selp.u32 %0, 1, 0, p0;\n\t"
+        "selp.u32 t, 2, 0, p1;\n\tor.b32 %0, %0, t;\n\t"
+        "selp.u32 t, 4, 0, p2;\n\tor.b32 %0, %0, t;\n\t"
+        "selp.u32 t, 8, 0, p3;\n\tor.b32 %0, %0, t;\n\t"
+        "selp.u32 t, 16, 0, p4;\n\tor.b32 %0, %0, t;\n\t"
+        "selp.u32 t, 32, 0, p5;\n\tor.b32 %0, %0, t;\n\t}"
+        : "=r"(mask)
+        : "r"(bar[0]), "r"(bar[1]), "r"(bar[2]), "r"(bar[3]), "r"(bar[4]), "r"(bar[5]),
+          "r"(par[0]), "r"(par[1]), "r"(par[2]), "r"(par[3]), "r"(par[4]), "r"(par[5])
+        : "memory");
+    return mask;
+}
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
