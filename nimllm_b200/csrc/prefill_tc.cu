@@ -56,6 +56,7 @@ constexpr int kVSlots = 2;          // ring of V tiles
 template <int kD> constexpr int tile_bytes() { return kBN * kD * 2; }
 constexpr int kThreads = 384;                // 8 softmax warps + one warpgroup holding producer, MMA issuer, 2 idle
 constexpr uint32_t kTmemCols = 512;
+constexpr int kBarSFree = 1, kBarPReady = 2;     // named barriers (0 is __syncthreads): 128 arriving threads + the issuing warp
 constexpr uint32_t kColS = 0, kColP = 128, kColO = 256;   // S (shared by both tiles) | P0 P1 | O0 O1
 constexpr float kRescaleThreshold = 8.0f;    // log2 units: O is rescaled when a row maximum grows by more
 
@@ -219,62 +220,47 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 if (j == (w ? n1 : n0) - 1) tc_commit_if(leader, w ? &sm.o_full[1] : &sm.o_full[0]);
             };
 
-            // Work still to issue: the S fills in their fixed order (tile 0 and tile 1 alternate,
-            // each waits for the previous fill to have been read out of TMEM) and, per tile, the PV
-            // of every finished softmax.  A look at a barrier costs this warp a few hundred cycles
-            // while the tensor cores stream operands out of shared memory, so it never waits on one
-            // item: every round it looks (non-blocking, all six looks in flight together) at what
-            // the pending items need and issues everything that is ready -- the fill first, because
-            // a softmax group will wait for it, while the PV products are not needed before the
-            // same tile's next P is stored.  (Measured: waiting on the items in a fixed order, fewer
-            // looks per round, and sleeping on the fill's barrier between rounds were all slower.)
-            int q_fills = 0, jf0 = 0, jf1 = 0, jp0 = 0, jp1 = 0, j_rel = 0;
-            int k_known = -1, v_known = -1;                 // tiles known to have landed in shared memory
-            uint32_t idle = 0;
-            uint64_t t_idle = 0;
-            while (ok && (jf0 < n0 || jf1 < n1 || jp0 < n0 || jp1 < n1)) {
-                int wf = -1;
-                if (jf0 < n0 && jf1 < n1) wf = jf0 <= jf1 ? 0 : 1;
-                else if (jf0 < n0) wf = 0;
-                else if (jf1 < n1) wf = 1;
-                const int jf = wf == 1 ? jf1 : jf0;         // step of the next fill (when there is one)
-                // (a look at a barrier that does not apply this round is harmless)
-                const int jk = min(jf, nmax - 1), jv0 = min(jp0, nmax - 1), jv1 = min(jp1, nmax - 1);
-                const uint32_t bars[6] = {smem_u32(&sm.s_free), smem_u32(&sm.k_full[jk % kKSlots]), smem_u32(&sm.p_ready[0]),
-                                          smem_u32(&sm.v_full[jv0 % kVSlots]), smem_u32(&sm.p_ready[1]),
-                                          smem_u32(&sm.v_full[jv1 % kVSlots])};
-                const uint32_t pars[6] = {(uint32_t)(q_fills - 1) & 1u, (uint32_t)(jk / kKSlots) & 1u, (uint32_t)jp0 & 1u,
-                                          (uint32_t)(jv0 / kVSlots) & 1u, (uint32_t)jp1 & 1u, (uint32_t)(jv1 / kVSlots) & 1u};
-                const uint32_t seen = mbar_test6(bars, pars);
-                const bool t_sf = seen & 1u, t_k = seen & 2u, t_p0 = seen & 4u, t_v0 = seen & 8u, t_p1 = seen & 16u, t_v1 = seen & 32u;
-                uint32_t bits = 0;
-                if (wf >= 0 && (q_fills == 0 || t_sf) && (jf <= k_known || t_k)) bits |= 1u;
-                if (jp0 < n0 && t_p0 && (jp0 <= v_known || t_v0)) bits |= 2u;
-                if (jp1 < n1 && t_p1 && (jp1 <= v_known || t_v1)) bits |= 4u;
-                bits = __shfl_sync(0xffffffffu, bits, 0);   // one answer for the whole warp
-                if (bits & 1u) {
-                    issue_fill(wf, jf);
-                    k_known = max(k_known, jf);
-                    if (wf) jf1++; else jf0++;
-                    q_fills++;
+            // Hand-overs from the softmax groups (scores read out of TMEM, P stored) come through
+            // named hardware barriers: a look at a shared-memory barrier costs this warp several
+            // hundred cycles while the tensor cores stream operands out of shared memory, a
+            // barrier.sync a few tens.  The order is fixed and is the order of the events: every
+            // end of a softmax (tile w, KV tile i) is followed by that group reading its next
+            // scores, which lets the OTHER tile's next scores be computed, and by P_w(i) V_i.
+            int fills = 0, k_known = -1, v_known = -1;
+            auto fill = [&](int w, int j) {
+                if (!ok) return;
+                if (fills > 0) { named_sync(kBarSFree, 160); if (*abort_flag) { ok = false; return; } }
+                if (j > k_known) {
+                    if (!(ok = mbar_wait(&sm.k_full[j % kKSlots], (j / kKSlots) & 1, abort_flag))) return;
+                    k_known = j;
                 }
-                if (bits & 2u) { issue_pv(0, jp0); v_known = max(v_known, jp0); jp0++; }
-                if (bits & 4u) { issue_pv(1, jp1); v_known = max(v_known, jp1); jp1++; }
-                if (bits & 6u) {
-                    // V_j goes back to the producer once both tiles' products with it are issued
-                    while (j_rel < nmax && (jp0 > j_rel || j_rel >= n0) && (jp1 > j_rel || j_rel >= n1)) {
-                        tc_commit_if(leader, &sm.v_empty[j_rel % kVSlots]);
-                        j_rel++;
-                    }
+                issue_fill(w, j);
+                fills++;
+            };
+            auto pv = [&](int w, int j) {
+                if (!ok) return;
+                named_sync(kBarPReady + w, 160);
+                if (*abort_flag) { ok = false; return; }
+                if (j > v_known) {
+                    if (!(ok = mbar_wait(&sm.v_full[j % kVSlots], (j / kVSlots) & 1, abort_flag))) return;
+                    v_known = j;
                 }
-                if (bits) { idle = 0; continue; }
-                // nothing ready: bounded
-                if ((++idle & 63u) == 0u) {
-                    if (*abort_flag) { ok = false; break; }
-                    const uint64_t now = globaltimer_ns();
-                    if (idle == 64u) t_idle = now;
-                    else if (now - t_idle > 2000000000ull) { *abort_flag = 1; ok = false; break; }
-                }
+                issue_pv(w, j);
+            };
+            if (0 < n0) fill(0, 0);
+            if (0 < n1) fill(1, 0);
+            if (1 < n0) fill(0, 1);
+            for (int i = 0; ok && i < nmax; i++) {
+                // tile 0 finished the softmax of KV tile i and took S_0(i+1) out of TMEM
+                if (i + 1 < n1) fill(1, i + 1);
+                if (i < n0) pv(0, i);
+                // look ahead (the answers come back while this warp sits in the next barrier)
+                if (i + 2 < nmax && i + 2 > k_known && mbar_test(&sm.k_full[(i + 2) % kKSlots], ((i + 2) / kKSlots) & 1)) k_known = i + 2;
+                // tile 1 finished the softmax of KV tile i and took S_1(i+1) out of TMEM
+                if (i + 2 < n0) fill(0, i + 2);
+                if (i < n1) pv(1, i);
+                if (ok) tc_commit_if(leader, &sm.v_empty[i % kVSlots]);
+                if (i + 1 < nmax && i + 1 > v_known && mbar_test(&sm.v_full[(i + 1) % kVSlots], ((i + 1) / kVSlots) & 1)) v_known = i + 1;
             }
             // every MMA issued by this warp has completed once this commit arrives
             tc_commit_if(leader, &sm.drain);
@@ -377,19 +363,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             // the scores are in registers: the other tile's next scores may take their place
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.s_free);
+            named_arrive(kBarSFree, 160);
 
+            // the diagonal tile: columns past the row's own position drop out (exp2(-inf) = 0); every
+            // other tile goes straight to the unmasked code below
+            if (masked) {
+#pragma unroll
+                for (int i = 0; i < 128; i++)
+                    if (col0 + i > qrow) v[i] = 0xff800000u;
+            }
             // row maximum of the raw scores, four independent chains
             float mx;
-            if (masked) {
-                float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-                for (int i = 0; i < 128; i += 2) {
-                    if (col0 + i <= qrow) m0 = fmaxf(m0, __uint_as_float(v[i]));
-                    if (col0 + i + 1 <= qrow) m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
-                }
-                mx = fmaxf(m0, m1);
-            } else {
+            {
                 float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 128; i += 8) {
@@ -428,7 +413,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 tc_wait_st();
             }
 
-            // P = exp2(S*c - m_ref) as bf16 pairs, written over the first 64 columns of S
+            // P = exp2(S*c - m_ref) as bf16 pairs, for the tile's own P columns
             const float neg_m = -m_ref;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
             uint32_t pk[64];
@@ -442,7 +427,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     x[u] = fmaf(__uint_as_float(v[i + u]), c, neg_m);
-                    if (masked && col0 + i + u > qrow) x[u] = -INFINITY;
                     e[u] = ex2(x[u]);
                 }
                 sum0 += e[0]; sum1 += e[1]; sum2 += e[2]; sum3 += e[3];
@@ -460,10 +444,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             tmem_st32(p_addr + 32, pk + 32);
             tc_wait_st();
             tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.p_ready[w]);     // one arrival per warp
+            named_arrive(kBarPReady + w, 160);
         }
 
+        if (!ok) {
+            // giving up: the issuing warp may sit in one of the named barriers this group feeds;
+            // let it through (it looks at the abort flag behind every barrier)
+            named_arrive(kBarSFree, 160);
+            named_arrive(kBarPReady + w, 160);
+        }
         // epilogue: O / l -> bf16 -> global
         if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_full[w], 0, abort_flag));
         if (ok && n > 0) {

@@ -70,6 +70,9 @@ __device__ __forceinline__ uint32_t mbar_test6(const uint32_t (&bar)[6], const u
         : "memory");
     return mask;
 }
+// named hardware barriers of the CTA: arrive does not block, sync does
+__device__ __forceinline__ void named_arrive(int id, int count) { asm volatile("barrier.cta.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void named_sync(int id, int count) { asm volatile("barrier.cta.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
