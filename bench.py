@@ -363,7 +363,10 @@ def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
     sampler = ClockSampler(dist.local)
     with sampler:
         ms = timed_steps(torch, step, args.steps, args.warmup, flush, dist)
-        # sustained: about two seconds of back-to-back steps (one rotation over the replicas per graph)
+    # sustained: about two seconds of back-to-back steps (one rotation over the replicas per graph),
+    # with its own clock record: a long loop meets the power cap, the short timed region does not
+    sus_sampler = ClockSampler(dist.local)
+    with sus_sampler:
         sus_ms, sus_steps = sustained_loop(torch, eager_step if not graphed else step, sum(ms) / len(ms), dist,
                                            seconds=args.sustain, unit_steps=1 if graphed else len(w["kcs"]),
                                            capture=not graphed) \
@@ -459,7 +462,8 @@ def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
         line["sustained"] = {"ms_per_step": round(sus_ms, 5), "steps": sus_steps,
                              "value": round(total_bytes / (sus_ms / 1e3) / 1e9, 2), "unit": "GB/s",
                              "frac": round(float(w["bytes"]) / (sus_ms / 1e3) / 1e9 / pk["hbm"], 4),
-                             "how": "back-to-back steps for about two seconds, replayed as a CUDA graph, one event pair"}
+                             "how": "back-to-back steps for about two seconds, replayed as a CUDA graph, one event pair",
+                             "clocks": sus_sampler.summary()}
     if e2e is not None:
         line["e2e"] = e2e
     if paged is not None:
@@ -505,6 +509,8 @@ def run_prefill(args, dist, with_e2e=True, with_cpu=True):
     sampler = ClockSampler(dist.local)
     with sampler:
         ms = timed_steps(torch, step, args.steps, args.warmup, flush, dist)
+    sus_sampler = ClockSampler(dist.local)      # the long loop meets the power cap: its own clock record
+    with sus_sampler:
         sus_ms, sus_steps = sustained_loop(torch, step, sum(ms) / len(ms), dist, seconds=args.sustain, capture=False) \
             if args.sustain > 0 else (None, 0)
     t_max = dist.max(sum(ms) / 1e3)
@@ -535,7 +541,7 @@ def run_prefill(args, dist, with_e2e=True, with_cpu=True):
         line["sustained"] = {"ms_per_step": round(sus_ms, 4), "steps": sus_steps,
                              "value": round(flops_rank * dist.world / (sus_ms / 1e3) / 1e12, 2), "unit": "TFLOP/s",
                              "frac_of_sustained_peak": round(flops_rank / (sus_ms / 1e3) / 1e12 / pk["bf16_sustained"], 4),
-                             "how": "back-to-back steps for about two seconds, one event pair"}
+                             "how": "back-to-back steps for about two seconds, one event pair", "clocks": sus_sampler.summary()}
     if with_e2e:
         # end to end: pinned host q/k/v -> device, attention, result back to pinned host
         hq_, hk_, hv_ = (torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v))

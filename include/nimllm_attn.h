@@ -120,6 +120,17 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
                        int n_kv_head, int head_dim, float scale, int chunk_rows,
                        void *workspace, size_t workspace_bytes, void *stream);
 
+/* How the library's own split (chunk_rows = 0, bf16 cache) would cut a batch, computed on the
+ * host with the arithmetic the kernels use; no GPU involved.  The batch is one list of row units
+ * (`unit` rows: 32 at head_dim 64, 16 at 128) ordered by sequence, KV head, row, cut into equal
+ * spans for `warps` workers.  segs_out receives 6 ints per segment (worker, sequence, KV head,
+ * first unit, end unit, record slot or -1 when the worker covers the whole (sequence, KV head)
+ * pair), pairs_out (optional) 3 ints per pair (first worker, pieces, slot of the first piece).
+ * Returns the number of segments, or -1 when max_segs is too small or an argument is bad.
+ * No counterpart in the reference. */
+int nimllm_attn_decode_plan(const int32_t *lens, int batch, int n_kv_head, int unit, int warps,
+                            int32_t *segs_out, int max_segs, int32_t *pairs_out);
+
 /* ---- decode over a paged KV cache ---------------------------------------------------------
  * No counterpart in the reference, whose cache is one buffer per (layer, KV head)
  * (src/model.nim:729-739); this is the block-managed cache its chat loop's multi-turn reuse
@@ -246,9 +257,19 @@ int nimllm_attn_wait_combine(nimllm_peer_exchange *x, int rows, void *out, int o
  *   lse      optional fp32 [B, Hq, S]: log-sum-exp of the scaled scores per row
  *   dtype F32 runs on the CUDA cores in fp32 (the <= 1e-4 parity path); BF16 runs
  *   QK^T and PV on the tcgen05 tensor cores with fp32 accumulation.
+ *   workspace: nimllm_attn_prefill_workspace_bytes(...) bytes (currently 0: NULL is accepted)
+ *
+ * The bf16 kernel's internal waits are bounded (about 2 s without progress); a launch in which
+ * one gave up leaves incomplete results in out / lse and raises a per-device status word that
+ * stays raised until it is cleared:
+ *   nimllm_attn_prefill_status(reset)  returns 0 (every bf16 prefill since the last reset ran to
+ *            completion), 1 (one did not), or a negative NIMLLM_ERR_* code; reset != 0 clears the
+ *            word.  It synchronises the device, so call it where the host waits for results anyway
+ *            (after a forward pass, before sampling), not per layer.
  */
 size_t nimllm_attn_prefill_workspace_bytes(int batch, int seq_len, int n_head, int n_kv_head,
                                            int head_dim, int dtype);
+int nimllm_attn_prefill_status(int reset);
 int nimllm_attn_prefill(void *q, void *k, const void *v, int dtype, const float *rope_cos,
                         const float *rope_sin, int pos0, void *out, int batch, int seq_len,
                         int n_head, int n_kv_head, int head_dim, float scale, int save_cache,

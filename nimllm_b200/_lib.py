@@ -33,6 +33,7 @@ PROTOTYPES = {
                                  i32, i32, i32, i32, i32, i32, vp]),
     "nimllm_rope_append_paged": (i32, [vp, i32, vp, vp, i32, i32, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32,
                                        i32, i32, i32, i32, vp]),
+    "nimllm_attn_decode_plan": (i32, [vp, i32, i32, i32, i32, vp, i32, vp]),
     "nimllm_attn_decode_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "nimllm_attn_decode": (i32, [vp, i32, vp, vp, i32, vp, i64, i64, vp, i32, vp, i32, vp, i32, i32, i32,
                                  i32, f32, i32, vp, sz, vp]),
@@ -54,6 +55,7 @@ PROTOTYPES = {
     "nimllm_attn_decode_push": (i32, [vp, vp, i32, vp, vp, vp, i64, i64, vp, i32, i32, i32, i32, i32, f32, vp, sz, vp]),
     "nimllm_attn_wait_combine": (i32, [vp, i32, vp, i32, vp, vp]),
     "nimllm_attn_prefill_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
+    "nimllm_attn_prefill_status": (i32, [i32]),
     "nimllm_attn_prefill": (i32, [vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, f32, i32,
                                   vp, vp, i32, vp, i64, i64, i32, vp, vp, sz, vp]),
     "nimllm_attn_prefill_bwd_workspace_bytes": (sz, [i32, i32, i32, i32]),
@@ -69,14 +71,6 @@ PROTOTYPES = {
     "gpu_flash_attn_fwd": (None, [vp, vp, vp, vp, i32, i32, f32, i32]),
 }
 
-# testing hooks exported by the library but not part of include/nimllm_attn.h
-_EXTRA = {
-    "nimllm_attn_debug_force_decode_kernel": (None, [i32]),
-    "nimllm_attn_debug_balanced_plan": (i32, [vp, i32, i32, i32, i32, vp, i32, vp]),
-    "nimllm_attn_debug_prefill_variant": (None, [i32]),
-}
-
-
 class NimllmAttnError(RuntimeError):
     pass
 
@@ -89,7 +83,7 @@ def lib() -> C.CDLL:
                 f"{LIB_PATH} is missing: build it with `python -m nimllm_b200.build` "
                 "(nvcc, sm_100a). There is no fallback path.")
         L = C.CDLL(LIB_PATH)
-        for name, (res, args) in {**PROTOTYPES, **_EXTRA}.items():
+        for name, (res, args) in PROTOTYPES.items():
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args

@@ -186,6 +186,15 @@ def attn_forward(q, k, v, cos, sin, *, n_head, n_kv_head, head_dim, pos0=0, save
     return out[0] if squeeze else out
 
 
+def prefill_status(reset: bool = True) -> int:
+    """0 when every bf16 prefill launch on the current device since the last reset ran to
+    completion, 1 when a bounded wait inside one gave up (its outputs are incomplete).  Synchronises."""
+    rc = lib().nimllm_attn_prefill_status(int(reset))
+    if rc < 0:
+        check(-rc)
+    return rc
+
+
 def attn_backward(q_rot, k_rot, v, out, dout, lse, cos, sin, *, n_head, n_kv_head, head_dim, pos0=0, scale=None):
     """Backward of the causal attention block (fp32): returns (dq, dk, dv) in the pre-RoPE space.
     q_rot / k_rot are the rotated activations attn_forward(save_cache=True) left, lse its row

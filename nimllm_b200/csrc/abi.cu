@@ -175,7 +175,8 @@ int nimllm_rope_append_paged(void *q, int n_head, void *k_new, const void *v_new
 
 size_t nimllm_attn_prefill_workspace_bytes(int batch, int seq_len, int n_head, int n_kv_head,
                                            int head_dim, int dtype) {
-    if (dtype == NIMLLM_BF16) return prefill_tc_workspace_bytes(batch, seq_len, n_head, n_kv_head, head_dim);
+    // neither path needs scratch memory (kept in the interface so that a future kernel may ask for some)
+    (void)batch; (void)seq_len; (void)n_head; (void)n_kv_head; (void)head_dim; (void)dtype;
     return 0;
 }
 
@@ -216,11 +217,15 @@ int nimllm_attn_prefill(void *q, void *k, const void *v, int dtype, const float 
                                     seq_len, n_kv_head, head_dim, stream);
         if (rc) return rc;
     }
-    if (g_prefill_variant == 2)
-        return launch_prefill_tc2(q, k, v, out, lse, rope_cos, rope_sin, pos0, save_cache ? 1 : 0, batch, seq_len,
-                             n_head, n_kv_head, head_dim, scale, workspace, workspace_bytes, st);
+    (void)workspace; (void)workspace_bytes;
     return launch_prefill_tc(q, k, v, out, lse, rope_cos, rope_sin, pos0, save_cache ? 1 : 0, batch, seq_len,
-                             n_head, n_kv_head, head_dim, scale, workspace, workspace_bytes, st);
+                             n_head, n_kv_head, head_dim, scale, st);
+}
+
+int nimllm_attn_prefill_status(int reset) {
+    int st = 0;
+    const int rc = prefill_tc_status(reset, &st);
+    return rc ? -rc : st;
 }
 
 }  // extern "C"

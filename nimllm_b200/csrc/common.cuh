@@ -136,18 +136,11 @@ int launch_prefill_f32(const float *q, const float *k, const float *v, float *ou
                        int B, int S, int Hq, int Hkv, int D, float scale, int causal,
                        cudaStream_t st);
 
-size_t prefill_tc_workspace_bytes(int B, int S, int Hq, int Hkv, int D);
 int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *lse,
                       const float *cos_tab, const float *sin_tab, int pos0, int write_back_q,
-                      int B, int S, int Hq, int Hkv, int D, float scale, void *workspace,
-                      size_t workspace_bytes, cudaStream_t st);
+                      int B, int S, int Hq, int Hkv, int D, float scale, cudaStream_t st);
 
-// the same on CTA pairs (tcgen05 cta_group::2); prefill_variant: 1 one CTA per 256 query rows, 2 pairs
-int launch_prefill_tc2(void *q, const void *k, const void *v, void *out, float *lse,
-                       const float *cos_tab, const float *sin_tab, int pos0, int write_back_q,
-                       int B, int S, int Hq, int Hkv, int D, float scale, void *workspace,
-                       size_t workspace_bytes, cudaStream_t st);
-extern int g_prefill_variant;
+int prefill_tc_status(int reset, int *status_out);
 
 }  // namespace nimllm
 

@@ -985,8 +985,6 @@ __global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
     }
 }
 
-int g_force_kernel = 0;  // 0 auto, 1 generic, 2 mma on the chunk grid, 3 balanced mma (testing hook)
-
 int auto_chunk_rows(int B, int Hkv, int max_len);
 
 // launch shape of the balanced kernel: a grid that fills the GPU exactly once
@@ -1103,14 +1101,12 @@ using namespace nimllm;
 
 extern "C" {
 
-void nimllm_attn_debug_force_decode_kernel(int which) { g_force_kernel = which; }
-
-// Host-side replay of the balanced kernel's work split (testing hook, no GPU needed): the same
+// Host-side replay of the balanced kernel's work split (no GPU needed): the same
 // walk and merge arithmetic the kernels run, for `warps` workers over sequences of `lens` rows.
 // segs_out receives (warp, sequence, kv head, first unit, end unit, slot or -1 for a whole pair)
 // per segment, pairs_out (first warp, pieces, slot of the first piece) per (sequence, KV head);
 // returns the number of segments, or -1 when max_segs is too small.
-int nimllm_attn_debug_balanced_plan(const int32_t *lens, int batch, int n_kv_head, int unit, int warps,
+int nimllm_attn_decode_plan(const int32_t *lens, int batch, int n_kv_head, int unit, int warps,
                                     int32_t *segs_out, int max_segs, int32_t *pairs_out) {
     if (!lens || batch <= 0 || n_kv_head <= 0 || unit <= 0 || warps <= 0) return -1;
     int *cum_v = new int[batch + 1];
@@ -1182,13 +1178,10 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
     const bool mma_ok = cache_dtype == NIMLLM_BF16 && n_head / n_kv_head <= 8;
     // The balanced kernel is the default for a bf16 cache when the caller leaves the chunking to
     // the library and the workspace holds its records; an explicit chunk_rows keeps the chunk grid.
-    const size_t bal_need = (mma_ok && chunk_rows == 0 && g_force_kernel != 1 && g_force_kernel != 2)
+    const size_t bal_need = (mma_ok && chunk_rows == 0)
                                 ? bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, seq_len != nullptr)
                                 : 0;
     const bool balanced = bal_need > 0 && workspace && workspace_bytes >= bal_need && !((uintptr_t)workspace & 15);
-    if (g_force_kernel == 3 && !balanced)
-        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: the balanced kernel needs a bf16 cache, Hq/Hkv <= 8, "
-                                            "chunk_rows = 0 and a workspace of %zu bytes", bal_need);
     if (chunk_rows == 0) chunk_rows = auto_chunk_rows(batch, n_kv_head, max_len);
     const int max_chunks = (max_len + chunk_rows - 1) / chunk_rows;
     const size_t need = balanced ? bal_need : split_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, chunk_rows);
@@ -1212,10 +1205,7 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
                                          max_len, workspace, st);
 
     dim3 grid(max_chunks, n_kv_head, batch);
-    if (g_force_kernel == 2 && !mma_ok)
-        return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: mma kernel needs a bf16 cache and Hq/Hkv <= 8");
-    const bool use_mma = mma_ok && g_force_kernel != 1;
-    if (use_mma) {
+    if (mma_ok) {
         // D = 64: one 8-warp CTA per SM (8 KiB in flight per warp, finer tail than two 4-warp
         // CTAs: measured 0.790 vs 0.783 of the HBM peak on the ragged batch); D = 128: two
         // 4-warp CTAs per SM

@@ -47,6 +47,11 @@ namespace {
 
 using namespace tc;
 
+// Sticky per-device status of the bf16 prefill: becomes 1 when a bounded wait inside a launch gave
+// up (the outputs of that launch are then incomplete) and stays 1 until the host clears it through
+// nimllm_attn_prefill_status.
+__device__ int g_prefill_status = 0;
+
 constexpr int kBM = 128;           // query rows per tile (= TMEM lanes)
 constexpr int kBN = 128;           // KV rows per tile
 constexpr int kKSlots = 3;          // ring of K tiles
@@ -66,7 +71,7 @@ template <int kD> struct Smem {
     uint8_t k[kKSlots][tile_bytes<kD>()];
     uint8_t v[kVSlots][tile_bytes<kD>()];
     uint64_t q_full, k_full[kKSlots], k_empty[kKSlots], v_full[kVSlots], v_empty[kVSlots];
-    uint64_t s_full[2], s_free, p_ready[2], pv_done[2], o_full[2], drain;
+    uint64_t s_full[2], pv_done[2], o_full[2], drain;
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -76,7 +81,6 @@ struct PrefillParams {
     __nv_bfloat16 *out;      // [B, S, Hq*D]
     float *lse;              // [B, Hq, S] or null
     const float *cos_tab, *sin_tab;  // rows pos0.. used when rotate_q
-    int *status;             // device status word: 0 ok, 1 a bounded wait gave up
     int B, S, Hq, Hkv, pos0;
     int rotate_q;            // 1: stage Q through registers with RoPE; 0: Q is loaded by TMA
     int write_back_q;        // with rotate_q: also store the rotated Q to global
@@ -119,10 +123,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         for (int s = 0; s < kKSlots; s++) { mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1); }
         for (int s = 0; s < kVSlots; s++) { mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1); }
         for (int w = 0; w < 2; w++) {
-            mbar_init(&sm.s_full[w], 1); mbar_init(&sm.p_ready[w], 4); mbar_init(&sm.pv_done[w], 1);
+            mbar_init(&sm.s_full[w], 1); mbar_init(&sm.pv_done[w], 1);
             mbar_init(&sm.o_full[w], 1);
         }
-        mbar_init(&sm.s_free, 4);
         mbar_init(&sm.drain, 1);
         sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -487,7 +490,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && sm.abort_flag) atomicExch(p.status, 1);
+    if (threadIdx.x == 0 && sm.abort_flag) atomicExch(&g_prefill_status, 1);
     if (warp == 9) {
         __syncwarp();
         tc_fence_after();
@@ -527,17 +530,31 @@ int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols) {
     return NIMLLM_OK;
 }
 
-}  // namespace
+// The descriptors of the most recent operands are kept (a model's layers call with the same few
+// buffers again and again): a hit costs a lookup instead of three driver calls.
+struct MapKey { const void *base; uint64_t rows, cols; };
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+thread_local MapSlot g_maps[8];
+thread_local int g_map_next = 0;
 
-// status word (4 bytes) + optional debug area
-size_t prefill_tc_workspace_bytes(int, int, int, int, int) { return 256; }
-
-namespace {
+int cached_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols) {
+    for (int i = 0; i < 8; i++)
+        if (g_maps[i].used && g_maps[i].key.base == base && g_maps[i].key.rows == rows && g_maps[i].key.cols == cols) {
+            *map = g_maps[i].map;
+            return NIMLLM_OK;
+        }
+    const int rc = make_map(map, base, rows, cols);
+    if (rc) return rc;
+    MapSlot &s = g_maps[g_map_next];
+    g_map_next = (g_map_next + 1) % 8;
+    s.key = MapKey{base, rows, cols}; s.map = *map; s.used = true;
+    return NIMLLM_OK;
+}
 
 template <int kD>
 int launch_prefill_tc_d(void *q, const void *k, const void *v, void *out, float *lse, const float *cos_tab,
                         const float *sin_tab, int pos0, int write_back_q, int B, int S, int Hq, int Hkv,
-                        float scale, void *workspace, cudaStream_t st) {
+                        float scale, cudaStream_t st) {
     static bool attr_set[64] = {false};
     const size_t smem_bytes = sizeof(Smem<kD>) + 1024;
     int dev = 0;
@@ -550,21 +567,18 @@ int launch_prefill_tc_d(void *q, const void *k, const void *v, void *out, float 
 
     CUtensorMap q_map, k_map, v_map;
     int rc;
-    if ((rc = make_map(&q_map, q, (uint64_t)B * S, (uint64_t)Hq * kD))) return rc;
-    if ((rc = make_map(&k_map, k, (uint64_t)B * S, (uint64_t)Hkv * kD))) return rc;
-    if ((rc = make_map(&v_map, v, (uint64_t)B * S, (uint64_t)Hkv * kD))) return rc;
+    if ((rc = cached_map(&q_map, q, (uint64_t)B * S, (uint64_t)Hq * kD))) return rc;
+    if ((rc = cached_map(&k_map, k, (uint64_t)B * S, (uint64_t)Hkv * kD))) return rc;
+    if ((rc = cached_map(&v_map, v, (uint64_t)B * S, (uint64_t)Hkv * kD))) return rc;
 
     PrefillParams p;
     p.q = (__nv_bfloat16 *)q; p.out = (__nv_bfloat16 *)out; p.lse = lse;
     p.cos_tab = cos_tab; p.sin_tab = sin_tab;
-    p.status = (int *)workspace;
     p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.pos0 = pos0;
     p.rotate_q = cos_tab ? 1 : 0;
     p.write_back_q = write_back_q;
     p.scale_log2e = scale * kLog2e;
 
-    cudaError_t e = cudaMemsetAsync(workspace, 0, 4, st);
-    if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill bf16: %s", cudaGetErrorString(e));
     const int n_pairs = (S + 2 * kBM - 1) / (2 * kBM);
     dim3 grid((unsigned)n_pairs * Hq * B);
     prefill_tc_kernel<kD><<<grid, kThreads, smem_bytes, st>>>(q_map, k_map, v_map, p);
@@ -576,16 +590,29 @@ int launch_prefill_tc_d(void *q, const void *k, const void *v, void *out, float 
 
 int launch_prefill_tc(void *q, const void *k, const void *v, void *out, float *lse, const float *cos_tab,
                       const float *sin_tab, int pos0, int write_back_q, int B, int S, int Hq, int Hkv, int D,
-                      float scale, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+                      float scale, cudaStream_t st) {
     if (D != 64 && D != 128)
         return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: head_dim %d (the tensor-core kernel is built for 64 and 128)", D);
-    if (!workspace || workspace_bytes < 256) return fail(NIMLLM_ERR_WORKSPACE, "attn_prefill bf16: workspace %zu bytes, need 256", workspace_bytes);
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
         return fail(NIMLLM_ERR_ARG, "attn_prefill bf16: q, k, v, out must be 16-byte aligned");
     if ((int64_t)B * S > 0x7fffffff) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_prefill bf16: B*S too large");
     if (D == 64)
-        return launch_prefill_tc_d<64>(q, k, v, out, lse, cos_tab, sin_tab, pos0, write_back_q, B, S, Hq, Hkv, scale, workspace, st);
-    return launch_prefill_tc_d<128>(q, k, v, out, lse, cos_tab, sin_tab, pos0, write_back_q, B, S, Hq, Hkv, scale, workspace, st);
+        return launch_prefill_tc_d<64>(q, k, v, out, lse, cos_tab, sin_tab, pos0, write_back_q, B, S, Hq, Hkv, scale, st);
+    return launch_prefill_tc_d<128>(q, k, v, out, lse, cos_tab, sin_tab, pos0, write_back_q, B, S, Hq, Hkv, scale, st);
+}
+
+// Reads (and with reset != 0 clears) the sticky status word of the current device.  Synchronises
+// the device: call it where the host waits for results anyway.
+int prefill_tc_status(int reset, int *status_out) {
+    int st = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&st, g_prefill_status, sizeof(int));
+    if (e == cudaSuccess && reset && st != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_prefill_status, &zero, sizeof(int));
+    }
+    if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill_status: %s", cudaGetErrorString(e));
+    *status_out = st;
+    return NIMLLM_OK;
 }
 
 }  // namespace nimllm

@@ -1,4 +1,4 @@
-// tcgen05.cuh -- inline-PTX helpers shared by the tensor-core prefill kernels (sm_100a):
+// tcgen05.cuh -- inline-PTX helpers of the tensor-core prefill kernel (sm_100a):
 // mbarriers with bounded waits, TMA tile loads, tcgen05 MMA / commit / TMEM load-store, the
 // shared-memory and instruction descriptors, and the swizzled tile addressing they agree on.
 #pragma once
@@ -45,30 +45,6 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
         : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
-}
-// Six non-blocking looks issued back to back (one shared-memory round trip for all of them
-// instead of six in a row); bit i of the result = phase `par[i]` of barrier `bar[i]` completed.
-__device__ __forceinline__ uint32_t mbar_test6(const uint32_t (&bar)[6], const uint32_t (&par)[6]) {
-    uint32_t mask;
-    asm volatile(
-        "{\n\t.reg .pred p0, p1, p2, p3, p4, p5;\n\t.reg .u32 t;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p0, [%1], %7;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p1, [%2], %8;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p2, [%3], %9;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p3, [%4], %10;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p4, [%5], %11;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p5, [%6], %12;\n\t"
-        "selp.u32 %0, 1, 0, p0;\n\t"
-        "selp.u32 t, 2, 0, p1;\n\tor.b32 %0, %0, t;\n\t"
-        "selp.u32 t, 4, 0, p2;\n\tor.b32 %0, %0, t;\n\t"
-        "selp.u32 t, 8, 0, p3;\n\tor.b32 %0, %0, t;\n\t"
-        "selp.u32 t, 16, 0, p4;\n\tor.b32 %0, %0, t;\n\t"
-        "selp.u32 t, 32, 0, p5;\n\tor.b32 %0, %0, t;\n\t}"
-        : "=r"(mask)
-        : "r"(bar[0]), "r"(bar[1]), "r"(bar[2]), "r"(bar[3]), "r"(bar[4]), "r"(bar[5]),
-          "r"(par[0]), "r"(par[1]), "r"(par[2]), "r"(par[3]), "r"(par[4]), "r"(par[5])
-        : "memory");
-    return mask;
 }
 // named hardware barriers of the CTA: arrive does not block, sync does
 __device__ __forceinline__ void named_arrive(int id, int count) { asm volatile("barrier.cta.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
@@ -218,64 +194,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
-}
-
-// ------------------------------------------------------------------ CTA-pair (cta_group::2) forms
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// shared::cluster address of the same shared-memory object in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(const void *p, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
-    return r;
-}
-// Arrival on a barrier that may live in the pair's other CTA.  Default (CTA-scope release)
-// semantics: what is handed over is TMEM / async-proxy state ordered by the tcgen05 fences around
-// the barrier, not generic-proxy global memory; a cluster-scope release here was measured to cost
-// several hundred cycles per hand-over.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// TMA tile load of a CTA pair: the bytes land in this CTA's shared memory, the transaction is
-// counted on the barrier `bar_cluster_addr`, which may live in the pair's other CTA.  No multicast.
-__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
-        : "memory");
-}
-// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs
-// issued so far have completed
-__device__ __forceinline__ void tc_commit_pair(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
-}
-// ... on this CTA's barrier only
-__device__ __forceinline__ void tc_commit_pair_local(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// D[tmem of both CTAs] (+)= A[smem, 128 rows per CTA] * B[smem, N/2 per CTA]
-__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// D[tmem] (+)= A[tmem, each CTA its 128 rows] * B[smem, N/2 per CTA]
-__device__ __forceinline__ void mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
 }
 
 }  // namespace tc

@@ -95,6 +95,8 @@ int attnForwardCached(const ModelShape &m, KvCache &kv, int li, GpuBuf q, GpuBuf
                               m.headDim, scale, 0, ws, wsBytes, nullptr);
 }
 
+int prefillStatus(bool reset) { return nimllm_attn_prefill_status(reset ? 1 : 0); }
+
 std::string lastError() { return nimllm_attn_last_error(); }
 
 }  // namespace nimllm

@@ -72,6 +72,11 @@ int attnForward(const ModelShape &m, GpuBuf q, GpuBuf k, GpuBuf v, GpuBuf ropeCo
 int attnForwardCached(const ModelShape &m, KvCache &kv, int li, GpuBuf q, GpuBuf kNew, GpuBuf vNew,
                       GpuBuf ropeCos, GpuBuf ropeSin, GpuBuf attnOut, Arena &arena);
 
+// Sticky status of the bf16 tensor-core prefill on the current device (0 ok, 1 a launch gave up on a
+// bounded wait and left incomplete results); synchronises the device.  Call it where the host waits
+// for results anyway -- after a forward pass, before sampling (src/chat.nim:97-101).
+int prefillStatus(bool reset = true);
+
 std::string lastError();
 
 }  // namespace nimllm

@@ -108,7 +108,7 @@ def test_balanced_decode_plan_covers_every_unit_once():
         lens = rng.choice([0, 0, 1, 5, 16, 33, 100, 700, 4096, int(rng.integers(0, 3000))], size=B).astype(np.int32)
         warps = int(rng.choice([8, 37, 1184]))
         segs = np.zeros((20000, 6), np.int32); pairs = np.zeros((B * Hkv, 3), np.int32)
-        n = L.nimllm_attn_debug_balanced_plan(lens.ctypes.data_as(C.c_void_p), B, Hkv, unit, warps,
+        n = L.nimllm_attn_decode_plan(lens.ctypes.data_as(C.c_void_p), B, Hkv, unit, warps,
                                               segs.ctypes.data_as(C.c_void_p), len(segs), pairs.ctypes.data_as(C.c_void_p))
         assert n >= 0
         segs = segs[:n]

@@ -4,27 +4,25 @@ import pytest
 import torch
 
 from gpu_util import bf16_bits, dev, host, ragged_cache
-from nimllm_b200 import _lib, attention as A
+from nimllm_b200 import attention as A
 from oracle import oracle as O
 from util import SEED_C3, SEED_C5, TOL_BF16, TOL_F32, assert_close, normal, rng
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True)
-def _auto_kernel():
-    yield
-    _lib.lib().nimllm_attn_debug_force_decode_kernel(0)
+# Which kernel serves a call follows from its arguments: an fp32 cache or more than 8 query heads
+# per KV head -> the fp32-FMA kernel; a bf16 cache with an explicit chunk_rows -> the mma.sync kernel
+# on the chunk grid; a bf16 cache with chunk_rows = 0 -> the balanced mma.sync kernel.
 
 
-def _run(seed, lens, Hq, Hkv, D, kv_dtype, chunk_rows, force=0, q_dtype=torch.float32, pad_rows=3):
+def _run(seed, lens, Hq, Hkv, D, kv_dtype, chunk_rows, q_dtype=torch.float32, pad_rows=3):
     B = len(lens)
     k, v, off, hs = ragged_cache(seed, lens, Hkv, D, kv_dtype, normal, pad_rows)
     q = normal(seed, 12, (B, Hq * D))
     if q_dtype == torch.bfloat16:
         q = O.from_bf16(O.to_bf16(q))
     scale = 1.0 / np.sqrt(D)
-    _lib.lib().nimllm_attn_debug_force_decode_kernel(force)
     out, rec = A.decode_batch(dev(q, q_dtype), dev(k, kv_dtype), dev(v, kv_dtype), n_head=Hq, n_kv_head=Hkv,
                               head_dim=D, max_len=int(max(max(lens), 1)), seq_len=dev(np.asarray(lens, np.int32)),
                               kv_off=dev(off), head_stride=int(hs[0]), scale=scale, chunk_rows=chunk_rows,
@@ -42,7 +40,7 @@ LENS = [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 200, 255, 256, 257, 300]
 @pytest.mark.parametrize("Hq,Hkv,D", [(9, 3, 64), (8, 2, 128), (4, 4, 64), (2, 1, 128), (16, 2, 64), (5, 1, 64)])
 @pytest.mark.parametrize("chunk_rows", [0, 64, 128])
 def test_generic_fp32_cache_matches_reference_arithmetic(Hq, Hkv, D, chunk_rows):
-    out, rec, ref32, ref64, m, l = _run(101, LENS, Hq, Hkv, D, torch.float32, chunk_rows, force=1)
+    out, rec, ref32, ref64, m, l = _run(101, LENS, Hq, Hkv, D, torch.float32, chunk_rows)
     assert_close(out, ref32, TOL_F32, "decode fp32 vs oracle fp32")
     assert_close(out, ref64, TOL_F32, "decode fp32 vs oracle fp64")
     assert_close(rec[:, :D].reshape(out.shape), ref64, TOL_F32, "partials o")
@@ -50,12 +48,11 @@ def test_generic_fp32_cache_matches_reference_arithmetic(Hq, Hkv, D, chunk_rows)
     np.testing.assert_allclose(rec[:, D] + np.log(rec[:, D + 1]), (m + np.log(l)).reshape(-1), atol=2e-4)
 
 
-@pytest.mark.parametrize("Hq,Hkv,D", [(9, 3, 64), (32, 8, 128), (8, 8, 64), (8, 1, 128), (16, 2, 64)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(9, 3, 64), (32, 8, 128), (8, 8, 64), (8, 1, 128), (16, 2, 64),      # mma.sync kernels
+                                      (18, 2, 64), (16, 1, 128), (9, 1, 64), (20, 2, 128)])                    # > 8 heads per KV head: fp32 FMA
 @pytest.mark.parametrize("chunk_rows", [0, 64, 192])
-@pytest.mark.parametrize("force", [1, 2])
-def test_bf16_cache_matches_f64_ground_truth(Hq, Hkv, D, chunk_rows, force):
-    out, rec, ref32, ref64, m, l = _run(102, LENS, Hq, Hkv, D, torch.bfloat16, chunk_rows, force=force,
-                                        q_dtype=torch.bfloat16)
+def test_bf16_cache_matches_f64_ground_truth(Hq, Hkv, D, chunk_rows):
+    out, rec, ref32, ref64, m, l = _run(102, LENS, Hq, Hkv, D, torch.bfloat16, chunk_rows, q_dtype=torch.bfloat16)
     assert_close(out, ref64, TOL_BF16, "decode bf16 vs fp64 ground truth")
     np.testing.assert_allclose(rec[:, D] + np.log(rec[:, D + 1]), (m + np.log(l)).reshape(-1), atol=3e-2)
 
@@ -69,7 +66,7 @@ def test_balanced_kernel_matches_f64_ground_truth(Hq, Hkv, D, lens):
     """The balanced kernel cuts the flattened batch into equal spans per warp: pieces of a pair
     held by several warps, whole pairs inside one warp, empty sequences and warps with nothing
     to do all occur in these cases."""
-    out, rec, ref32, ref64, m, l = _run(106, lens, Hq, Hkv, D, torch.bfloat16, 0, force=3, q_dtype=torch.bfloat16)
+    out, rec, ref32, ref64, m, l = _run(106, lens, Hq, Hkv, D, torch.bfloat16, 0, q_dtype=torch.bfloat16)
     assert_close(out, ref64, TOL_BF16, "balanced decode vs fp64 ground truth")
     assert_close(rec[:, :D].reshape(out.shape), out, 1e-6, "records carry the output")
     live = np.repeat(np.asarray(lens) > 0, Hq)
@@ -77,22 +74,16 @@ def test_balanced_kernel_matches_f64_ground_truth(Hq, Hkv, D, lens):
     assert not out[~(np.asarray(lens) > 0)].any() and not rec[~live, D + 1].any()
 
 
-def test_balanced_kernel_uniform_cache_and_refusals():
+def test_balanced_kernel_uniform_cache():
     Hq, Hkv, D, B, L, cap = 8, 2, 128, 5, 1000, 1024
     kv = O.from_bf16(O.to_bf16(normal(107, 0, (2, B, Hkv, cap, D))))
     q = O.from_bf16(O.to_bf16(normal(107, 1, (B, Hq * D))))
-    _lib.lib().nimllm_attn_debug_force_decode_kernel(3)
     kw = dict(n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=L, seq_stride=Hkv * cap * D, head_stride=cap * D)
     out = A.decode_batch(dev(q, torch.bfloat16), dev(kv[0], torch.bfloat16), dev(kv[1], torch.bfloat16), **kw)
     off = np.arange(B, dtype=np.int64) * Hkv * cap * D
     ref = O.decode_batch(q, kv[0].reshape(-1), kv[1].reshape(-1), off, np.full(B, cap * D, np.int64),
                          np.full(B, L, np.int32), Hq, Hkv, D, 1.0 / np.sqrt(D), acc64=True)
     assert_close(host(out), ref, TOL_BF16, "balanced, seq_len = NULL")
-    # an explicit chunking or an fp32 cache keeps the chunk grid: forcing the balanced kernel is refused
-    with pytest.raises(RuntimeError):
-        A.decode_batch(dev(q, torch.bfloat16), dev(kv[0], torch.bfloat16), dev(kv[1], torch.bfloat16), chunk_rows=64, **kw)
-    with pytest.raises(RuntimeError):
-        A.decode_batch(dev(q), dev(kv[0]), dev(kv[1]), **kw)
 
 
 def test_mma_kernel_is_tight_when_p_is_exact():
@@ -102,25 +93,24 @@ def test_mma_kernel_is_tight_when_p_is_exact():
     lens = [1] * 6
     k, v, off, hs = ragged_cache(103, lens, Hkv, D, torch.bfloat16, normal, 0)
     q = normal(103, 12, (6, Hq * D))
-    _lib.lib().nimllm_attn_debug_force_decode_kernel(2)
-    out = A.decode_batch(dev(q), dev(k, torch.bfloat16), dev(v, torch.bfloat16), n_head=Hq, n_kv_head=Hkv,
-                         head_dim=D, max_len=1, seq_len=dev(np.asarray(lens, np.int32)), kv_off=dev(off),
-                         head_stride=int(hs[0]))
-    out = host(out).reshape(6, Hq, D)
-    for b in range(6):
-        for h in range(Hq):
-            np.testing.assert_array_equal(out[b, h], v[off[b] + (h // 4) * hs[b]: off[b] + (h // 4) * hs[b] + D])
+    for chunk_rows in (64, 0):                                   # chunk grid, balanced
+        out = A.decode_batch(dev(q), dev(k, torch.bfloat16), dev(v, torch.bfloat16), n_head=Hq, n_kv_head=Hkv,
+                             head_dim=D, max_len=1, seq_len=dev(np.asarray(lens, np.int32)), kv_off=dev(off),
+                             head_stride=int(hs[0]), chunk_rows=chunk_rows)
+        out = host(out).reshape(6, Hq, D)
+        for b in range(6):
+            for h in range(Hq):
+                np.testing.assert_array_equal(out[b, h], v[off[b] + (h // 4) * hs[b]: off[b] + (h // 4) * hs[b] + D])
 
 
 def test_zero_length_and_missing_seq_len():
     Hq, Hkv, D = 9, 3, 64
     lens = [0, 5, 0, 70]
-    for force, dt in [(1, torch.float32), (2, torch.bfloat16)]:
-        out, rec, ref32, ref64, m, l = _run(104, lens, Hq, Hkv, D, dt, 64, force=force)
+    for dt in (torch.float32, torch.bfloat16):
+        out, rec, ref32, ref64, m, l = _run(104, lens, Hq, Hkv, D, dt, 64)
         assert not out[0].any() and not out[2].any()
         assert_close(out, ref64, TOL_BF16 if dt == torch.bfloat16 else TOL_F32, "zero-length rows")
     # seq_len = NULL: every sequence attends max_len rows of a uniform cache
-    _lib.lib().nimllm_attn_debug_force_decode_kernel(0)
     B, L = 3, 77
     kv = normal(105, 0, (2, B, Hkv, 80, D))
     q = normal(105, 1, (B, Hq * D))

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from gpu_util import bf16_bits, host
-from nimllm_b200 import _lib, attention as A
+from nimllm_b200 import attention as A
 from oracle import oracle as O
 from util import TOL_BF16, assert_close
 
@@ -48,11 +48,8 @@ def test_paged_equals_contiguous_and_ground_truth(Hq, Hkv, D, page_rows):
     q = torch.randn(B, Hq * D, generator=g, device="cuda").bfloat16()
     sl = torch.from_numpy(lens).cuda()
     geom = dict(n_head=Hq, n_kv_head=Hkv, head_dim=D, max_len=cap, seq_len=sl)
-    _lib.lib().nimllm_attn_debug_force_decode_kernel(3)
-    try:
-        flat, flat_rec = A.decode_batch(q, kc, vc, seq_stride=Hkv * cap * D, head_stride=cap * D, partials=True, **geom)
-    finally:
-        _lib.lib().nimllm_attn_debug_force_decode_kernel(0)
+    # chunk_rows = 0 on a bf16 cache: the same balanced kernel the paged entry point runs
+    flat, flat_rec = A.decode_batch(q, kc, vc, seq_stride=Hkv * cap * D, head_stride=cap * D, partials=True, **geom)
     kp, vp, table = _paged_copy(kc, vc, lens, page_rows, torch.Generator().manual_seed(5))
     paged, paged_rec = A.decode_paged(q, kp, vp, table, partials=True, **geom)
     torch.cuda.synchronize()
