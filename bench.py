@@ -370,7 +370,7 @@ def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
         sus_ms, sus_steps = sustained_loop(torch, eager_step if not graphed else step, sum(ms) / len(ms), dist,
                                            seconds=args.sustain, unit_steps=1 if graphed else len(w["kcs"]),
                                            capture=not graphed) \
-            if args.sustain > 0 and (not sharded or graphed) else (None, 0)
+            if args.sustain > 0 and not sharded else (None, 0)   # (ranks that wait for each other: the timed steps say it all)
     t_local = sum(ms) / 1e3
     t_max = dist.max(t_local)
     total_bytes = dist.sum(float(w["bytes"])) if not sharded else float(w["bytes"]) * dist.world

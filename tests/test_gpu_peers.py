@@ -1,7 +1,8 @@
-"""KV-sequence shards exchanged over peer memory (nimllm_attn_combine_peers) on 2+ GPUs: every
-rank decodes its rows, pushes its (o, m, l) records to the peers, and merges -- compared with the
-unsharded decode and with the NCCL all-gather + nimllm_attn_combine route.  Skipped on a box
-with a single GPU."""
+"""KV-sequence shards exchanged over peer memory on 2+ GPUs, one process per GPU: every rank decodes
+its rows, its records reach the peers' buffers (stored by the decode's own merge launch,
+nimllm_attn_decode_push, or copied by nimllm_attn_combine_peers), and every rank merges --
+compared with the unsharded decode and with the NCCL all-gather + nimllm_attn_combine route.
+Skipped on a box with a single GPU (tests/test_gpu_peers_local.py covers the kernels there)."""
 import os
 import socket
 
@@ -39,7 +40,8 @@ def _worker(rank, world, port, q_out):
         errs = []
         for it in range(5):                                          # several calls: slots and counters roll over
             _, rec = A.decode_batch(q, kc, vc, max_len=rows, kv_off=off, head_stride=L * D, partials=True, **base)
-            merged = xch.combine(rec).view(B, Hq * D)
+            merged = xch.combine(rec).view(B, Hq * D) if it % 2 else \
+                xch.decode_combine(q, kc, vc, max_len=rows, kv_off=off, head_stride=L * D, **base).view(B, Hq * D)
             gathered = sharding.gather_partials(rec)
             via_nccl = A.combine(gathered, D).view(B, Hq * D)
             torch.cuda.synchronize()
