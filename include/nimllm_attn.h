@@ -194,6 +194,44 @@ int nimllm_attn_decode_noalloc(const void *q, int q_dtype, const void *k_cache, 
                                int out_dtype, float *partials_out, int batch, int n_head,
                                int n_kv_head, int head_dim, float scale, int chunk_rows, void *stream);
 
+/* ---- the steps either side of decode attention (one new token per sequence) -----------------
+ * Weight matrices are row-major [out, in] as the reference stores them (gpuSgemm op 2 multiplies
+ * by the transpose, src/gpu.nim:185-207).  w_type: */
+#define NIMLLM_W_F32 0  /* float rows */
+#define NIMLLM_W_BF16 1 /* bf16 rows */
+#define NIMLLM_W_Q8_0 2 /* blocks {half d; int8 qs[32]}, 34 bytes per 32 weights (src/kernels.cu:1013-1016) */
+#define NIMLLM_W_Q4_0 3 /* blocks {half d; uint8 qs[16]}, 18 bytes per 32 weights (src/kernels.cu:898-901) */
+
+/* Replaces, in one launch, the q / k / v projections, ropeFwd on q and kNew and the per-KV-head
+ * append of forwardCached (src/model.nim:775-815: three quantMatvec or gpuSgemm calls, two
+ * gpu_rope_fwd launches, 2*nKvHead cudaMemcpy): q, k and v are computed from x_norm and the three
+ * weight matrices, q and k are rotated at each sequence's position, and rotated K / raw V go
+ * straight into the cache row -- they are never written to and re-read from activation buffers.
+ *   x_norm [batch, n_embd] fp32 (the output of the layer's RMSNorm)
+ *   wq [n_head*head_dim, n_embd], wk, wv [n_kv_head*head_dim, n_embd] of w_type, 16-byte aligned
+ *   q_out  [batch, n_head*head_dim] fp32, rotated: what nimllm_attn_decode takes as q
+ *   k_out, v_out  optional [batch, n_kv_head*head_dim] fp32 copies (rotated K, raw V); NULL: cache only
+ *   rope tables, seq_pos / pos0, caches, kv_off, strides, cache_row0, max_seq: as nimllm_rope_append
+ * A weight byte is fetched once per 8 sequences (larger batches re-read the weights per group of 8:
+ * a decode batch that large wants a GEMM, which this entry point is not). */
+int nimllm_qkv_rope_append(const float *x_norm, const void *wq, const void *wk, const void *wv, int w_type, float *q_out,
+                           float *k_out, float *v_out, const float *rope_cos, const float *rope_sin,
+                           const int32_t *seq_pos, int pos0, void *k_cache, void *v_cache, int cache_dtype,
+                           const int64_t *kv_off, int64_t seq_stride, int64_t head_stride, int cache_row0, int max_seq,
+                           int batch, int n_embd, int n_head, int n_kv_head, int head_dim, void *stream);
+
+/* Replaces the output projection and the residual add after attention (src/model.nim:843-849:
+ * quantMatvec or gpuSgemm, then gpu_add): x_out[b] = x_resid[b] + wo attn_out[b].
+ *   attn_out [batch, n_in] fp32, wo [n_embd, n_in] of w_type, x_resid / x_out [batch, n_embd] fp32 */
+int nimllm_wo_residual(const float *attn_out, const void *wo, int w_type, const float *x_resid, float *x_out, int batch,
+                       int n_embd, int n_in, void *stream);
+
+/* y[b] = w x[b] (+ residual[b]) for any of the weight types: the general form of the two entry
+ * points above and of the reference's quantMatvec (src/model.nim:445-450).  x [batch, cols],
+ * y and residual (optional) [batch, rows], fp32. */
+int nimllm_matvec(const void *w, int w_type, const float *x, const float *residual, float *y, int batch, int rows,
+                  int cols, void *stream);
+
 /* ---- merge of (max, sum, output) partials ----------------------------------------
  * No counterpart in the reference (it never splits a softmax row, src/kernels.cu:
  * 267-303 sees the whole row).  parts [n_parts, rows, rec_stride] fp32 records
@@ -323,6 +361,9 @@ void gpu_softmax_fwd(const float *x, float *y, int rows, int cols);
  * attention on dense [S, hd] fp32 buffers */
 void gpu_flash_attn_fwd(const float *Q, const float *K, const float *V, float *O, int S, int hd,
                         float scale, int causal);
+/* src/kernels.cu:996-1003 and :1053-1059: y[rows] = A[rows, cols] x[cols] with A in Q4_0 / Q8_0 blocks */
+void gpu_matvec_q4_0(const void *A, const float *x, float *y, int rows, int cols);
+void gpu_matvec_q8_0(const void *A, const float *x, float *y, int rows, int cols);
 
 #ifdef __cplusplus
 }

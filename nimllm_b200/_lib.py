@@ -10,6 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libnimllm_attn.so")
 
 F32, BF16 = 0, 1
+W_F32, W_BF16, W_Q8_0, W_Q4_0 = 0, 1, 2, 3
 
 _lib = None
 
@@ -42,6 +43,10 @@ PROTOTYPES = {
     "nimllm_attn_decode_noalloc_max_bytes": (sz, []),
     "nimllm_attn_decode_noalloc": (i32, [vp, i32, vp, vp, i32, vp, i64, i64, vp, i32, vp, i32, vp, i32, i32, i32,
                                          i32, f32, i32, vp]),
+    "nimllm_qkv_rope_append": (i32, [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, i64, i64, i32, i32,
+                                     i32, i32, i32, i32, i32, vp]),
+    "nimllm_wo_residual": (i32, [vp, vp, i32, vp, vp, i32, i32, i32, vp]),
+    "nimllm_matvec": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, vp]),
     "nimllm_attn_combine": (i32, [vp, i32, i32, i32, i32, vp, i32, vp, vp]),
     "nimllm_peer_exchange_create": (vp, [i32, i32, i32, i32]),
     "nimllm_peer_exchange_export": (i32, [vp, vp]),
@@ -69,6 +74,8 @@ PROTOTYPES = {
     "gpu_scale": (None, [vp, f32, vp, i32]),
     "gpu_softmax_fwd": (None, [vp, vp, i32, i32]),
     "gpu_flash_attn_fwd": (None, [vp, vp, vp, vp, i32, i32, f32, i32]),
+    "gpu_matvec_q4_0": (None, [vp, vp, vp, i32, i32]),
+    "gpu_matvec_q8_0": (None, [vp, vp, vp, i32, i32]),
 }
 
 class NimllmAttnError(RuntimeError):

@@ -153,6 +153,48 @@ def rope_append_paged(q, k_new, v_new, cos, sin, k_pages, v_pages, page_table, *
         k_pages.shape[2], k_pages.shape[0], B, n, n_kv_head, head_dim, _stream()))
 
 
+def _wtype(w, w_type):
+    if w_type is not None:
+        return w_type
+    return {torch.float32: _lib.W_F32, torch.bfloat16: _lib.W_BF16}[w.dtype]
+
+
+def qkv_rope_append(x_norm, wq, wk, wv, cos, sin, *, n_head, n_kv_head, head_dim, w_type=None, pos0=0, seq_pos=None,
+                    k_cache=None, v_cache=None, kv_off=None, seq_stride=0, head_stride=0, cache_row0=0, max_seq=0,
+                    want_kv=False):
+    """The q / k / v projections, RoPE and the cache append of one decode step in one launch
+    (forwardCached, src/model.nim:775-815).  x_norm [B, n_embd] fp32; weights [out, n_embd] as fp32 or
+    bf16 tensors, or uint8 tensors of Q8_0 / Q4_0 blocks with w_type given.  Returns rotated q
+    [B, Hq*D] (and rotated k, raw v [B, Hkv*D] with want_kv)."""
+    B, n_embd = x_norm.shape
+    q = torch.empty((B, n_head * head_dim), dtype=torch.float32, device=x_norm.device)
+    k = torch.empty((B, n_kv_head * head_dim), dtype=torch.float32, device=x_norm.device) if want_kv or k_cache is None else None
+    v = torch.empty_like(k) if k is not None else None
+    check(lib().nimllm_qkv_rope_append(
+        _ptr(x_norm), _ptr(wq), _ptr(wk), _ptr(wv), _wtype(wq, w_type), _ptr(q), _ptr(k), _ptr(v), _ptr(cos), _ptr(sin),
+        _ptr(seq_pos), pos0, _ptr(k_cache), _ptr(v_cache), _code(k_cache) if k_cache is not None else F32, _ptr(kv_off),
+        seq_stride, head_stride, cache_row0, max_seq, B, n_embd, n_head, n_kv_head, head_dim, _stream()))
+    return (q, k, v) if k is not None else q
+
+
+def wo_residual(attn_out, wo, x_resid, *, w_type=None):
+    """x_resid + wo attn_out (src/model.nim:843-849) in one launch; attn_out [B, n_in], wo [n_embd, n_in]."""
+    B, n_in = attn_out.shape
+    n_embd = x_resid.shape[1]
+    out = torch.empty_like(x_resid)
+    check(lib().nimllm_wo_residual(_ptr(attn_out), _ptr(wo), _wtype(wo, w_type), _ptr(x_resid), _ptr(out), B, n_embd, n_in,
+                                   _stream()))
+    return out
+
+
+def matvec(w, x, rows, *, w_type=None, residual=None):
+    """y[b] = w x[b] (+ residual[b]); x [B, cols] fp32, w [rows, cols] in any of the weight types."""
+    B, cols = x.shape
+    y = torch.empty((B, rows), dtype=torch.float32, device=x.device)
+    check(lib().nimllm_matvec(_ptr(w), _wtype(w, w_type), _ptr(x), _ptr(residual), _ptr(y), B, rows, cols, _stream()))
+    return y
+
+
 def combine(parts, head_dim, out_dtype=torch.float32, partials=False):
     """Merge (o, m, l) records [n_parts, rows, D+4] -> out [rows, D]."""
     n_parts, rows, W = parts.shape

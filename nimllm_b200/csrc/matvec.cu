@@ -1,0 +1,473 @@
+// matvec.cu -- the steps either side of decode attention, HBM-bound on the weight bytes.
+//
+// Replaces, for one new token per sequence (forwardCached with newTokens == 1):
+//   * the three projections + RoPE + cache append of src/model.nim:775-815 (quantMatvec /
+//     gpuSgemm x3, ropeFwd x2, 2*nKvHead cudaMemcpy) by ONE launch that reads xNorm and
+//     wq | wk | wv, rotates q and k in registers and stores rotated K / raw V straight into
+//     the cache row -- q, kNew and vNew never make the round trip through HBM;
+//   * the output projection + residual of src/model.nim:843-849 (quantMatvec / gpuSgemm,
+//     gpu_add) by one launch;
+//   * the reference's quantised mat-vec launchers gpu_matvec_q4_0 / gpu_matvec_q8_0
+//     (src/kernels.cu:941-1060), same names and arguments.
+//
+// Weight formats: fp32 and bf16 rows, and the reference's block formats -- Q4_0 {half d;
+// uint8 qs[16]} = 18 bytes and Q8_0 {half d; int8 qs[32]} = 34 bytes per 32 weights
+// (src/kernels.cu:898-901,1013-1016), value = d * (nibble - 8) or d * q.
+//
+// One warp owns one output row (or the rotation pair of rows f, f + D/2 of a head) and serves
+// up to kMaxBatch input vectors with it, so a weight byte is fetched once per launch tile.
+// Lanes stride over the row in units of 16 bytes (fp32 / bf16) or of block pairs read as
+// aligned 32-bit words (Q4_0: 9 words, Q8_0: 17 words per 64 weights; single blocks through
+// 16-bit loads when a row holds an odd number of blocks).  The input vectors sit in shared
+// memory, padded by one float per 64 for the block formats so that lanes reading different
+// block pairs hit different banks.  A warp takes several rows per pass (their loads are in flight
+// together, and every input value read from shared memory serves all of them).
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace nimllm {
+namespace {
+
+constexpr int kMaxBatch = 8;      // input vectors served per weight fetch
+constexpr int kMvWarps = 16;
+
+enum { W_F32 = 0, W_BF16 = 1, W_Q8_0 = 2, W_Q4_0 = 3 };
+
+__host__ __device__ inline size_t row_bytes(int wt, int cols) {
+    return wt == W_F32 ? (size_t)cols * 4 : wt == W_BF16 ? (size_t)cols * 2 : wt == W_Q8_0 ? (size_t)(cols / 32) * 34
+                                                                                             : (size_t)(cols / 32) * 18;
+}
+// index of x[j] in shared memory: one pad float per 64 for the block formats, so that lanes working
+// on consecutive block pairs (65 floats apart) read different banks
+template <int WT> __device__ __forceinline__ int xs_index(int j) { return (WT >= W_Q8_0) ? j + (j >> 6) : j; }
+template <int WT> __host__ __device__ inline int xs_stride(int cols) { return (WT >= W_Q8_0) ? cols + cols / 64 + 4 : cols; }
+
+__device__ __forceinline__ uint32_t ldg_u32(const void *p) {
+    uint32_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint32_t ldg_u16(const void *p) {
+    uint16_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(r) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ float half_bits_to_float(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)(h & 0xffffu))); }
+
+// acc[r][b] += sum_e wv[r][e] * x_b[j0 + e] for N consecutive weights of R rows: every input value
+// is read from shared memory once and used for all R rows
+template <int R, int NB, int N, bool VEC>
+__device__ __forceinline__ void fma_chunk(const float (&wv)[R][N], const float *xs, int xs_ld, int j0, float (&acc)[R][NB]) {
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+        float xv[N];
+        if (VEC) {                                           // unpadded layout, j0 a multiple of 4: 16-byte reads
+#pragma unroll
+            for (int e = 0; e < N; e += 4) {
+                const float4 t = *reinterpret_cast<const float4 *>(xs + b * xs_ld + j0 + e);
+                xv[e] = t.x; xv[e + 1] = t.y; xv[e + 2] = t.z; xv[e + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < N; e++) xv[e] = xs[b * xs_ld + j0 + e];
+        }
+#pragma unroll
+        for (int e = 0; e < N; e++)
+#pragma unroll
+            for (int r = 0; r < R; r++) acc[r][b] = fmaf(wv[r][e], xv[e], acc[r][b]);
+    }
+}
+
+// the 32 weights of one block as floats, already multiplied by the block's scale.  Q4_0: weight 2i =
+// low nibble of byte i, weight 2i+1 = high nibble, minus 8 (src/kernels.cu:966-970); Q8_0: int8
+// (src/kernels.cu:1033-1036).  `q` are the quantised bytes as words, w4 selects one word.
+template <int WT> __device__ __forceinline__ void dequant_word(uint32_t q, float d, float *out) {
+    if (WT == W_Q4_0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t byte = (q >> (8 * i)) & 0xffu;
+            out[2 * i] = d * (float)((int)(byte & 0xfu) - 8);
+            out[2 * i + 1] = d * (float)((int)(byte >> 4) - 8);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) out[i] = d * (float)(int)(int8_t)((q >> (8 * i)) & 0xffu);
+    }
+}
+
+// Partial dot products of R weight rows with NB input vectors: this lane's share (lanes stride over
+// the row, the loads of all R rows are in flight together); the caller adds the lanes up.
+template <int WT, int NB, int R>
+__device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], int cols, const float *xs, int xs_ld, int lane,
+                                         float (&acc)[R][NB]) {
+    if (WT == W_F32 || WT == W_BF16) {
+        constexpr int N = WT == W_F32 ? 4 : 8;               // weights per 16-byte load
+        constexpr int EB = WT == W_F32 ? 4 : 2;
+        for (int j = lane * N; j < cols; j += 64 * N) {      // two units per lane and round: 2 R loads in flight
+            const int j2 = j + 32 * N;
+            const bool has2 = j2 < cols;
+            uint4 u[2][R];
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                u[0][r] = ldg_stream(row[r] + (size_t)j * EB);
+                u[1][r] = has2 ? ldg_stream(row[r] + (size_t)j2 * EB) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                if (h == 1 && !has2) break;
+                float wv[R][N];
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    if (WT == W_F32) {
+                        wv[r][0] = __uint_as_float(u[h][r].x); wv[r][1] = __uint_as_float(u[h][r].y);
+                        wv[r][2] = __uint_as_float(u[h][r].z); wv[r][3] = __uint_as_float(u[h][r].w);
+                    } else {
+                        Elem<__nv_bfloat16>::unpack(u[h][r], wv[r]);
+                    }
+                }
+                fma_chunk<R, NB, N, true>(wv, xs, xs_ld, h ? j2 : j, acc);
+            }
+        }
+    } else {
+        constexpr int BS = WT == W_Q4_0 ? 18 : 34;           // bytes per block
+        constexpr int QW = WT == W_Q4_0 ? 4 : 8;             // 32-bit words of quantised values per block
+        constexpr int N = 32 / QW;                           // weights per word
+        const int bpr = cols >> 5;
+        bool aligned = (bpr & 1) == 0;
+#pragma unroll
+        for (int r = 0; r < R; r++) aligned = aligned && ((uintptr_t)row[r] & 3) == 0;
+        if (aligned) {
+            // block pairs as aligned words: {d0 | q0[0..1]} q0.. {q0 tail | d1} q1..
+            for (int pr = lane; pr < (bpr >> 1); pr += 32) {
+                uint32_t w[R][2 * QW + 1];
+#pragma unroll
+                for (int r = 0; r < R; r++)
+#pragma unroll
+                    for (int i = 0; i < 2 * QW + 1; i++) w[r][i] = ldg_u32(row[r] + (size_t)pr * (2 * BS) + 4 * i);
+                const int base = pr * 65;                     // 64 weights + 1 pad float per pair
+#pragma unroll
+                for (int i = 0; i < QW; i++) {
+                    float wv[R][N];
+#pragma unroll
+                    for (int r = 0; r < R; r++) dequant_word<WT>((w[r][i] >> 16) | (w[r][i + 1] << 16), half_bits_to_float(w[r][0]), wv[r]);
+                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + i * N, acc);
+                }
+#pragma unroll
+                for (int i = 0; i < QW; i++) {
+                    float wv[R][N];
+#pragma unroll
+                    for (int r = 0; r < R; r++) dequant_word<WT>(w[r][QW + 1 + i], half_bits_to_float(w[r][QW] >> 16), wv[r]);
+                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + 32 + i * N, acc);
+                }
+            }
+        } else {
+            // rows with an odd number of blocks: single blocks through 16-bit loads
+            for (int bk = lane; bk < bpr; bk += 32) {
+#pragma unroll
+                for (int i = 0; i < QW; i++) {
+                    float wv[R][N];
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        const unsigned char *p = row[r] + (size_t)bk * BS;
+                        dequant_word<WT>(ldg_u16(p + 2 + 4 * i) | (ldg_u16(p + 4 + 4 * i) << 16), half_bits_to_float(ldg_u16(p)), wv[r]);
+                    }
+                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, bk * 32 + (bk >> 1) + i * N, acc);
+                }
+            }
+        }
+    }
+}
+
+template <int R, int NB> __device__ __forceinline__ void warp_sum2(float (&acc)[R][NB]) {
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc[r][b] += __shfl_xor_sync(0xffffffffu, acc[r][b], off);
+}
+
+// the input vectors of this batch tile into shared memory (layout of xs_index)
+template <int WT>
+__device__ __forceinline__ void stage_x(float *xs, const float *x, int cols, int x_ld, int nb) {
+    const int ld = xs_stride<WT>(cols);
+    for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
+        const int b = i / cols, j = i - b * cols;
+        xs[b * ld + xs_index<WT>(j)] = x[(size_t)b * x_ld + j];
+    }
+}
+
+// ------------------------------------------------------------------ y = W x (+ residual)
+struct MatvecParams {
+    const unsigned char *w;
+    const float *x;          // [batch, cols], row stride x_ld
+    const float *resid;      // [batch, rows] or null (row stride y_ld)
+    float *y;                // [batch, rows], row stride y_ld
+    int rows, cols, x_ld, y_ld, batch;
+};
+
+template <int WT, int NB>
+__global__ void __launch_bounds__(kMvWarps * 32) matvec_kernel(MatvecParams p) {
+    constexpr int R = NB >= 8 ? 2 : 4;                       // rows per warp pass
+    extern __shared__ __align__(16) float xs[];
+    const int b0 = blockIdx.y * NB;
+    const int nb = min(NB, p.batch - b0);
+    const int ld = xs_stride<WT>(p.cols);
+    stage_x<WT>(xs, p.x + (size_t)b0 * p.x_ld, p.cols, p.x_ld, nb);
+    for (int i = threadIdx.x + nb * ld; i < NB * ld; i += blockDim.x) xs[i] = 0.f;     // unused vectors read as zeros
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t rb = row_bytes(WT, p.cols);
+    for (int row0 = (blockIdx.x * kMvWarps + warp) * R; row0 < p.rows; row0 += gridDim.x * kMvWarps * R) {
+        float acc[R][NB];
+        const unsigned char *rows[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            rows[r] = p.w + (size_t)min(row0 + r, p.rows - 1) * rb;     // rows past the end repeat the last one, unstored
+#pragma unroll
+            for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
+        }
+        rows_dot<WT, NB, R>(rows, p.cols, xs, ld, lane, acc);
+        warp_sum2<R, NB>(acc);
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+                if (lane == r * NB + b && b < nb && row0 + r < p.rows) {
+                    const size_t o = (size_t)(b0 + b) * p.y_ld + row0 + r;
+                    p.y[o] = acc[r][b] + (p.resid ? p.resid[o] : 0.f);
+                }
+    }
+}
+
+// ------------------------------------------------------------------ q | k | v = W x, RoPE, cache append
+struct QkvParams {
+    const unsigned char *wq, *wk, *wv;
+    const float *x;                     // [batch, n_embd]
+    float *q_out, *k_out, *v_out;       // [batch, Hq*D]; [batch, Hkv*D] or null
+    const float *cos_tab, *sin_tab;
+    const int32_t *seq_pos;
+    void *k_cache, *v_cache;
+    const int64_t *kv_off;
+    int64_t seq_stride, head_stride;
+    int pos0, cache_row0, max_seq;
+    int batch, n_embd, Hq, Hkv, D;
+};
+
+template <typename T> __device__ __forceinline__ void store_cache(T *p, float v);
+template <> __device__ __forceinline__ void store_cache<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_cache<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+// One warp task = the rotation pair (f, f + D/2) of one head of q, k or v.
+template <int WT, int NB, typename CacheT>
+__global__ void __launch_bounds__(kMvWarps * 32) qkv_rope_append_kernel(QkvParams p) {
+    extern __shared__ __align__(16) float xs[];
+    const int b0 = blockIdx.y * NB;
+    const int nb = min(NB, p.batch - b0);
+    const int ld = xs_stride<WT>(p.n_embd);
+    stage_x<WT>(xs, p.x + (size_t)b0 * p.n_embd, p.n_embd, p.n_embd, nb);
+    for (int i = threadIdx.x + nb * ld; i < NB * ld; i += blockDim.x) xs[i] = 0.f;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = p.D / 2;
+    const int tasks = (p.Hq + 2 * p.Hkv) * half;
+    const size_t rb = row_bytes(WT, p.n_embd);
+    for (int t = blockIdx.x * kMvWarps + warp; t < tasks; t += gridDim.x * kMvWarps) {
+        const int slot = t / half, f = t - slot * half;
+        const bool is_q = slot < p.Hq, is_k = !is_q && slot < p.Hq + p.Hkv;
+        const int head = is_q ? slot : (is_k ? slot - p.Hq : slot - p.Hq - p.Hkv);
+        const unsigned char *w = is_q ? p.wq : (is_k ? p.wk : p.wv);
+        const int row0 = head * p.D + f;
+        float acc[2][NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) { acc[0][b] = 0.f; acc[1][b] = 0.f; }
+        const unsigned char *rows[2] = {w + (size_t)row0 * rb, w + (size_t)(row0 + half) * rb};
+        rows_dot<WT, NB, 2>(rows, p.n_embd, xs, ld, lane, acc);
+        warp_sum2<2, NB>(acc);
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+            if (lane == b && b < nb) {
+                const int bb = b0 + b;
+                const int pos = p.seq_pos ? p.seq_pos[bb] : p.pos0;
+                float x0 = acc[0][b], x1 = acc[1][b];
+                if (!(!is_q && !is_k) && p.cos_tab) {
+                    // the expression of src/kernels.cu:412-413 with sign = +1
+                    const float c = p.cos_tab[(size_t)pos * half + f], s = p.sin_tab[(size_t)pos * half + f];
+                    const float ra = x0 * c - x1 * s, rd = x0 * s + x1 * c;
+                    x0 = ra; x1 = rd;
+                }
+                if (is_q) {
+                    float *o = p.q_out + (size_t)bb * p.Hq * p.D + row0;
+                    o[0] = x0; o[half] = x1;
+                } else {
+                    float *o = is_k ? p.k_out : p.v_out;
+                    if (o) { o[(size_t)bb * p.Hkv * p.D + row0] = x0; o[(size_t)bb * p.Hkv * p.D + row0 + half] = x1; }
+                    const int crow = pos - p.cache_row0;
+                    if (p.k_cache && crow >= 0 && crow < p.max_seq) {
+                        const int64_t base = (p.kv_off ? p.kv_off[bb] : (int64_t)bb * p.seq_stride) + (int64_t)head * p.head_stride +
+                                             (int64_t)crow * p.D + f;
+                        CacheT *dst = reinterpret_cast<CacheT *>(is_k ? p.k_cache : p.v_cache) + base;
+                        store_cache<CacheT>(dst, x0);
+                        store_cache<CacheT>(dst + half, x1);
+                    }
+                }
+            }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+template <typename K, typename P> int launch_with_smem(K kernel, dim3 grid, size_t smem, cudaStream_t st, const char *what, const P &params) {
+    if (smem > 48 * 1024) {
+        // opt in once per kernel and device (the attribute is per function, per device)
+        static thread_local const void *done[64][32];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        bool seen = false;
+        if (dev >= 0 && dev < 64)
+            for (int i = 0; i < 32 && done[dev][i]; i++) seen |= done[dev][i] == (const void *)kernel;
+        if (!seen) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "%s: shared memory opt-in: %s", what, cudaGetErrorString(e));
+            if (dev >= 0 && dev < 64)
+                for (int i = 0; i < 32; i++)
+                    if (!done[dev][i]) { done[dev][i] = (const void *)kernel; break; }
+        }
+    }
+    kernel<<<grid, kMvWarps * 32, smem, st>>>(params);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return NIMLLM_OK;
+}
+
+int batch_tile(int batch) { return batch >= 8 ? 8 : batch > 2 ? 4 : batch; }      // 1, 2, 4 or 8 vectors per weight fetch
+
+template <int WT> size_t smem_for(int nb, int cols) { return (size_t)nb * xs_stride<WT>(cols) * sizeof(float); }
+
+template <int WT>
+int launch_matvec_t(const MatvecParams &p, cudaStream_t st) {
+    const int nb = batch_tile(p.batch);
+    const size_t smem = smem_for<WT>(nb, p.cols);
+    if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "matvec: %d input vectors of %d floats do not fit shared memory", nb, p.cols);
+    const int rows_per_cta = kMvWarps * (nb >= 8 ? 2 : 4);
+    int gx = (p.rows + rows_per_cta - 1) / rows_per_cta;
+    const int cap = sm_count() * 4;
+    if (gx > cap) gx = cap;
+    dim3 grid(gx, (p.batch + nb - 1) / nb);
+    switch (nb) {
+        case 1: return launch_with_smem(matvec_kernel<WT, 1>, grid, smem, st, "matvec", p);
+        case 2: return launch_with_smem(matvec_kernel<WT, 2>, grid, smem, st, "matvec", p);
+        case 4: return launch_with_smem(matvec_kernel<WT, 4>, grid, smem, st, "matvec", p);
+        default: return launch_with_smem(matvec_kernel<WT, 8>, grid, smem, st, "matvec", p);
+    }
+}
+
+int launch_matvec(int wt, const MatvecParams &p, cudaStream_t st) {
+    switch (wt) {
+        case W_F32: return launch_matvec_t<W_F32>(p, st);
+        case W_BF16: return launch_matvec_t<W_BF16>(p, st);
+        case W_Q8_0: return launch_matvec_t<W_Q8_0>(p, st);
+        default: return launch_matvec_t<W_Q4_0>(p, st);
+    }
+}
+
+template <int WT, typename CacheT>
+int launch_qkv_t(const QkvParams &p, cudaStream_t st) {
+    const int nb = batch_tile(p.batch);
+    const size_t smem = smem_for<WT>(nb, p.n_embd);
+    if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "qkv_rope_append: %d input vectors of %d floats do not fit shared memory", nb, p.n_embd);
+    const int tasks = (p.Hq + 2 * p.Hkv) * (p.D / 2);
+    int gx = (tasks + kMvWarps - 1) / kMvWarps;
+    const int cap = sm_count() * 4;
+    if (gx > cap) gx = cap;
+    dim3 grid(gx, (p.batch + nb - 1) / nb);
+    switch (nb) {
+        case 1: return launch_with_smem(qkv_rope_append_kernel<WT, 1, CacheT>, grid, smem, st, "qkv_rope_append", p);
+        case 2: return launch_with_smem(qkv_rope_append_kernel<WT, 2, CacheT>, grid, smem, st, "qkv_rope_append", p);
+        case 4: return launch_with_smem(qkv_rope_append_kernel<WT, 4, CacheT>, grid, smem, st, "qkv_rope_append", p);
+        default: return launch_with_smem(qkv_rope_append_kernel<WT, 8, CacheT>, grid, smem, st, "qkv_rope_append", p);
+    }
+}
+
+template <typename CacheT>
+int launch_qkv(int wt, const QkvParams &p, cudaStream_t st) {
+    switch (wt) {
+        case W_F32: return launch_qkv_t<W_F32, CacheT>(p, st);
+        case W_BF16: return launch_qkv_t<W_BF16, CacheT>(p, st);
+        case W_Q8_0: return launch_qkv_t<W_Q8_0, CacheT>(p, st);
+        default: return launch_qkv_t<W_Q4_0, CacheT>(p, st);
+    }
+}
+
+bool weight_shape_ok(int wt, int cols) {
+    if (wt < W_F32 || wt > W_Q4_0 || cols <= 0) return false;
+    return wt == W_F32 ? cols % 4 == 0 : wt == W_BF16 ? cols % 8 == 0 : cols % 32 == 0;
+}
+
+}  // namespace
+}  // namespace nimllm
+
+using namespace nimllm;
+
+extern "C" {
+
+int nimllm_matvec(const void *w, int w_type, const float *x, const float *residual, float *y, int batch, int rows,
+                  int cols, void *stream) {
+    if (!w || !x || !y) return fail(NIMLLM_ERR_ARG, "matvec: null pointer");
+    if (batch <= 0 || rows <= 0 || !weight_shape_ok(w_type, cols))
+        return fail(NIMLLM_ERR_ARG, "matvec: bad shape batch=%d rows=%d cols=%d for weight type %d (fp32 rows: cols %% 4, bf16: "
+                                    "cols %% 8, Q8_0 / Q4_0: cols %% 32)", batch, rows, cols, w_type);
+    if (((uintptr_t)w & 15) || ((uintptr_t)x & 3) || ((uintptr_t)y & 3))
+        return fail(NIMLLM_ERR_ARG, "matvec: the weights must be 16-byte aligned");
+    MatvecParams p;
+    p.w = (const unsigned char *)w; p.x = x; p.resid = residual; p.y = y;
+    p.rows = rows; p.cols = cols; p.x_ld = cols; p.y_ld = rows; p.batch = batch;
+    return launch_matvec(w_type, p, (cudaStream_t)stream);
+}
+
+int nimllm_wo_residual(const float *attn_out, const void *wo, int w_type, const float *x_resid, float *x_out, int batch,
+                       int n_embd, int n_in, void *stream) {
+    if (!x_resid) return fail(NIMLLM_ERR_ARG, "wo_residual: null residual");
+    return nimllm_matvec(wo, w_type, attn_out, x_resid, x_out, batch, n_embd, n_in, stream);
+}
+
+int nimllm_qkv_rope_append(const float *x_norm, const void *wq, const void *wk, const void *wv, int w_type, float *q_out,
+                           float *k_out, float *v_out, const float *rope_cos, const float *rope_sin,
+                           const int32_t *seq_pos, int pos0, void *k_cache, void *v_cache, int cache_dtype,
+                           const int64_t *kv_off, int64_t seq_stride, int64_t head_stride, int cache_row0, int max_seq,
+                           int batch, int n_embd, int n_head, int n_kv_head, int head_dim, void *stream) {
+    if (!x_norm || !wq || !wk || !wv || !q_out) return fail(NIMLLM_ERR_ARG, "qkv_rope_append: null x / weights / q_out");
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || head_dim <= 0 || (head_dim & 1) || !weight_shape_ok(w_type, n_embd))
+        return fail(NIMLLM_ERR_ARG, "qkv_rope_append: bad shape batch=%d n_embd=%d Hq=%d Hkv=%d D=%d weight type %d", batch,
+                    n_embd, n_head, n_kv_head, head_dim, w_type);
+    if ((rope_cos == nullptr) != (rope_sin == nullptr))
+        return fail(NIMLLM_ERR_ARG, "qkv_rope_append: give both RoPE tables or neither");
+    if ((k_cache == nullptr) != (v_cache == nullptr))
+        return fail(NIMLLM_ERR_ARG, "qkv_rope_append: give both cache pointers or neither");
+    if (!k_cache && (!k_out || !v_out)) return fail(NIMLLM_ERR_ARG, "qkv_rope_append: nowhere to put k and v");
+    if (k_cache && (!dtype_ok(cache_dtype) || max_seq <= 0))
+        return fail(NIMLLM_ERR_ARG, "qkv_rope_append: bad cache dtype or max_seq");
+    if (((uintptr_t)wq | (uintptr_t)wk | (uintptr_t)wv) & 15)
+        return fail(NIMLLM_ERR_ARG, "qkv_rope_append: the weights must be 16-byte aligned");
+    QkvParams p;
+    p.wq = (const unsigned char *)wq; p.wk = (const unsigned char *)wk; p.wv = (const unsigned char *)wv;
+    p.x = x_norm; p.q_out = q_out; p.k_out = k_out; p.v_out = v_out;
+    p.cos_tab = rope_cos; p.sin_tab = rope_sin; p.seq_pos = seq_pos;
+    p.k_cache = k_cache; p.v_cache = v_cache; p.kv_off = kv_off; p.seq_stride = seq_stride; p.head_stride = head_stride;
+    p.pos0 = pos0; p.cache_row0 = cache_row0; p.max_seq = max_seq;
+    p.batch = batch; p.n_embd = n_embd; p.Hq = n_head; p.Hkv = n_kv_head; p.D = head_dim;
+    if (k_cache && cache_dtype == NIMLLM_BF16) return launch_qkv<__nv_bfloat16>(w_type, p, (cudaStream_t)stream);
+    return launch_qkv<float>(w_type, p, (cudaStream_t)stream);
+}
+
+/* src/kernels.cu:996-1003 and :1053-1059: y[rows] = A[rows, cols] x[cols], legacy default stream, void */
+void gpu_matvec_q4_0(const void *A, const float *x, float *y, int rows, int cols) {
+    if (nimllm_matvec(A, W_Q4_0, x, nullptr, y, 1, rows, cols, nullptr))
+        fprintf(stderr, "gpu_matvec_q4_0: %s\n", nimllm_attn_last_error());
+}
+void gpu_matvec_q8_0(const void *A, const float *x, float *y, int rows, int cols) {
+    if (nimllm_matvec(A, W_Q8_0, x, nullptr, y, 1, rows, cols, nullptr))
+        fprintf(stderr, "gpu_matvec_q8_0: %s\n", nimllm_attn_last_error());
+}
+
+}  // extern "C"

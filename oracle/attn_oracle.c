@@ -575,3 +575,91 @@ ORACLE_API void oracle_combine(const float *parts, int n_parts, int rows, int D,
         if (out_m) { out_m[r] = (float)m; out_l[r] = (float)wsum; }
     }
 }
+
+/* ------------------------------------------------ quantised weights (decode projections)
+ * Block formats of src/kernels.cu:898-901 (Q4_0: half scale + 16 bytes of nibbles) and
+ * :1013-1016 (Q8_0: half scale + 32 int8).  Blocks are packed without padding: 18 and 34 bytes. */
+static inline uint16_t f32_to_f16_bits(float f) { _Float16 h = (_Float16)f; uint16_t u; memcpy(&u, &h, 2); return u; }
+static inline float f16_bits_to_f32(uint16_t u) { _Float16 h; memcpy(&h, &u, 2); return (float)h; }
+
+/* k_quantize_q4_0, src/kernels.cu:904-932: d = amax / 7, q = min(15, (int)(x / d + 8.5)) */
+ORACLE_API void oracle_quantize_q4_0(const float *x, uint8_t *y, int64_t n) {
+    for (int64_t blk = 0; blk < n / 32; blk++) {
+        const float *src = x + blk * 32;
+        uint8_t *dst = y + blk * 18;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) { float a = fabsf(src[i]); if (a > amax) amax = a; }
+        float d = amax / 7.0f;
+        float id = d ? 1.0f / d : 0.0f;
+        uint16_t hb = f32_to_f16_bits(d);
+        memcpy(dst, &hb, 2);
+        for (int i = 0; i < 16; i++) {
+            int v0 = (int)(src[i * 2 + 0] * id + 8.5f); if (v0 > 15) v0 = 15;
+            int v1 = (int)(src[i * 2 + 1] * id + 8.5f); if (v1 > 15) v1 = 15;
+            dst[2 + i] = (uint8_t)(v0 | (v1 << 4));
+        }
+    }
+}
+
+/* The reference has no Q8_0 quantiser (its Q8_0 weights come out of GGUF files,
+ * src/model.nim:405-407); this is the usual one for the format: d = amax / 127, q = round(x / d). */
+ORACLE_API void oracle_quantize_q8_0(const float *x, uint8_t *y, int64_t n) {
+    for (int64_t blk = 0; blk < n / 32; blk++) {
+        const float *src = x + blk * 32;
+        uint8_t *dst = y + blk * 34;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) { float a = fabsf(src[i]); if (a > amax) amax = a; }
+        float d = amax / 127.0f;
+        float id = d ? 1.0f / d : 0.0f;
+        uint16_t hb = f32_to_f16_bits(d);
+        memcpy(dst, &hb, 2);
+        for (int i = 0; i < 32; i++) dst[2 + i] = (uint8_t)(int8_t)lrintf(src[i] * id);
+    }
+}
+
+/* value of weight j of a row: d * (nibble - 8) (src/kernels.cu:966-970) or d * q (:1033-1036) */
+ORACLE_API void oracle_dequantize(const uint8_t *A, int q4, float *out, int64_t n) {
+    const int bs = q4 ? 18 : 34;
+    for (int64_t blk = 0; blk < n / 32; blk++) {
+        const uint8_t *b = A + blk * bs;
+        uint16_t hb; memcpy(&hb, b, 2);
+        const float d = f16_bits_to_f32(hb);
+        for (int i = 0; i < 32; i++) {
+            int q = q4 ? ((i & 1) ? (b[2 + i / 2] >> 4) : (b[2 + i / 2] & 0x0F)) - 8 : (int)(int8_t)b[2 + i];
+            out[blk * 32 + i] = d * (float)q;
+        }
+    }
+}
+
+/* k_matvec_q4_0 / k_matvec_q8_0: y[row] = sum over blocks of d * (sum over the block of q * x), the
+ * block sums in float as the kernels form them; the sum over blocks in float (acc64 = 0, any order
+ * is within the 1e-4 bound) or in double (acc64 = 1: ground truth). */
+ORACLE_API void oracle_matvec_q(const uint8_t *A, int q4, const float *x, float *y, int rows, int cols, int acc64) {
+    const int bs = q4 ? 18 : 34, bpr = cols / 32;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; r++) {
+        const uint8_t *rp = A + (int64_t)r * bpr * bs;
+        double sum64 = 0.0; float sum32 = 0.0f;
+        for (int blk = 0; blk < bpr; blk++) {
+            const uint8_t *b = rp + blk * bs;
+            uint16_t hb; memcpy(&hb, b, 2);
+            const float d = f16_bits_to_f32(hb);
+            if (acc64) {
+                double local = 0.0;
+                for (int i = 0; i < 32; i++) {
+                    int q = q4 ? ((i & 1) ? (b[2 + i / 2] >> 4) : (b[2 + i / 2] & 0x0F)) - 8 : (int)(int8_t)b[2 + i];
+                    local += (double)q * (double)x[blk * 32 + i];
+                }
+                sum64 += (double)d * local;
+            } else {
+                float local = 0.0f;
+                for (int i = 0; i < 32; i++) {
+                    int q = q4 ? ((i & 1) ? (b[2 + i / 2] >> 4) : (b[2 + i / 2] & 0x0F)) - 8 : (int)(int8_t)b[2 + i];
+                    local += (float)q * x[blk * 32 + i];
+                }
+                sum32 += d * local;
+            }
+        }
+        y[r] = acc64 ? (float)sum64 : sum32;
+    }
+}

@@ -29,8 +29,9 @@ def build(force: bool = False) -> None:
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
         subprocess.check_call(["make", "-s", "-C", _HERE, os.path.join(_HERE, "liboracle.so")])
     ref = os.path.join(_HERE, "_ref", "libnimllm_ref.so")
-    if os.path.exists("/root/reference/src/kernels.cu") and (force or not os.path.exists(ref)):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+    root = os.environ.get("REFERENCE_ROOT", "/root/reference")     # the same variable oracle/Makefile reads
+    if os.path.exists(os.path.join(root, "src", "kernels.cu")) and (force or not os.path.exists(ref)):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REFERENCE_ROOT={root}"])
 
 
 def lib() -> C.CDLL:
@@ -58,6 +59,11 @@ def lib() -> C.CDLL:
         L.oracle_combine.argtypes = [f32p, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.c_void_p, C.c_void_p]
         L.oracle_f32_to_bf16.argtypes = [f32p, u16p, C.c_int64]
         L.oracle_bf16_to_f32.argtypes = [u16p, f32p, C.c_int64]
+        u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
+        L.oracle_quantize_q4_0.argtypes = [f32p, u8p, C.c_int64]
+        L.oracle_quantize_q8_0.argtypes = [f32p, u8p, C.c_int64]
+        L.oracle_dequantize.argtypes = [u8p, C.c_int, f32p, C.c_int64]
+        L.oracle_matvec_q.argtypes = [u8p, C.c_int, f32p, f32p, C.c_int, C.c_int, C.c_int]
         L.oracle_num_threads.restype = C.c_int
         L.oracle_set_threads.argtypes = [C.c_int]
         _LIB = L
@@ -65,6 +71,30 @@ def lib() -> C.CDLL:
 
 
 # ----------------------------------------------------------------- numpy API
+
+def quantize(w, kind):
+    """w [rows, cols] float32 -> packed Q4_0 (18 bytes per 32 weights, the reference's quantiser,
+    src/kernels.cu:904-932) or Q8_0 (34 bytes per 32) blocks as a flat uint8 array."""
+    w = np.ascontiguousarray(w, np.float32)
+    q4 = kind == "q4_0"
+    out = np.empty(w.size // 32 * (18 if q4 else 34), np.uint8)
+    (lib().oracle_quantize_q4_0 if q4 else lib().oracle_quantize_q8_0)(w.reshape(-1), out, w.size)
+    return out
+
+
+def dequantize(blocks, kind, shape):
+    out = np.empty(int(np.prod(shape)), np.float32)
+    lib().oracle_dequantize(np.ascontiguousarray(blocks), int(kind == "q4_0"), out, out.size)
+    return out.reshape(shape)
+
+
+def matvec_q(blocks, kind, x, rows, cols, acc64=False):
+    """The reference's k_matvec_q4_0 / k_matvec_q8_0 arithmetic (src/kernels.cu:941-1051) on the CPU."""
+    y = np.empty(rows, np.float32)
+    lib().oracle_matvec_q(np.ascontiguousarray(blocks), int(kind == "q4_0"), np.ascontiguousarray(x, np.float32), y, rows, cols,
+                          int(acc64))
+    return y
+
 
 def rope_tables(max_pos: int, head_dim: int, base: float):
     cos = np.empty((max_pos, head_dim // 2), np.float32)
