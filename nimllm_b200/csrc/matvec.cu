@@ -30,7 +30,7 @@ namespace nimllm {
 namespace {
 
 constexpr int kMaxBatch = 8;      // input vectors served per weight fetch
-constexpr int kMvWarps = 16;
+constexpr int kMvWarps = 8;
 
 enum { W_F32 = 0, W_BF16 = 1, W_Q8_0 = 2, W_Q4_0 = 3 };
 
@@ -79,21 +79,37 @@ __device__ __forceinline__ void fma_chunk(const float (&wv)[R][N], const float *
     }
 }
 
-// the 32 weights of one block as floats, already multiplied by the block's scale.  Q4_0: weight 2i =
-// low nibble of byte i, weight 2i+1 = high nibble, minus 8 (src/kernels.cu:966-970); Q8_0: int8
-// (src/kernels.cu:1033-1036).  `q` are the quantised bytes as words, w4 selects one word.
-template <int WT> __device__ __forceinline__ void dequant_word(uint32_t q, float d, float *out) {
+// Four (Q8_0) or eight (Q4_0) quantised values of one 32-bit word of a block as floats (the block's
+// scale is applied to the block's sum, as the reference's kernels do).  Q4_0: weight 2i = low nibble
+// of byte i, weight 2i+1 = high nibble, minus 8 (src/kernels.cu:966-970); Q8_0: int8
+// (src/kernels.cu:1033-1036).  No integer-to-float conversion instruction (a quarter-rate pipe): a
+// byte b placed into the mantissa of 2^23 is the float 8388608 + b, and one exact subtraction takes
+// the offset out.
+__device__ __forceinline__ float byte_as_float(uint32_t word, int i) {         // 8388608 + byte i of word
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(word), "r"(0x4B000000u), "r"(0x7440u | (uint32_t)i));
+    return __uint_as_float(r);
+}
+template <int WT> __device__ __forceinline__ void dequant_word(uint32_t q, float *out) {
     if (WT == W_Q4_0) {
+        const uint32_t lo = q & 0x0F0F0F0Fu, hi = (q >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const uint32_t byte = (q >> (8 * i)) & 0xffu;
-            out[2 * i] = d * (float)((int)(byte & 0xfu) - 8);
-            out[2 * i + 1] = d * (float)((int)(byte >> 4) - 8);
+            out[2 * i] = byte_as_float(lo, i) - 8388616.f;          // nibble - 8
+            out[2 * i + 1] = byte_as_float(hi, i) - 8388616.f;
         }
     } else {
+        const uint32_t u = q ^ 0x80808080u;                  // int8 + 128 as unsigned bytes
 #pragma unroll
-        for (int i = 0; i < 4; i++) out[i] = d * (float)(int)(int8_t)((q >> (8 * i)) & 0xffu);
+        for (int i = 0; i < 4; i++) out[i] = byte_as_float(u, i) - 8388736.f;
     }
+}
+// acc += d * part for the finished block of every row
+template <int R, int NB> __device__ __forceinline__ void add_block(const float (&d)[R], float (&part)[R][NB], float (&acc)[R][NB]) {
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int b = 0; b < NB; b++) { acc[r][b] = fmaf(d[r], part[r][b], acc[r][b]); part[r][b] = 0.f; }
 }
 
 // Partial dot products of R weight rows with NB input vectors: this lane's share (lanes stride over
@@ -146,34 +162,53 @@ __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], i
 #pragma unroll
                     for (int i = 0; i < 2 * QW + 1; i++) w[r][i] = ldg_u32(row[r] + (size_t)pr * (2 * BS) + 4 * i);
                 const int base = pr * 65;                     // 64 weights + 1 pad float per pair
+                float part[R][NB], d[R];
 #pragma unroll
-                for (int i = 0; i < QW; i++) {
-                    float wv[R][N];
+                for (int r = 0; r < R; r++) {
+                    d[r] = half_bits_to_float(w[r][0]);
 #pragma unroll
-                    for (int r = 0; r < R; r++) dequant_word<WT>((w[r][i] >> 16) | (w[r][i + 1] << 16), half_bits_to_float(w[r][0]), wv[r]);
-                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + i * N, acc);
+                    for (int b = 0; b < NB; b++) part[r][b] = 0.f;
                 }
 #pragma unroll
                 for (int i = 0; i < QW; i++) {
                     float wv[R][N];
 #pragma unroll
-                    for (int r = 0; r < R; r++) dequant_word<WT>(w[r][QW + 1 + i], half_bits_to_float(w[r][QW] >> 16), wv[r]);
-                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + 32 + i * N, acc);
+                    for (int r = 0; r < R; r++) dequant_word<WT>((w[r][i] >> 16) | (w[r][i + 1] << 16), wv[r]);
+                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + i * N, part);
                 }
+                add_block<R, NB>(d, part, acc);
+#pragma unroll
+                for (int r = 0; r < R; r++) d[r] = half_bits_to_float(w[r][QW] >> 16);
+#pragma unroll
+                for (int i = 0; i < QW; i++) {
+                    float wv[R][N];
+#pragma unroll
+                    for (int r = 0; r < R; r++) dequant_word<WT>(w[r][QW + 1 + i], wv[r]);
+                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + 32 + i * N, part);
+                }
+                add_block<R, NB>(d, part, acc);
             }
         } else {
             // rows with an odd number of blocks: single blocks through 16-bit loads
             for (int bk = lane; bk < bpr; bk += 32) {
+                float part[R][NB], d[R];
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    d[r] = half_bits_to_float(ldg_u16(row[r] + (size_t)bk * BS));
+#pragma unroll
+                    for (int b = 0; b < NB; b++) part[r][b] = 0.f;
+                }
 #pragma unroll
                 for (int i = 0; i < QW; i++) {
                     float wv[R][N];
 #pragma unroll
                     for (int r = 0; r < R; r++) {
                         const unsigned char *p = row[r] + (size_t)bk * BS;
-                        dequant_word<WT>(ldg_u16(p + 2 + 4 * i) | (ldg_u16(p + 4 + 4 * i) << 16), half_bits_to_float(ldg_u16(p)), wv[r]);
+                        dequant_word<WT>(ldg_u16(p + 2 + 4 * i) | (ldg_u16(p + 4 + 4 * i) << 16), wv[r]);
                     }
-                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, bk * 32 + (bk >> 1) + i * N, acc);
+                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, bk * 32 + (bk >> 1) + i * N, part);
                 }
+                add_block<R, NB>(d, part, acc);
             }
         }
     }
@@ -207,9 +242,8 @@ struct MatvecParams {
     int rows, cols, x_ld, y_ld, batch;
 };
 
-template <int WT, int NB>
+template <int WT, int NB, int R>                             // R rows per warp pass
 __global__ void __launch_bounds__(kMvWarps * 32) matvec_kernel(MatvecParams p) {
-    constexpr int R = NB >= 8 ? 2 : 4;                       // rows per warp pass
     extern __shared__ __align__(16) float xs[];
     const int b0 = blockIdx.y * NB;
     const int nb = min(NB, p.batch - b0);
@@ -349,16 +383,21 @@ int launch_matvec_t(const MatvecParams &p, cudaStream_t st) {
     const int nb = batch_tile(p.batch);
     const size_t smem = smem_for<WT>(nb, p.cols);
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "matvec: %d input vectors of %d floats do not fit shared memory", nb, p.cols);
-    const int rows_per_cta = kMvWarps * (nb >= 8 ? 2 : 4);
+    // four rows per warp pass when that still leaves two CTAs of work per SM, else two
+    const bool r4 = nb < 8 && p.rows >= 2 * sm_count() * kMvWarps * 4;
+    const int rows_per_cta = kMvWarps * (r4 ? 4 : 2);
     int gx = (p.rows + rows_per_cta - 1) / rows_per_cta;
-    const int cap = sm_count() * 4;
+    const int cap = sm_count() * 8;
     if (gx > cap) gx = cap;
     dim3 grid(gx, (p.batch + nb - 1) / nb);
     switch (nb) {
-        case 1: return launch_with_smem(matvec_kernel<WT, 1>, grid, smem, st, "matvec", p);
-        case 2: return launch_with_smem(matvec_kernel<WT, 2>, grid, smem, st, "matvec", p);
-        case 4: return launch_with_smem(matvec_kernel<WT, 4>, grid, smem, st, "matvec", p);
-        default: return launch_with_smem(matvec_kernel<WT, 8>, grid, smem, st, "matvec", p);
+        case 1: return r4 ? launch_with_smem(matvec_kernel<WT, 1, 4>, grid, smem, st, "matvec", p)
+                          : launch_with_smem(matvec_kernel<WT, 1, 2>, grid, smem, st, "matvec", p);
+        case 2: return r4 ? launch_with_smem(matvec_kernel<WT, 2, 4>, grid, smem, st, "matvec", p)
+                          : launch_with_smem(matvec_kernel<WT, 2, 2>, grid, smem, st, "matvec", p);
+        case 4: return r4 ? launch_with_smem(matvec_kernel<WT, 4, 4>, grid, smem, st, "matvec", p)
+                          : launch_with_smem(matvec_kernel<WT, 4, 2>, grid, smem, st, "matvec", p);
+        default: return launch_with_smem(matvec_kernel<WT, 8, 2>, grid, smem, st, "matvec", p);
     }
 }
 
@@ -378,7 +417,7 @@ int launch_qkv_t(const QkvParams &p, cudaStream_t st) {
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "qkv_rope_append: %d input vectors of %d floats do not fit shared memory", nb, p.n_embd);
     const int tasks = (p.Hq + 2 * p.Hkv) * (p.D / 2);
     int gx = (tasks + kMvWarps - 1) / kMvWarps;
-    const int cap = sm_count() * 4;
+    const int cap = sm_count() * 8;
     if (gx > cap) gx = cap;
     dim3 grid(gx, (p.batch + nb - 1) / nb);
     switch (nb) {

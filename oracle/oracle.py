@@ -28,7 +28,7 @@ def build(force: bool = False) -> None:
     src = os.path.join(_HERE, "attn_oracle.c")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
         subprocess.check_call(["make", "-s", "-C", _HERE, os.path.join(_HERE, "liboracle.so")])
-    ref = os.path.join(_HERE, "_ref", "libnimllm_ref.so")
+    ref = os.path.join(_HERE, "_ref", "libnimllm_ref_pts.so")      # the later of the two outputs of `make ref`
     root = os.environ.get("REFERENCE_ROOT", "/root/reference")     # the same variable oracle/Makefile reads
     if os.path.exists(os.path.join(root, "src", "kernels.cu")) and (force or not os.path.exists(ref)):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REFERENCE_ROOT={root}"])
@@ -229,11 +229,29 @@ def ref_available() -> bool:
     return os.path.exists(os.path.join(_HERE, "_ref", "libnimllm_ref.so"))
 
 
+_REF_PTS = None
+
+
+def ref_pts_lib():
+    """The same sources built with nvcc --default-stream per-thread (oracle/Makefile): the
+    reference's launches go to a stream that can be captured into a CUDA graph.  None when absent."""
+    global _REF_PTS
+    path = os.path.join(_HERE, "_ref", "libnimllm_ref_pts.so")
+    if _REF_PTS is None and os.path.exists(path):
+        _REF_PTS = _bind_ref(C.CDLL(path))
+    return _REF_PTS
+
+
 def ref_lib() -> C.CDLL:
     """The reference's compiled kernels + the restated Nim host loop. Needs a GPU to call."""
     global _REF
     if _REF is None:
-        R = C.CDLL(os.path.join(_HERE, "_ref", "libnimllm_ref.so"))
+        _REF = _bind_ref(C.CDLL(os.path.join(_HERE, "_ref", "libnimllm_ref.so")))
+    return _REF
+
+
+def _bind_ref(R):
+    if True:
         R.ref_attn_forward.argtypes = [f32p] * 6 + [C.c_int] * 5
         R.ref_attn_backward.argtypes = [f32p] * 9 + [C.c_int] * 4
         R.ref_kvcache_create.restype = C.c_void_p
@@ -254,8 +272,10 @@ def ref_lib() -> C.CDLL:
         R.ref_model_destroy.argtypes = [C.c_void_p]
         R.ref_model_step.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, f32p]
         R.ref_model_prefill_lib.argtypes = [C.c_void_p, i32p, C.c_int, C.c_void_p, f32p]
-        _REF = R
-    return _REF
+        R.ref_model_set_proj.argtypes = [C.c_void_p] * 3
+        R.ref_model_step_graph.argtypes = [C.c_void_p, C.c_int, f32p, C.c_void_p]
+        R.ref_model_graph_available.restype = C.c_int
+    return R
 
 
 def ref_attn_backward(q_rot, k_rot, v, dout, cos, sin, Hq, Hkv, D):

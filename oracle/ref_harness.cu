@@ -49,6 +49,18 @@ void gpu_add(const float *a, const float *b, float *y, int n);
 
 static cublasHandle_t g_cublas = nullptr;
 
+/* The reference launches everything with <<<grid, block>>> on the default stream.  Built normally
+ * that is the legacy stream; built with nvcc --default-stream per-thread (the second library
+ * oracle/Makefile makes from the same sources) it is the per-thread stream, which -- unlike the legacy
+ * one -- can be captured into a CUDA graph.  The harness follows whichever it was built with. */
+#ifdef CUDA_API_PER_THREAD_DEFAULT_STREAM
+#define REF_STREAM cudaStreamPerThread
+#define REF_CAN_CAPTURE 1
+#else
+#define REF_STREAM ((cudaStream_t)0)
+#define REF_CAN_CAPTURE 0
+#endif
+
 #define CK(x)                                                                          \
     do {                                                                               \
         cudaError_t e_ = (x);                                                          \
@@ -73,7 +85,9 @@ extern "C" {
 /* src/gpu.nim:173-181 gpuInit */
 int ref_init(void) {
     if (g_cublas) return 0;
-    return cublasCreate_v2(&g_cublas) == CUBLAS_STATUS_SUCCESS ? 0 : -1;
+    if (cublasCreate_v2(&g_cublas) != CUBLAS_STATUS_SUCCESS) return -1;
+    cublasSetStream_v2(g_cublas, REF_STREAM);       /* the reference never sets one (src/gpu.nim:166-175): default stream */
+    return 0;
 }
 
 /* src/model.nim:469-475,494-508 on DEVICE buffers.  q [S,E], k,v [S,Ekv],
@@ -346,6 +360,11 @@ typedef int (*DecodeFn)(const void *, int, const void *, const void *, int, cons
                         const int32_t *, int, void *, int, float *, int, int, int, int, float, int, void *, size_t,
                         void *);
 
+typedef int (*QkvFn)(const float *, const void *, const void *, const void *, int, float *, float *, float *, const float *,
+                     const float *, const int32_t *, int, void *, void *, int, const int64_t *, int64_t, int64_t, int, int,
+                     int, int, int, int, int, void *);
+typedef int (*WoFn)(const float *, const void *, int, const float *, float *, int, int, int, void *);
+
 struct RefModel {
     int nLayer, nEmbd, nHead, nKvHead, headDim, ffnDim, vocab, maxSeq, maxPrefill;
     const float *wte, *lmHead, *lnFg, *cosTab, *sinTab;
@@ -359,6 +378,10 @@ struct RefModel {
     void *ws;
     size_t wsBytes;
     PrefillFn prefill; RopeAppendFn ropeAppend; DecodeWsFn decodeWs; DecodeFn decode;
+    QkvFn qkv; WoFn woResid;
+    /* whole-token graph: the token id, its position and the attended length live in device memory */
+    int32_t *dPos, *dLen;
+    cudaGraphExec_t graphExec;
 };
 
 static float *dalloc(size_t n) {
@@ -404,6 +427,8 @@ void *ref_model_create(int nLayer, int nEmbd, int nHead, int nKvHead, int headDi
     m->wsBytes = 16u << 20;
     cudaMalloc(&m->ws, m->wsBytes);
     m->prefill = nullptr; m->ropeAppend = nullptr; m->decodeWs = nullptr; m->decode = nullptr;
+    m->qkv = nullptr; m->woResid = nullptr; m->graphExec = nullptr;
+    cudaMalloc(&m->dPos, sizeof(int32_t)); cudaMalloc(&m->dLen, sizeof(int32_t));
     return m;
 }
 
@@ -411,6 +436,12 @@ void ref_model_set_attn(void *h, void *prefill, void *ropeAppend, void *decodeWs
     RefModel *m = (RefModel *)h;
     m->prefill = (PrefillFn)prefill; m->ropeAppend = (RopeAppendFn)ropeAppend;
     m->decodeWs = (DecodeWsFn)decodeWs; m->decode = (DecodeFn)decode;
+}
+
+/* the fused projection entry points of the library under test (impl 2 and the graph) */
+void ref_model_set_proj(void *h, void *qkv, void *woResid) {
+    RefModel *m = (RefModel *)h;
+    m->qkv = (QkvFn)qkv; m->woResid = (WoFn)woResid;
 }
 
 void ref_model_reset(void *h) {                              /* src/model.nim:741-746 */
@@ -430,8 +461,21 @@ void ref_model_destroy(void *h) {
     float *bufs[] = {m->mk, m->mv, m->x, m->xn, m->rms, m->q, m->k, m->v, m->attn, m->proj, m->x2, m->gateo, m->upo,
                      m->sw, m->mlp, m->xnew, m->scores, m->probs, m->logits};
     for (float *p : bufs) cudaFree(p);
-    cudaFree(m->tokIds); cudaFree(m->ws);
+    cudaFree(m->tokIds); cudaFree(m->ws); cudaFree(m->dPos); cudaFree(m->dLen);
+    if (m->graphExec) cudaGraphExecDestroy(m->graphExec);
     delete m;
+}
+
+/* the feed-forward half of a layer, from x2 = x + wo(attn): src/model.nim:518-532 / :851-875 */
+static float *ref_layer_ffn(RefModel *m, int l, int S) {
+    int n = m->nEmbd, f = m->ffnDim;
+    gpu_rmsnorm_affine_fwd(m->x2, m->ln2[l], m->xn, m->rms, S, n);
+    ref_sgemm(2, S, f, n, m->xn, m->gate[l], m->gateo);
+    ref_sgemm(2, S, f, n, m->xn, m->up[l], m->upo);
+    gpu_swiglu_fwd(m->gateo, m->upo, m->sw, S * f);
+    ref_sgemm(2, S, n, f, m->sw, m->down[l], m->mlp);
+    gpu_add(m->x2, m->mlp, m->xnew, S * n);
+    return m->xnew;
 }
 
 /* everything of a layer after the attention block: src/model.nim:510-532 / :842-875 */
@@ -464,6 +508,27 @@ int ref_model_step(void *h, int token, int impl, float *attn_dump, float *logits
     float *cur = x;
     for (int l = 0; l < m->nLayer; l++) {
         gpu_rmsnorm_affine_fwd(cur, m->ln1[l], m->xn, m->rms, 1, n);
+        if (impl == 2) {
+            /* attention AND the projections either side of it from the library: q/k/v projection +
+             * RoPE + append in one launch, decode, output projection + residual in one launch */
+            if (!m->qkv || !m->woResid) return -4;
+            int64_t headStride = (int64_t)m->maxSeq * D, seqStride = headStride * Hkv;
+            float *kcl = m->mk + (size_t)l * seqStride, *vcl = m->mv + (size_t)l * seqStride;
+            int rc = m->qkv(m->xn, m->wq[l], m->wk[l], m->wv[l], 0, m->q, nullptr, nullptr, m->cosTab, m->sinTab, nullptr, pos,
+                            kcl, vcl, 0, nullptr, seqStride, headStride, 0, m->maxSeq, 1, n, Hq, Hkv, D, REF_STREAM);
+            if (rc) return 400 + rc;
+            size_t need = m->decodeWs(1, Hq, Hkv, D, S, 0);
+            if (need > m->wsBytes) return -3;
+            rc = m->decode(m->q, 0, kcl, vcl, 0, nullptr, seqStride, headStride, nullptr, S, m->attn, 0, nullptr, 1, Hq,
+                           Hkv, D, scale, 0, m->ws, need, REF_STREAM);
+            if (rc) return 200 + rc;
+            if (attn_dump) cudaMemcpyAsync(attn_dump + (size_t)l * n, m->attn, n * sizeof(float), cudaMemcpyDeviceToDevice, REF_STREAM);
+            rc = m->woResid(m->attn, m->wo[l], 0, cur, m->x2, 1, n, n, REF_STREAM);
+            if (rc) return 500 + rc;
+            float *nx = ref_layer_ffn(m, l, 1);
+            if (nx == m->xnew) { std::swap(m->x, m->xnew); cur = m->x; }
+            continue;
+        }
         ref_sgemm(2, 1, n, n, m->xn, m->wq[l], m->q);
         ref_sgemm(2, 1, nKv, n, m->xn, m->wk[l], m->k);
         ref_sgemm(2, 1, nKv, n, m->xn, m->wv[l], m->v);
@@ -503,6 +568,86 @@ int ref_model_step(void *h, int token, int impl, float *attn_dump, float *logits
     ref_sgemm(2, 1, m->vocab, n, m->xn, m->lmHead, m->logits);
     pos += 1;
     CK(cudaMemcpy(logits_host, m->logits, (size_t)m->vocab * sizeof(float), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+/* ---- the whole single-token step as ONE CUDA graph (the reference's unused graph bindings,
+ * src/gpu.nim:80-102, and its TODO "CUDA graphs for the single-token forward") ----------------
+ * Same work as ref_model_step with impl 2, but nothing in it depends on host values that change
+ * from token to token: the token id, its position and the attended length are read from device
+ * memory, the decode is sized for the whole cache.  Captured once, replayed per token.  Needs the
+ * build whose default stream can be captured. */
+int ref_model_graph_available(void) { return REF_CAN_CAPTURE; }
+
+static int ref_token_body(RefModel *m) {
+    int n = m->nEmbd, D = m->headDim, Hq = m->nHead, Hkv = m->nKvHead;
+    float scale = 1.0f / sqrtf((float)D);
+    int64_t headStride = (int64_t)m->maxSeq * D, seqStride = headStride * Hkv;
+    size_t need = m->decodeWs(1, Hq, Hkv, D, m->maxSeq, 0);
+    if (need > m->wsBytes) return -3;
+    gpu_embed_fwd(m->wte, m->tokIds, m->x, 1, n);
+    float *cur = m->x, *other = m->xnew;
+    for (int l = 0; l < m->nLayer; l++) {
+        gpu_rmsnorm_affine_fwd(cur, m->ln1[l], m->xn, m->rms, 1, n);
+        float *kcl = m->mk + (size_t)l * seqStride, *vcl = m->mv + (size_t)l * seqStride;
+        int rc = m->qkv(m->xn, m->wq[l], m->wk[l], m->wv[l], 0, m->q, nullptr, nullptr, m->cosTab, m->sinTab, m->dPos, 0, kcl,
+                        vcl, 0, nullptr, seqStride, headStride, 0, m->maxSeq, 1, n, Hq, Hkv, D, REF_STREAM);
+        if (rc) return 400 + rc;
+        rc = m->decode(m->q, 0, kcl, vcl, 0, nullptr, seqStride, headStride, m->dLen, m->maxSeq, m->attn, 0, nullptr, 1, Hq,
+                       Hkv, D, scale, 0, m->ws, need, REF_STREAM);
+        if (rc) return 200 + rc;
+        rc = m->woResid(m->attn, m->wo[l], 0, cur, m->x2, 1, n, n, REF_STREAM);
+        if (rc) return 500 + rc;
+        /* the feed-forward half with explicit buffers (no pointer swapping inside a captured body) */
+        int f = m->ffnDim;
+        gpu_rmsnorm_affine_fwd(m->x2, m->ln2[l], m->xn, m->rms, 1, n);
+        ref_sgemm(2, 1, f, n, m->xn, m->gate[l], m->gateo);
+        ref_sgemm(2, 1, f, n, m->xn, m->up[l], m->upo);
+        gpu_swiglu_fwd(m->gateo, m->upo, m->sw, f);
+        ref_sgemm(2, 1, n, f, m->sw, m->down[l], m->mlp);
+        gpu_add(m->x2, m->mlp, other, n);
+        std::swap(cur, other);
+    }
+    gpu_rmsnorm_affine_fwd(cur, m->lnFg, m->xn, m->rms, 1, n);
+    ref_sgemm(2, 1, m->vocab, n, m->xn, m->lmHead, m->logits);
+    return 0;
+}
+
+/* returns 0, or -5 when this build cannot capture; launches_out (optional): kernel nodes of the graph */
+int ref_model_step_graph(void *h, int token, float *logits_host, int *launches_out) {
+    RefModel *m = (RefModel *)h;
+    if (!REF_CAN_CAPTURE) return -5;
+    if (!m->qkv || !m->woResid || !m->decode) return -4;
+    if (m->mpos + 1 > m->maxSeq) return -2;
+    int32_t pos = m->mpos, len = m->mpos + 1;
+    CK(cudaMemcpyAsync(m->tokIds, &token, sizeof(int), cudaMemcpyHostToDevice, REF_STREAM));
+    CK(cudaMemcpyAsync(m->dPos, &pos, sizeof(int32_t), cudaMemcpyHostToDevice, REF_STREAM));
+    CK(cudaMemcpyAsync(m->dLen, &len, sizeof(int32_t), cudaMemcpyHostToDevice, REF_STREAM));
+    CK(cudaStreamSynchronize(REF_STREAM));
+    if (!m->graphExec) {
+        /* once eagerly (module loading, cuBLAS set-up: none of that may happen inside a capture; the
+         * step is idempotent, the replay below recomputes the same token), then the capture */
+        int rc = ref_token_body(m);
+        if (rc) return rc;
+        CK(cudaStreamSynchronize(REF_STREAM));
+        cudaGraph_t graph = nullptr;
+        CK(cudaStreamBeginCapture(REF_STREAM, cudaStreamCaptureModeThreadLocal));
+        rc = ref_token_body(m);
+        cudaError_t e = cudaStreamEndCapture(REF_STREAM, &graph);
+        if (rc || e != cudaSuccess || !graph) {
+            fprintf(stderr, "ref_harness: capture of the token step failed (%d, %s)\n", rc, cudaGetErrorString(e));
+            return rc ? rc : -6;
+        }
+        size_t nodes = 0;
+        cudaGraphGetNodes(graph, nullptr, &nodes);
+        if (launches_out) *launches_out = (int)nodes;
+        CK(cudaGraphInstantiate(&m->graphExec, graph, 0));
+        cudaGraphDestroy(graph);
+    }
+    CK(cudaGraphLaunch(m->graphExec, REF_STREAM));
+    CK(cudaMemcpyAsync(logits_host, m->logits, (size_t)m->vocab * sizeof(float), cudaMemcpyDeviceToHost, REF_STREAM));
+    CK(cudaStreamSynchronize(REF_STREAM));
+    m->mpos += 1;
     return 0;
 }
 

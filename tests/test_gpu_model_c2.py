@@ -106,3 +106,95 @@ def test_c2_only_attention_swapped():
             assert margins[PROMPT - 1 + first] <= noise, f"free-running stream diverges at step {first} on a clear margin"
     finally:
         R.ref_model_destroy(m)
+
+
+def _model(R, L, context, prefill):
+    keep = _weights()
+    ptrs = np.array([t.data_ptr() for t in keep], np.uint64)
+    m = R.ref_model_create(N_LAYER, N_EMBD, N_HEAD, N_KV, HEAD_DIM, FFN, VOCAB, context, prefill, ptrs)
+    assert m
+    fn = lambda name: C.cast(getattr(L, name), C.c_void_p)
+    R.ref_model_set_attn(m, fn("nimllm_attn_prefill"), fn("nimllm_rope_append"), fn("nimllm_attn_decode_workspace_bytes"),
+                         fn("nimllm_attn_decode"))
+    R.ref_model_set_proj(m, fn("nimllm_qkv_rope_append"), fn("nimllm_wo_residual"))
+    return m, keep
+
+
+def test_c2_attention_and_projections_swapped():
+    """The same model with the attention block AND the steps either side of it from the library
+    (q/k/v projection + RoPE + append in one launch, decode, output projection + residual in one
+    launch; fp32 weights): every layer's attention output within 1e-4 of the reference's token by
+    token, the same argmax stream."""
+    import time
+    R, L = O.ref_lib(), _lib.lib()
+    steps = 384
+    m, keep = _model(R, L, steps, 8)
+    try:
+        logits = np.zeros(VOCAB, np.float32)
+        tokens = np.zeros(steps + 1, np.int32)
+        tokens[:32] = rng(SEED_C2, 2).integers(0, VOCAB, 32)
+        ref_attn = torch.zeros(steps, N_LAYER, N_EMBD, device="cuda")
+        margins = np.zeros(steps)
+        t0 = time.perf_counter()
+        for t in range(steps):
+            assert R.ref_model_step(m, int(tokens[t]), 0, ref_attn[t].data_ptr(), logits) == 0
+            top2 = np.partition(logits, -2)[-2:]
+            margins[t] = top2[1] - top2[0]
+            if t + 1 >= 32:
+                tokens[t + 1] = int(np.argmax(logits))
+        t_ref = time.perf_counter() - t0
+        noise = 1e-4 * float(np.abs(logits).max())
+        lib_attn = torch.zeros(steps, N_LAYER, N_EMBD, device="cuda")
+        mism = []
+        t0 = time.perf_counter()
+        for t in range(steps):
+            assert R.ref_model_step(m, int(tokens[t]), 2, lib_attn[t].data_ptr(), logits) == 0
+            if t + 1 >= 32 and int(np.argmax(logits)) != tokens[t + 1]:
+                mism.append((t, margins[t]))
+        t_lib = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        err = (lib_attn - ref_attn).abs().amax(dim=2) / ref_attn.abs().amax(dim=2).clamp_min(1e-30)
+        print(f"attention + projections swapped: worst per-layer attention rel err {float(err.max()):.2e}; argmax mismatches "
+              f"{len(mism)} of {steps - 31}; {steps / t_ref:.0f} tokens/s reference sequence, {steps / t_lib:.0f} tokens/s swapped (eager)")
+        assert float(err.max()) <= TOL_F32
+        assert all(margin <= noise for _, margin in mism), mism[:5]
+    finally:
+        R.ref_model_destroy(m)
+
+
+def test_c2_whole_token_step_as_one_cuda_graph():
+    """The whole single-token step (embedding to logits, 30 layers) captured once as a CUDA graph
+    and replayed per token while the sequence grows: the same argmax stream and logits as the
+    eager step, and tokens/s of both.  Uses the build of the reference's kernels whose default
+    stream can be captured."""
+    import time
+    P = O.ref_pts_lib()
+    if P is None or not P.ref_model_graph_available():
+        pytest.skip("oracle/_ref/libnimllm_ref_pts.so not built")
+    L = _lib.lib()
+    steps = 256
+    m, keep = _model(P, L, steps, 8)
+    try:
+        logits = np.zeros(VOCAB, np.float32)
+        tokens = rng(SEED_C2, 3).integers(0, VOCAB, steps).astype(np.int32)
+        eager = np.zeros((steps, VOCAB), np.float32)
+        t0 = time.perf_counter()
+        for t in range(steps):
+            assert P.ref_model_step(m, int(tokens[t]), 2, None, eager[t]) == 0
+        t_eager = time.perf_counter() - t0
+        P.ref_model_reset(m)
+        nodes = C.c_int(0)
+        assert P.ref_model_step_graph(m, int(tokens[0]), logits, C.byref(nodes)) == 0       # captures
+        worst, flips = float(np.abs(logits - eager[0]).max()), 0
+        t0 = time.perf_counter()
+        for t in range(1, steps):
+            assert P.ref_model_step_graph(m, int(tokens[t]), logits, None) == 0
+            worst = max(worst, float(np.abs(logits - eager[t]).max()))
+            flips += int(np.argmax(logits) != np.argmax(eager[t]))
+        t_graph = time.perf_counter() - t0
+        print(f"whole-token graph: {nodes.value} nodes, {(steps - 1) / t_graph:.0f} tokens/s replayed vs {steps / t_eager:.0f} tokens/s eager; "
+              f"max |logit difference| {worst:.2e}, argmax flips {flips}")
+        assert worst <= 1e-4 * float(np.abs(eager).max()) and flips == 0
+        assert _lib.lib().nimllm_attn_prefill_status(0) == 0
+    finally:
+        P.ref_model_destroy(m)
