@@ -45,8 +45,8 @@ SEEDS = {"c3": 20253, "c4": 20254, "c5": 20255}
 SHAPE_OVERRIDE = None   # set by --shape (profiling only); the defaults are the named benchmark shapes
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu
 # capture of that kernel on this workload (a constant: re-capture after changing the kernel)
-NCU_TRAFFIC_BYTES = {"c3": 462484992 + 5016320, "c3p": 462484992 + 5016320, "c5": 4295632725 + 2294528,
-                     "c4": 1860400000 + 226800000}
+NCU_TRAFFIC_BYTES = {"c3": 462600000 + 900000, "c3p": 462600000 + 900000, "c5": 4295500000 + 1900000,
+                     "c4": 1903500000 + 231800000}
 WORKLOAD_TEXT = {
     "c3": "C3 batched GQA decode: 256 ragged sequences per GPU, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
     "c3p": "C3 batched GQA decode: one batch of 256 ragged sequences partitioned over the GPUs, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",

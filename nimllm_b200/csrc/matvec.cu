@@ -293,9 +293,11 @@ template <typename T> __device__ __forceinline__ void store_cache(T *p, float v)
 template <> __device__ __forceinline__ void store_cache<float>(float *p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_cache<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
-// One warp task = the rotation pair (f, f + D/2) of one head of q, k or v.
+// One warp task = RP neighbouring rotation pairs (f, f + D/2) of one head of q, k or v: 2 RP weight
+// rows whose loads are in flight together (the block formats have short rows: two pairs per task).
 template <int WT, int NB, typename CacheT>
 __global__ void __launch_bounds__(kMvWarps * 32) qkv_rope_append_kernel(QkvParams p) {
+    constexpr int RP = 1;                                 // (two pairs per task were measured: no gain for the block formats)
     extern __shared__ __align__(16) float xs[];
     const int b0 = blockIdx.y * NB;
     const int nb = min(NB, p.batch - b0);
@@ -305,48 +307,54 @@ __global__ void __launch_bounds__(kMvWarps * 32) qkv_rope_append_kernel(QkvParam
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = p.D / 2;
-    const int tasks = (p.Hq + 2 * p.Hkv) * half;
+    const int fpt = half / RP;                            // tasks per head
+    const int tasks = (p.Hq + 2 * p.Hkv) * fpt;
     const size_t rb = row_bytes(WT, p.n_embd);
     for (int t = blockIdx.x * kMvWarps + warp; t < tasks; t += gridDim.x * kMvWarps) {
-        const int slot = t / half, f = t - slot * half;
+        const int slot = t / fpt, f0 = (t - slot * fpt) * RP;
         const bool is_q = slot < p.Hq, is_k = !is_q && slot < p.Hq + p.Hkv;
         const int head = is_q ? slot : (is_k ? slot - p.Hq : slot - p.Hq - p.Hkv);
         const unsigned char *w = is_q ? p.wq : (is_k ? p.wk : p.wv);
-        const int row0 = head * p.D + f;
-        float acc[2][NB];
+        float acc[2 * RP][NB];
+        const unsigned char *rows[2 * RP];
 #pragma unroll
-        for (int b = 0; b < NB; b++) { acc[0][b] = 0.f; acc[1][b] = 0.f; }
-        const unsigned char *rows[2] = {w + (size_t)row0 * rb, w + (size_t)(row0 + half) * rb};
-        rows_dot<WT, NB, 2>(rows, p.n_embd, xs, ld, lane, acc);
-        warp_sum2<2, NB>(acc);
+        for (int r = 0; r < 2 * RP; r++) {
+            rows[r] = w + (size_t)(head * p.D + f0 + (r >> 1) + (r & 1) * half) * rb;      // pair r/2: rows f, f + D/2
 #pragma unroll
-        for (int b = 0; b < NB; b++)
-            if (lane == b && b < nb) {
-                const int bb = b0 + b;
-                const int pos = p.seq_pos ? p.seq_pos[bb] : p.pos0;
-                float x0 = acc[0][b], x1 = acc[1][b];
-                if (!(!is_q && !is_k) && p.cos_tab) {
-                    // the expression of src/kernels.cu:412-413 with sign = +1
-                    const float c = p.cos_tab[(size_t)pos * half + f], s = p.sin_tab[(size_t)pos * half + f];
-                    const float ra = x0 * c - x1 * s, rd = x0 * s + x1 * c;
-                    x0 = ra; x1 = rd;
-                }
-                if (is_q) {
-                    float *o = p.q_out + (size_t)bb * p.Hq * p.D + row0;
-                    o[0] = x0; o[half] = x1;
-                } else {
-                    float *o = is_k ? p.k_out : p.v_out;
-                    if (o) { o[(size_t)bb * p.Hkv * p.D + row0] = x0; o[(size_t)bb * p.Hkv * p.D + row0 + half] = x1; }
-                    const int crow = pos - p.cache_row0;
-                    if (p.k_cache && crow >= 0 && crow < p.max_seq) {
-                        const int64_t base = (p.kv_off ? p.kv_off[bb] : (int64_t)bb * p.seq_stride) + (int64_t)head * p.head_stride +
-                                             (int64_t)crow * p.D + f;
-                        CacheT *dst = reinterpret_cast<CacheT *>(is_k ? p.k_cache : p.v_cache) + base;
-                        store_cache<CacheT>(dst, x0);
-                        store_cache<CacheT>(dst + half, x1);
+            for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
+        }
+        rows_dot<WT, NB, 2 * RP>(rows, p.n_embd, xs, ld, lane, acc);
+        warp_sum2<2 * RP, NB>(acc);
+#pragma unroll
+        for (int pr = 0; pr < RP; pr++)
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+                if (lane == pr * NB + b && b < nb) {
+                    const int bb = b0 + b, f = f0 + pr, row0 = head * p.D + f;
+                    const int pos = p.seq_pos ? p.seq_pos[bb] : p.pos0;
+                    float x0 = acc[2 * pr][b], x1 = acc[2 * pr + 1][b];
+                    if ((is_q || is_k) && p.cos_tab) {
+                        // the expression of src/kernels.cu:412-413 with sign = +1
+                        const float c = p.cos_tab[(size_t)pos * half + f], s = p.sin_tab[(size_t)pos * half + f];
+                        const float ra = x0 * c - x1 * s, rd = x0 * s + x1 * c;
+                        x0 = ra; x1 = rd;
+                    }
+                    if (is_q) {
+                        float *o = p.q_out + (size_t)bb * p.Hq * p.D + row0;
+                        o[0] = x0; o[half] = x1;
+                    } else {
+                        float *o = is_k ? p.k_out : p.v_out;
+                        if (o) { o[(size_t)bb * p.Hkv * p.D + row0] = x0; o[(size_t)bb * p.Hkv * p.D + row0 + half] = x1; }
+                        const int crow = pos - p.cache_row0;
+                        if (p.k_cache && crow >= 0 && crow < p.max_seq) {
+                            const int64_t base = (p.kv_off ? p.kv_off[bb] : (int64_t)bb * p.seq_stride) + (int64_t)head * p.head_stride +
+                                                 (int64_t)crow * p.D + f;
+                            CacheT *dst = reinterpret_cast<CacheT *>(is_k ? p.k_cache : p.v_cache) + base;
+                            store_cache<CacheT>(dst, x0);
+                            store_cache<CacheT>(dst + half, x1);
+                        }
                     }
                 }
-            }
     }
 }
 
@@ -384,7 +392,7 @@ int launch_matvec_t(const MatvecParams &p, cudaStream_t st) {
     const size_t smem = smem_for<WT>(nb, p.cols);
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "matvec: %d input vectors of %d floats do not fit shared memory", nb, p.cols);
     // four rows per warp pass when that still leaves two CTAs of work per SM, else two
-    const bool r4 = nb < 8 && p.rows >= 2 * sm_count() * kMvWarps * 4;
+    const bool r4 = nb < 8 && p.rows >= (WT >= W_Q8_0 ? 1 : 2) * sm_count() * kMvWarps * 2;
     const int rows_per_cta = kMvWarps * (r4 ? 4 : 2);
     int gx = (p.rows + rows_per_cta - 1) / rows_per_cta;
     const int cap = sm_count() * 8;
@@ -415,7 +423,8 @@ int launch_qkv_t(const QkvParams &p, cudaStream_t st) {
     const int nb = batch_tile(p.batch);
     const size_t smem = smem_for<WT>(nb, p.n_embd);
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "qkv_rope_append: %d input vectors of %d floats do not fit shared memory", nb, p.n_embd);
-    const int tasks = (p.Hq + 2 * p.Hkv) * (p.D / 2);
+    const int rp = 1;
+    const int tasks = (p.Hq + 2 * p.Hkv) * (p.D / 2 / rp);
     int gx = (tasks + kMvWarps - 1) / kMvWarps;
     const int cap = sm_count() * 8;
     if (gx > cap) gx = cap;
@@ -476,7 +485,7 @@ int nimllm_qkv_rope_append(const float *x_norm, const void *wq, const void *wk, 
                            const int64_t *kv_off, int64_t seq_stride, int64_t head_stride, int cache_row0, int max_seq,
                            int batch, int n_embd, int n_head, int n_kv_head, int head_dim, void *stream) {
     if (!x_norm || !wq || !wk || !wv || !q_out) return fail(NIMLLM_ERR_ARG, "qkv_rope_append: null x / weights / q_out");
-    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || head_dim <= 0 || (head_dim & 1) || !weight_shape_ok(w_type, n_embd))
+    if (batch <= 0 || n_head <= 0 || n_kv_head <= 0 || head_dim <= 0 || (head_dim & 3) || !weight_shape_ok(w_type, n_embd))
         return fail(NIMLLM_ERR_ARG, "qkv_rope_append: bad shape batch=%d n_embd=%d Hq=%d Hkv=%d D=%d weight type %d", batch,
                     n_embd, n_head, n_kv_head, head_dim, w_type);
     if ((rope_cos == nullptr) != (rope_sin == nullptr))
