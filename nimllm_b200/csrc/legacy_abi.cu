@@ -2,8 +2,8 @@
 // names and argument lists (src/kernels.cu, bound in src/gpu.nim:227-248,274-276,309-311),
 // so that code which still walks the unfused sequence (backward(), the test programs)
 // links against this library alone.  Same semantics: void return, legacy default stream,
-// fp32.  The kernels are new: vector accesses where the shapes allow, warp-shuffle
-// reductions in the softmax, and the fused fp32 flash kernel behind gpu_flash_attn_fwd.
+// fp32.  The kernels are new: grid-stride element loops, warp-shuffle reductions in the
+// softmax, and the fused fp32 flash kernel behind gpu_flash_attn_fwd.
 #include <float.h>
 
 #include "common.cuh"
@@ -157,7 +157,10 @@ void gpu_softmax_fwd(const float *x, float *y, int rows, int cols) {
 void gpu_flash_attn_fwd(const float *Q, const float *K, const float *V, float *O, int S, int hd,
                         float scale, int causal) {
     if (S <= 0) return;
-    launch_prefill_f32(Q, K, V, O, nullptr, 1, S, 1, 1, hd, scale, causal, 0);
+    // the void return cannot carry an error (the reference's launcher takes any hd up to 256,
+    // src/kernels.cu:750-755; the fp32 flash kernel here is built for 32, 64 and 128): say so
+    if (launch_prefill_f32(Q, K, V, O, nullptr, 1, S, 1, 1, hd, scale, causal, 0))
+        fprintf(stderr, "gpu_flash_attn_fwd: %s\n", nimllm_attn_last_error());
 }
 
 }  // extern "C"

@@ -6,9 +6,9 @@ SHA-256 of the inputs guards against drift of the generator.
     python tests/golden/make_golden.py
 
 The reference's own tests hold no vector for multi-token attention (its checks stop at the
-Q projection or at S = 1), so these fixtures pin the mathematics, and
-attn_ref_golden.npz (made by make_ref_golden.py on a GPU from the reference's compiled
-kernels) pins the reference's arithmetic.
+Q projection or at S = 1), so these fixtures pin the mathematics; the reference's
+arithmetic is pinned by running its own compiled kernels beside the library in the GPU
+tests (tests/test_gpu_prefill_f32.py, tests/test_gpu_model_c2.py), not by a stored file.
 """
 import hashlib
 import os
