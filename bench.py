@@ -359,6 +359,33 @@ def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
             graphed = True
         except Exception as e:  # pragma: no cover
             log(f"CUDA graph capture of the sharded step failed ({e}); timing eager launches")
+    if not sharded and not args.eager:
+        # the decode step (decode kernel + its merge launch, a programmatic dependent) replayed as a
+        # CUDA graph, one graph per replica of the cache: what a serving loop does with a step whose
+        # launches do not depend on host values
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(len(w["kcs"])):
+                    step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graphs = []
+            for _ in range(len(w["kcs"])):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    step()
+                graphs.append(g)
+            gturn = [0]
+
+            def step():
+                gturn[0] = (gturn[0] + 1) % len(graphs)
+                graphs[gturn[0]].replay()
+            graphed = True
+        except Exception as e:  # pragma: no cover
+            log(f"CUDA graph capture of the decode step failed ({e}); timing eager launches")
+            step = eager_step
     flush = None        # inputs larger than L2 (see decode_workload); no flush kernel
     sampler = ClockSampler(dist.local)
     with sampler:
@@ -367,9 +394,8 @@ def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
     # with its own clock record: a long loop meets the power cap, the short timed region does not
     sus_sampler = ClockSampler(dist.local)
     with sus_sampler:
-        sus_ms, sus_steps = sustained_loop(torch, eager_step if not graphed else step, sum(ms) / len(ms), dist,
-                                           seconds=args.sustain, unit_steps=1 if graphed else len(w["kcs"]),
-                                           capture=not graphed) \
+        sus_ms, sus_steps = sustained_loop(torch, step, sum(ms) / len(ms), dist, seconds=args.sustain,
+                                           unit_steps=1 if graphed else len(w["kcs"]), capture=not graphed) \
             if args.sustain > 0 and not sharded else (None, 0)   # (ranks that wait for each other: the timed steps say it all)
     t_local = sum(ms) / 1e3
     t_max = dist.max(t_local)
@@ -435,6 +461,8 @@ def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
         parallelism = f"one batch of 256 sequences split over {dist.world} GPU(s) by greedy longest-first on KV rows, no collective"
     else:
         parallelism = f"independent sequences x{dist.world}, no collective"
+    if graphed and not sharded:
+        parallelism += "; step replayed as a CUDA graph"
     n_tokens = {"c3": B * dist.world, "c3p": 256, "c5": B}[name]
     line = {
         "metric": "decode_attn_kv_gbps", "value": round(value, 2), "unit": "GB/s", "n_gpus": dist.world,
@@ -462,7 +490,7 @@ def run_decode(args, dist, name, with_e2e=True, with_cpu=True):
         line["sustained"] = {"ms_per_step": round(sus_ms, 5), "steps": sus_steps,
                              "value": round(total_bytes / (sus_ms / 1e3) / 1e9, 2), "unit": "GB/s",
                              "frac": round(float(w["bytes"]) / (sus_ms / 1e3) / 1e9 / pk["hbm"], 4),
-                             "how": "back-to-back steps for about two seconds, replayed as a CUDA graph, one event pair",
+                             "how": "back-to-back graph-replayed steps for about two seconds, one event pair",
                              "clocks": sus_sampler.summary()}
     if e2e is not None:
         line["e2e"] = e2e
@@ -689,6 +717,7 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all", "c3", "c3p", "c5", "c4"])
     ap.add_argument("--sustain", type=float, default=2.0, help="seconds of the back-to-back sustained loop per workload (0: skip)")
     ap.add_argument("--chunk-rows", type=int, default=0)
+    ap.add_argument("--eager", action="store_true", help="decode workloads: launch the step's kernels eagerly instead of replaying a graph")
     ap.add_argument("--page-rows", type=int, default=0,
                     help="c3 / c5 on one GPU: store the cache in shuffled pages of this many rows and time the paged decode")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
