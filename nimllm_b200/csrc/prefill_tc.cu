@@ -70,7 +70,7 @@ template <int kD> struct Smem {
     uint8_t q[2][tile_bytes<kD>()];
     uint8_t k[kKSlots][tile_bytes<kD>()];
     uint8_t v[kVSlots][tile_bytes<kD>()];
-    uint64_t q_full, k_full[kKSlots], k_empty[kKSlots], v_full[kVSlots], v_empty[kVSlots];
+    uint64_t q_full[2], k_full[kKSlots], k_empty[kKSlots], v_full[kVSlots], v_empty[kVSlots];
     uint64_t s_full[2], pv_done[2], o_full[2], drain;
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -119,7 +119,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     volatile int *abort_flag = &sm.abort_flag;
 
     if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, p.rotate_q ? 8 : 1);
+        mbar_init(&sm.q_full[0], p.rotate_q ? 8 : 1);
+        mbar_init(&sm.q_full[1], p.rotate_q ? 8 : 1);
         for (int s = 0; s < kKSlots; s++) { mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1); }
         for (int s = 0; s < kVSlots; s++) { mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1); }
         for (int w = 0; w < 2; w++) {
@@ -150,10 +151,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const int qx = h * kD, kx = kvh * kD;
             const int y0 = b * p.S + row_base;
             if (!p.rotate_q) {
-                mbar_expect_tx(&sm.q_full, active1 ? 2 * kTileBytes : kTileBytes);
+                mbar_expect_tx(&sm.q_full[0], kTileBytes);
+                if (active1) mbar_expect_tx(&sm.q_full[1], kTileBytes);
                 for (int bx = 0; bx < kBoxes; bx++) {
-                    tma_load_2d(sm.q[0] + bx * kBoxBytes, &q_map, qx + bx * 64, y0, &sm.q_full);
-                    if (active1) tma_load_2d(sm.q[1] + bx * kBoxBytes, &q_map, qx + bx * 64, y0 + kBM, &sm.q_full);
+                    tma_load_2d(sm.q[0] + bx * kBoxBytes, &q_map, qx + bx * 64, y0, &sm.q_full[0]);
+                    if (active1) tma_load_2d(sm.q[1] + bx * kBoxBytes, &q_map, qx + bx * 64, y0 + kBM, &sm.q_full[1]);
                 }
             }
             // K_j goes to slot j % kKSlots (phase (j / kKSlots) & 1), V_j to slot j % kVSlots; loads
@@ -193,8 +195,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const uint32_t q_lo0 = ((smem_u32(sm.q[0]) >> 4) & 0x3FFFu) | kLboK, q_lo1 = ((smem_u32(sm.q[1]) >> 4) & 0x3FFFu) | kLboK;
             const uint32_t k_base = smem_u32(sm.k[0]), v_base = smem_u32(sm.v[0]);
             const uint32_t s_tmem = tmem + kColS;
-            bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
-            tc_fence_after();
+            bool ok = true;
             // S = Q_w K_j^T : kD/16 steps of 16 along D; both operands K-major, 128-byte swizzle,
             // 1024 bytes between 8-row groups; a step advances 32 bytes inside the 128-byte row
             auto issue_fill = [&](int w, int j) {
@@ -233,6 +234,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             auto fill = [&](int w, int j) {
                 if (!ok) return;
                 if (fills > 0) { named_sync(kBarSFree, 160); if (*abort_flag) { ok = false; return; } }
+                // each tile's Q has a barrier of its own: tile 0 starts while tile 1 is still being rotated
+                if (j == 0 && !(ok = mbar_wait(&sm.q_full[w], 0, abort_flag))) return;
                 if (j > k_known) {
                     if (!(ok = mbar_wait(&sm.k_full[j % kKSlots], (j / kKSlots) & 1, abort_flag))) return;
                     k_known = j;
@@ -341,11 +344,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8)) = rlo;
                     *reinterpret_cast<uint4 *>(sm.q[tile_i] + tile_offset(rr, c8 + kD / 2)) = rhi;
                 }
+                // a batch of four steps covers 128 rows at head size 128 (= one query tile: hand it
+                // over now) and all 256 rows at head size 64; the generic-proxy stores are made
+                // visible to the tensor core's async proxy first
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    if (kLpr / 4 == 2) mbar_arrive(&sm.q_full[half_i]);
+                    else { mbar_arrive(&sm.q_full[0]); mbar_arrive(&sm.q_full[1]); }
+                }
             }
-            // make the generic-proxy stores visible to the tensor core's async proxy
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.q_full);
         }
 
         float m_ref = -INFINITY, l = 0.f;
