@@ -43,14 +43,16 @@ __host__ __device__ inline size_t row_bytes(int wt, int cols) {
 template <int WT> __device__ __forceinline__ int xs_index(int j) { return (WT >= W_Q8_0) ? j + (j >> 6) : j; }
 template <int WT> __host__ __device__ inline int xs_stride(int cols) { return (WT >= W_Q8_0) ? cols + cols / 64 + 4 : cols; }
 
+// 4- and 2-byte loads of block data: neighbouring lanes and the loads of one lane share 32-byte
+// sectors, so these allocate in L1 (every sector then comes out of L2 once per SM, not once per load)
 __device__ __forceinline__ uint32_t ldg_u32(const void *p) {
     uint32_t r;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r) : "l"(p));
     return r;
 }
 __device__ __forceinline__ uint32_t ldg_u16(const void *p) {
     uint16_t r;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(r) : "l"(p));
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
     return r;
 }
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)(h & 0xffffu))); }
