@@ -164,6 +164,41 @@ int nimllm_rope_append_paged(void *q, int n_head, void *k_new, const void *v_new
                              const int32_t *page_table, int max_pages, int page_rows, int n_pages, int batch,
                              int n, int n_kv_head, int head_dim, void *stream);
 
+/* ---- block manager of the paged KV cache ----------------------------------------------------
+ * Replaces the reference's cache policy: one conversation, one [blockSize, D] buffer per
+ * (layer, KV head), everything dropped when the next turn would not fit (src/chat.nim:86-91,
+ * resetKvCache at src/model.nim:741-743).  A pool owns n_pages pages per layer, shared by up to
+ * max_seqs sequences; a sequence holds ceil(rows / page_rows) of them, a finished one gives them
+ * back, and a request that does not fit is refused alone (NIMLLM_ERR_WORKSPACE, nothing changed)
+ * so the caller can release a sequence of its choosing.  All layers of a sequence use the same
+ * page numbers, so there is ONE table.  Host bookkeeping only, no kernel of its own:
+ *   create(..., on_device)   on_device = 1 allocates K and V pages (zero-filled) and the device
+ *                            table; 0 keeps only the host table (callers that own the memory, and
+ *                            machines without a GPU) -- k(), v() and table() then return NULL
+ *   reserve(seq, rows_total) pages for rows 0 .. rows_total-1 of sequence slot `seq`; never shrinks
+ *   release(seq)             all pages of the slot back to the free list
+ *   sync(stream)             uploads the table rows changed since the last sync, on `stream`,
+ *                            before the launches that read them
+ *   table(first_seq)         device int32 [max_seqs - first_seq][max_pages]: the page_table
+ *                            argument of the two paged entry points for the batch of sequence
+ *                            slots first_seq, first_seq+1, ...  (entries without a page are -1)
+ *   k(layer), v(layer)       [n_pages][n_kv_head][page_rows][head_dim] of that layer
+ * Not thread-safe: one pool, one calling thread at a time. */
+typedef struct nimllm_kvpool nimllm_kvpool;
+nimllm_kvpool *nimllm_kvpool_create(int n_layer, int n_pages, int page_rows, int n_kv_head, int head_dim,
+                                    int dtype, int max_seqs, int max_pages_per_seq, int on_device);
+void nimllm_kvpool_destroy(nimllm_kvpool *pool);
+int nimllm_kvpool_reserve(nimllm_kvpool *pool, int seq, int rows_total);
+int nimllm_kvpool_release(nimllm_kvpool *pool, int seq);
+int nimllm_kvpool_sync(nimllm_kvpool *pool, void *stream);
+int nimllm_kvpool_free_pages(const nimllm_kvpool *pool);
+int nimllm_kvpool_seq_pages(const nimllm_kvpool *pool, int seq);
+int nimllm_kvpool_seq_rows(const nimllm_kvpool *pool, int seq);
+const int32_t *nimllm_kvpool_table_host(const nimllm_kvpool *pool);
+const int32_t *nimllm_kvpool_table(const nimllm_kvpool *pool, int first_seq);
+void *nimllm_kvpool_k(const nimllm_kvpool *pool, int layer);
+void *nimllm_kvpool_v(const nimllm_kvpool *pool, int layer);
+
 /* ---- GQA decode for callers that cannot allocate ------------------------------------
  * No counterpart in the reference.  Same computation and arguments as nimllm_attn_decode,
  * minus the workspace: the chunk records of split sequences go to a fixed 8 MiB array that

@@ -34,6 +34,18 @@ PROTOTYPES = {
                                  i32, i32, i32, i32, i32, i32, vp]),
     "nimllm_rope_append_paged": (i32, [vp, i32, vp, vp, i32, i32, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32,
                                        i32, i32, i32, i32, vp]),
+    "nimllm_kvpool_create": (vp, [i32, i32, i32, i32, i32, i32, i32, i32, i32]),
+    "nimllm_kvpool_destroy": (None, [vp]),
+    "nimllm_kvpool_reserve": (i32, [vp, i32, i32]),
+    "nimllm_kvpool_release": (i32, [vp, i32]),
+    "nimllm_kvpool_sync": (i32, [vp, vp]),
+    "nimllm_kvpool_free_pages": (i32, [vp]),
+    "nimllm_kvpool_seq_pages": (i32, [vp, i32]),
+    "nimllm_kvpool_seq_rows": (i32, [vp, i32]),
+    "nimllm_kvpool_table_host": (vp, [vp]),
+    "nimllm_kvpool_table": (vp, [vp, i32]),
+    "nimllm_kvpool_k": (vp, [vp, i32]),
+    "nimllm_kvpool_v": (vp, [vp, i32]),
     "nimllm_attn_decode_plan": (i32, [vp, i32, i32, i32, i32, vp, i32, vp]),
     "nimllm_attn_decode_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "nimllm_attn_decode": (i32, [vp, i32, vp, vp, i32, vp, i64, i64, vp, i32, vp, i32, vp, i32, i32, i32,

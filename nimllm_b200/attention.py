@@ -8,6 +8,8 @@
   forward()'s attention block (:494-508)          attn_forward()
   forwardCached()'s attention block (:788-840)    attn_forward_cached()
   (no counterpart: batch 1 only)                  decode_batch(), combine()
+  chat loop's reset-when-full cache policy        PagedKvPool (pages shared by many sequences),
+    (src/chat.nim:86-91)                            rope_append_paged(), decode_paged()
 
 torch is used for device memory and streams only; every computation goes through
 libnimllm_attn.so and raises if that library is missing or reports an error."""
@@ -91,6 +93,80 @@ class KvCache:
         self.k.zero_()
         self.v.zero_()
         self.pos = 0
+
+
+class _DeviceView:
+    """Device memory owned by the library, shown to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr, shape, typestr, owner):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+        self._owner = owner
+
+
+class PagedKvPool:
+    """The library's block manager of the paged cache (nimllm_kvpool_*): pages shared by up to max_seqs
+    sequences instead of the reference's one-conversation cache that is reset when full
+    (src/chat.nim:86-91).  on_device=False keeps only the host table (no CUDA call)."""
+
+    def __init__(self, n_layer, n_pages, page_rows, n_kv_head, head_dim, max_seqs, max_pages_per_seq,
+                 dtype=torch.bfloat16, on_device=True):
+        self.shape = (n_pages, n_kv_head, page_rows, head_dim)
+        self.n_layer, self.max_seqs, self.max_pages, self.dtype, self.on_device = n_layer, max_seqs, max_pages_per_seq, dtype, on_device
+        self._h = lib().nimllm_kvpool_create(n_layer, n_pages, page_rows, n_kv_head, head_dim, _DT[dtype], max_seqs,
+                                             max_pages_per_seq, int(on_device))
+        if not self._h:
+            raise _lib.NimllmAttnError(lib().nimllm_attn_last_error().decode())
+
+    def close(self):
+        if self._h:
+            lib().nimllm_kvpool_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def reserve(self, seq: int, rows_total: int):
+        check(lib().nimllm_kvpool_reserve(self._h, seq, rows_total))
+
+    def release(self, seq: int):
+        check(lib().nimllm_kvpool_release(self._h, seq))
+
+    def sync(self):
+        check(lib().nimllm_kvpool_sync(self._h, _stream() if self.on_device else None))
+
+    @property
+    def free_pages(self) -> int:
+        return lib().nimllm_kvpool_free_pages(self._h)
+
+    def seq_pages(self, seq: int) -> int:
+        return lib().nimllm_kvpool_seq_pages(self._h, seq)
+
+    def seq_rows(self, seq: int) -> int:
+        return lib().nimllm_kvpool_seq_rows(self._h, seq)
+
+    def table_host(self) -> np.ndarray:
+        import ctypes
+        buf = (ctypes.c_int32 * (self.max_seqs * self.max_pages)).from_address(lib().nimllm_kvpool_table_host(self._h))
+        return np.frombuffer(buf, dtype=np.int32).reshape(self.max_seqs, self.max_pages).copy()
+
+    def table(self, first_seq: int = 0) -> torch.Tensor:
+        ptr = lib().nimllm_kvpool_table(self._h, first_seq)
+        if not ptr:
+            raise _lib.NimllmAttnError("the pool has no device table (on_device=False or bad first_seq)")
+        return torch.as_tensor(_DeviceView(ptr, (self.max_seqs - first_seq, self.max_pages), "<i4", self), device="cuda")
+
+    def _pages(self, fn, layer):
+        ptr = fn(self._h, layer)
+        if not ptr:
+            raise _lib.NimllmAttnError("the pool has no device pages (on_device=False or bad layer)")
+        if self.dtype == torch.float32:
+            return torch.as_tensor(_DeviceView(ptr, self.shape, "<f4", self), device="cuda")
+        return torch.as_tensor(_DeviceView(ptr, self.shape, "<i2", self), device="cuda").view(torch.bfloat16)
+
+    def k(self, layer: int) -> torch.Tensor:
+        return self._pages(lib().nimllm_kvpool_k, layer)
+
+    def v(self, layer: int) -> torch.Tensor:
+        return self._pages(lib().nimllm_kvpool_v, layer)
 
 
 def rope_append(q, k_new, v_new, cos, sin, *, n_head, n_kv_head, head_dim, pos0=0, seq_pos=None,

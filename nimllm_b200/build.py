@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnimllm_attn.so")
-SOURCES = ["abi.cu", "rope_append.cu", "decode.cu", "prefill_f32.cu", "prefill_tc.cu", "prefill_bwd.cu", "legacy_abi.cu", "peer.cu", "matvec.cu"]
+SOURCES = ["abi.cu", "rope_append.cu", "decode.cu", "prefill_f32.cu", "prefill_tc.cu", "prefill_bwd.cu", "legacy_abi.cu", "peer.cu", "matvec.cu", "kvpool.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
