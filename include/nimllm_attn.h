@@ -266,6 +266,12 @@ int nimllm_wo_residual(const float *attn_out, const void *wo, int w_type, const 
  * y and residual (optional) [batch, rows], fp32. */
 int nimllm_matvec(const void *w, int w_type, const float *x, const float *residual, float *y, int batch, int rows,
                   int cols, void *stream);
+/* The staged form of the projection kernels (eight input vectors per tile) waits for its weight copies
+ * with a bound (about 2 s without progress); a launch in which a wait gave up leaves incomplete results
+ * and raises a per-device status word that stays raised until it is cleared.  Returns 0, 1 (raised) or
+ * a negative NIMLLM_ERR_* code; reset != 0 clears the word.  Synchronises the device: call it where the
+ * host waits for results anyway.  No counterpart in the reference. */
+int nimllm_matvec_status(int reset);
 
 /* ---- merge of (max, sum, output) partials ----------------------------------------
  * No counterpart in the reference (it never splits a softmax row, src/kernels.cu:

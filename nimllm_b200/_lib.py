@@ -59,6 +59,7 @@ PROTOTYPES = {
                                      i32, i32, i32, i32, i32, vp]),
     "nimllm_wo_residual": (i32, [vp, vp, i32, vp, vp, i32, i32, i32, vp]),
     "nimllm_matvec": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, vp]),
+    "nimllm_matvec_status": (i32, [i32]),
     "nimllm_attn_combine": (i32, [vp, i32, i32, i32, i32, vp, i32, vp, vp]),
     "nimllm_peer_exchange_create": (vp, [i32, i32, i32, i32]),
     "nimllm_peer_exchange_export": (i32, [vp, vp]),

@@ -271,6 +271,15 @@ def matvec(w, x, rows, *, w_type=None, residual=None):
     return y
 
 
+def matvec_status(reset: bool = True) -> int:
+    """0 when every staged projection launch since the last reset ran to completion, 1 when a bounded wait
+    for weight copies gave up (results of that launch are incomplete).  Synchronises the device."""
+    rc = lib().nimllm_matvec_status(int(reset))
+    if rc < 0:
+        check(-rc)
+    return rc
+
+
 def combine(parts, head_dim, out_dtype=torch.float32, partials=False):
     """Merge (o, m, l) records [n_parts, rows, D+4] -> out [rows, D]."""
     n_parts, rows, W = parts.shape

@@ -22,15 +22,23 @@
 // memory, padded by one float per 64 for the block formats so that lanes reading different
 // block pairs hit different banks.  A warp takes several rows per pass (their loads are in flight
 // together, and every input value read from shared memory serves all of them).
+//
+// Two forms of every kernel: the weights loaded straight into registers (few input vectors), or
+// staged through shared memory by the copy engine (eight input vectors per tile; see
+// use_staged_matvec / use_staged_qkv for the measured crossover).
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace nimllm {
 namespace {
+using namespace tc;       // mbarrier and shared-memory address helpers
 
 constexpr int kMaxBatch = 8;      // input vectors served per weight fetch
 constexpr int kMvWarps = 8;
+constexpr int kStWarps = 8;       // warps of a staged kernel's CTA (one CTA per SM; 12 and 16 warps were measured: no gain)
+__device__ int g_matvec_status = 0;   // sticky: 1 after a weight copy did not arrive within the wait limit
 
 enum { W_F32 = 0, W_BF16 = 1, W_Q8_0 = 2, W_Q4_0 = 3 };
 
@@ -55,6 +63,25 @@ __device__ __forceinline__ uint32_t ldg_u16(const void *p) {
     asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
     return r;
 }
+// the same from the staging ring in shared memory
+__device__ __forceinline__ uint32_t lds_u32(const void *p) {
+    uint32_t r;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(smem_u32(p)));
+    return r;
+}
+__device__ __forceinline__ uint32_t lds_u16(const void *p) {
+    uint16_t r;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(r) : "r"(smem_u32(p)));
+    return r;
+}
+__device__ __forceinline__ uint4 lds_v4(const void *p) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(smem_u32(p)));
+    return r;
+}
+template <bool SM> __device__ __forceinline__ uint32_t ld_u32(const void *p) { return SM ? lds_u32(p) : ldg_u32(p); }
+template <bool SM> __device__ __forceinline__ uint32_t ld_u16(const void *p) { return SM ? lds_u16(p) : ldg_u16(p); }
+template <bool SM> __device__ __forceinline__ uint4 ld_v4(const void *p) { return SM ? lds_v4(p) : ldg_stream(p); }
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)(h & 0xffffu))); }
 
 // acc[r][b] += sum_e wv[r][e] * x_b[j0 + e] for N consecutive weights of R rows: every input value
@@ -116,7 +143,7 @@ template <int R, int NB> __device__ __forceinline__ void add_block(const float (
 
 // Partial dot products of R weight rows with NB input vectors: this lane's share (lanes stride over
 // the row, the loads of all R rows are in flight together); the caller adds the lanes up.
-template <int WT, int NB, int R>
+template <int WT, int NB, int R, bool SM = false>
 __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], int cols, const float *xs, int xs_ld, int lane,
                                          float (&acc)[R][NB]) {
     if (WT == W_F32 || WT == W_BF16) {
@@ -128,8 +155,8 @@ __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], i
             uint4 u[2][R];
 #pragma unroll
             for (int r = 0; r < R; r++) {
-                u[0][r] = ldg_stream(row[r] + (size_t)j * EB);
-                u[1][r] = has2 ? ldg_stream(row[r] + (size_t)j2 * EB) : make_uint4(0, 0, 0, 0);
+                u[0][r] = ld_v4<SM>(row[r] + (size_t)j * EB);
+                u[1][r] = has2 ? ld_v4<SM>(row[r] + (size_t)j2 * EB) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int h = 0; h < 2; h++) {
@@ -162,7 +189,7 @@ __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], i
 #pragma unroll
                 for (int r = 0; r < R; r++)
 #pragma unroll
-                    for (int i = 0; i < 2 * QW + 1; i++) w[r][i] = ldg_u32(row[r] + (size_t)pr * (2 * BS) + 4 * i);
+                    for (int i = 0; i < 2 * QW + 1; i++) w[r][i] = ld_u32<SM>(row[r] + (size_t)pr * (2 * BS) + 4 * i);
                 const int base = pr * 65;                     // 64 weights + 1 pad float per pair
                 float part[R][NB], d[R];
 #pragma unroll
@@ -196,7 +223,7 @@ __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], i
                 float part[R][NB], d[R];
 #pragma unroll
                 for (int r = 0; r < R; r++) {
-                    d[r] = half_bits_to_float(ldg_u16(row[r] + (size_t)bk * BS));
+                    d[r] = half_bits_to_float(ld_u16<SM>(row[r] + (size_t)bk * BS));
 #pragma unroll
                     for (int b = 0; b < NB; b++) part[r][b] = 0.f;
                 }
@@ -206,7 +233,7 @@ __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], i
 #pragma unroll
                     for (int r = 0; r < R; r++) {
                         const unsigned char *p = row[r] + (size_t)bk * BS;
-                        dequant_word<WT>(ldg_u16(p + 2 + 4 * i) | (ldg_u16(p + 4 + 4 * i) << 16), wv[r]);
+                        dequant_word<WT>(ld_u16<SM>(p + 2 + 4 * i) | (ld_u16<SM>(p + 4 + 4 * i) << 16), wv[r]);
                     }
                     fma_chunk<R, NB, N, false>(wv, xs, xs_ld, bk * 32 + (bk >> 1) + i * N, part);
                 }
@@ -229,10 +256,172 @@ template <int R, int NB> __device__ __forceinline__ void warp_sum2(float (&acc)[
 template <int WT>
 __device__ __forceinline__ void stage_x(float *xs, const float *x, int cols, int x_ld, int nb) {
     const int ld = xs_stride<WT>(cols);
-    for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
-        const int b = i / cols, j = i - b * cols;
-        xs[b * ld + xs_index<WT>(j)] = x[(size_t)b * x_ld + j];
+    // 16-byte loads, four per thread in flight (cols is a multiple of 4 for every weight type; a group of
+    // four floats never straddles a 64-float pad boundary).  x rows are 16-byte aligned when x and x_ld are.
+    const int c4 = cols >> 2, n4 = nb * c4;
+    if ((((uintptr_t)x | ((uintptr_t)x_ld << 2)) & 15) == 0) {
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * blockDim.x;
+                if (i < n4) {
+                    const int b = i / c4, j4 = i - b * c4;
+                    v[u] = *reinterpret_cast<const float4 *>(x + (size_t)b * x_ld + 4 * j4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * blockDim.x;
+                if (i < n4) {
+                    const int b = i / c4, j = 4 * (i - b * c4);
+                    float *d = xs + b * ld + xs_index<WT>(j);
+                    if (WT >= W_Q8_0) { d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w; }
+                    else *reinterpret_cast<float4 *>(d) = v[u];
+                }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < nb * cols; i += blockDim.x) {
+            const int b = i / cols, j = i - b * cols;
+            xs[b * ld + xs_index<WT>(j)] = x[(size_t)b * x_ld + j];
+        }
     }
+}
+
+// ------------------------------------------------------------------ weights staged by bulk copies
+// The weight bytes reach the SM through the copy engine, not through the warps' load instructions:
+// every warp runs a ring of its own -- lane 0 issues cp.async.bulk copies of the next row segments
+// into shared memory (completion counted on an mbarrier of the slot), the warp computes on the
+// segment that has arrived.  Many KB per warp are in flight without a register holding them, and the
+// block formats' 34- and 18-byte blocks are read from shared memory at full rate (lanes 68 or 36
+// bytes apart: odd word strides, no bank conflicts) instead of as scattered 4-byte global loads.
+//
+// A job is two weight rows (the rotation pair f, f + D/2 of a head, or two neighbouring rows); an
+// item is segment s of both rows.  A bulk copy wants 16-byte aligned addresses and sizes: a segment
+// is copied from its address rounded down to 16 bytes up to its end rounded up, clipped to the last
+// 16-byte boundary inside the matrix; the few bytes past that boundary come through the lanes.
+struct SlabGeom {
+    int cols, segw, nseg;     // weights per row, per segment, segments per row
+    int nstage, slot_half;    // ring depth per warp, bytes of one row's buffer in a slot (a slot = 2 of them)
+};
+__host__ __device__ inline int seg_weights(int wt) { return wt == W_F32 ? 512 : wt == W_BF16 ? 1024 : wt == W_Q8_0 ? 2048 : 4096; }
+
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t ldg_u8(const void *p) {
+    uint32_t r;
+    asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+// waits for copies that are in flight whatever the abort flag says (a CTA must not exit under them)
+__device__ __forceinline__ bool mbar_wait_drain(uint64_t *bar, uint32_t parity) {
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 255) == 255 && globaltimer_ns() - t0 > 1000000000ull) return false;
+    }
+}
+
+// rows_of(jj, row, wend): global pointers to the two rows of this warp's jj-th job and the ends of
+// their matrices; finish(jj, acc): the lanes' partial sums of a finished job.
+template <int WT, typename RowsOf>
+__device__ __forceinline__ void slab_issue(uint8_t *ring, uint64_t *full, const SlabGeom &g, int k, int lane, RowsOf rows_of) {
+    const int jj = k / g.nseg, s = k - jj * g.nseg, slot = k % g.nstage;
+    const unsigned char *row[2], *wend[2];
+    rows_of(jj, row, wend);
+    const int c0 = s * g.segw, nc = min(g.segw, g.cols - c0);
+    const size_t off = row_bytes(WT, c0);
+    const uint32_t len = (uint32_t)row_bytes(WT, nc);
+    uint8_t *dst = ring + (size_t)slot * 2 * g.slot_half;
+    uintptr_t ga0[2], ge0[2];
+    uint32_t tx = 0;
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const uintptr_t ga = (uintptr_t)row[r] + off, ge = ga + len;
+        const uintptr_t ge_up = (ge + 15) & ~(uintptr_t)15, w_dn = (uintptr_t)wend[r] & ~(uintptr_t)15;
+        ga0[r] = ga & ~(uintptr_t)15;
+        ge0[r] = ge_up < w_dn ? ge_up : w_dn;
+        tx += (uint32_t)(ge0[r] - ga0[r]);
+        // bytes past the last 16-byte boundary of the matrix (at most 15): through the lanes
+        const int tail = ge > ge0[r] ? (int)(ge - ge0[r]) : 0;
+        if (lane < tail) dst[r * g.slot_half + (ge0[r] - ga0[r]) + lane] = (uint8_t)ldg_u8((const void *)(ge0[r] + lane));
+    }
+    if (lane == 0) {
+        // the slot was read (and its tail bytes written) through the generic proxy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(&full[slot], tx);
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+            if (ge0[r] > ga0[r]) bulk_load(dst + r * g.slot_half, (const void *)ga0[r], (uint32_t)(ge0[r] - ga0[r]), &full[slot]);
+    }
+}
+
+// the first segments of a warp's jobs: issued before the input vectors are staged, so that the
+// weights are on their way while x is copied
+template <int WT, typename RowsOf>
+__device__ __forceinline__ void slab_prime(uint8_t *ring, uint64_t *full, const SlabGeom &g, int n_jobs, int lane, RowsOf rows_of) {
+    const int n_items = n_jobs * g.nseg;
+    for (int k = 0; k < min(g.nstage, n_items); k++) slab_issue<WT>(ring, full, g, k, lane, rows_of);
+}
+
+template <int WT, int NB, typename RowsOf, typename Finish>
+__device__ __forceinline__ void slab_pipeline(uint8_t *ring, uint64_t *full, const SlabGeom &g, const float *xs, int xs_ld,
+                                              int n_jobs, int lane, volatile int *abort_flag, RowsOf rows_of, Finish finish) {
+    const int n_items = n_jobs * g.nseg;
+    float acc[2][NB];
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
+    int k = 0;
+    for (; k < n_items; k++) {
+        const int jj = k / g.nseg, s = k - jj * g.nseg, slot = k % g.nstage;
+        if (!mbar_wait(&full[slot], (uint32_t)(k / g.nstage) & 1u, abort_flag)) break;
+        __syncwarp();
+        const unsigned char *row[2], *wend[2];
+        rows_of(jj, row, wend);
+        const int c0 = s * g.segw, nc = min(g.segw, g.cols - c0);
+        const size_t off = row_bytes(WT, c0);
+        const uint8_t *src = ring + (size_t)slot * 2 * g.slot_half;
+        const unsigned char *srow[2] = {src + (((uintptr_t)row[0] + off) & 15), src + g.slot_half + (((uintptr_t)row[1] + off) & 15)};
+        rows_dot<WT, NB, 2, true>(srow, nc, xs + xs_index<WT>(c0), xs_ld, lane, acc);
+        if (s == g.nseg - 1) {
+            finish(jj, acc);
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
+        }
+        __syncwarp();
+        if (k + g.nstage < n_items) slab_issue<WT>(ring, full, g, k + g.nstage, lane, rows_of);
+    }
+    if (k < n_items) {
+        // a copy did not arrive within the limit: nothing more is computed or issued, but the CTA may
+        // only exit once the copies already issued (items k .. k + nstage - 1) have landed
+        if (lane == 0) atomicExch(&g_matvec_status, 1);
+        for (int kk = k; kk < min(k + g.nstage, n_items); kk++)
+            if (!mbar_wait_drain(&full[kk % g.nstage], (uint32_t)(kk / g.nstage) & 1u)) break;
+    }
+}
+
+// shared memory of the staged kernels: x | barriers | rings
+__device__ __forceinline__ void slab_setup(float *xs_base, int xs_floats, const SlabGeom &g, uint64_t *&full, uint8_t *&ring,
+                                           volatile int *&abort_flag) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t *p = reinterpret_cast<uint8_t *>(xs_base) + (((size_t)xs_floats * 4 + 127) & ~(size_t)127);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(p);                   // kStWarps x 8 barriers, then the abort flag
+    abort_flag = reinterpret_cast<volatile int *>(bars + kStWarps * 8);
+    full = bars + warp * 8;
+    ring = p + 2048 + (size_t)warp * g.nstage * 2 * g.slot_half;
+    if (lane == 0) {
+        for (int i = 0; i < g.nstage; i++) mbar_init(&full[i], 1);
+        if (warp == 0) *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
 }
 
 // ------------------------------------------------------------------ y = W x (+ residual)
@@ -275,6 +464,46 @@ __global__ void __launch_bounds__(kMvWarps * 32) matvec_kernel(MatvecParams p) {
                     p.y[o] = acc[r][b] + (p.resid ? p.resid[o] : 0.f);
                 }
     }
+}
+
+// jobs = pairs of neighbouring rows (2j, 2j + 1); an odd last row is paired with itself, unstored
+template <int WT, int NB>
+__global__ void __launch_bounds__(kStWarps * 32, 1) matvec_staged_kernel(MatvecParams p, SlabGeom g) {
+    extern __shared__ __align__(128) float xs[];
+    const int b0 = blockIdx.y * NB;
+    const int nb = min(NB, p.batch - b0);
+    const int ld = xs_stride<WT>(p.cols);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t *full; uint8_t *ring; volatile int *abort_flag;
+    slab_setup(xs, NB * ld, g, full, ring, abort_flag);
+    const size_t rb = row_bytes(WT, p.cols);
+    const unsigned char *w_end = p.w + (size_t)p.rows * rb;
+    const int jobs = (p.rows + 1) >> 1;
+    const int gw = blockIdx.x * kStWarps + warp, n_warps = gridDim.x * kStWarps;
+    const int mine = gw < jobs ? (jobs - gw + n_warps - 1) / n_warps : 0;
+    auto rows_of = [&](int jj, const unsigned char *(&row)[2], const unsigned char *(&wend)[2]) {
+        const int r0 = 2 * (gw + jj * n_warps);
+        row[0] = p.w + (size_t)r0 * rb;
+        row[1] = p.w + (size_t)min(r0 + 1, p.rows - 1) * rb;
+        wend[0] = wend[1] = w_end;
+    };
+    auto finish = [&](int jj, float (&acc)[2][NB]) {
+        warp_sum2<2, NB>(acc);
+        const int r0 = 2 * (gw + jj * n_warps);
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+                if (lane == r * NB + b && b < nb && r0 + r < p.rows) {
+                    const size_t o = (size_t)(b0 + b) * p.y_ld + r0 + r;
+                    p.y[o] = acc[r][b] + (p.resid ? p.resid[o] : 0.f);
+                }
+    };
+    slab_prime<WT>(ring, full, g, mine, lane, rows_of);      // weights on their way while x is staged
+    stage_x<WT>(xs, p.x + (size_t)b0 * p.x_ld, p.cols, p.x_ld, nb);
+    for (int i = threadIdx.x + nb * ld; i < NB * ld; i += blockDim.x) xs[i] = 0.f;
+    __syncthreads();
+    slab_pipeline<WT, NB>(ring, full, g, xs, ld, mine, lane, abort_flag, rows_of, finish);
 }
 
 // ------------------------------------------------------------------ q | k | v = W x, RoPE, cache append
@@ -360,8 +589,75 @@ __global__ void __launch_bounds__(kMvWarps * 32) qkv_rope_append_kernel(QkvParam
     }
 }
 
+// the same epilogue as qkv_rope_append_kernel, on weights staged through shared memory
+template <int WT, int NB, typename CacheT>
+__global__ void __launch_bounds__(kStWarps * 32, 1) qkv_rope_append_staged_kernel(QkvParams p, SlabGeom g) {
+    extern __shared__ __align__(128) float xs[];
+    const int b0 = blockIdx.y * NB;
+    const int nb = min(NB, p.batch - b0);
+    const int ld = xs_stride<WT>(p.n_embd);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t *full; uint8_t *ring; volatile int *abort_flag;
+    slab_setup(xs, NB * ld, g, full, ring, abort_flag);
+    const int half = p.D / 2;
+    const int jobs = (p.Hq + 2 * p.Hkv) * half;
+    const size_t rb = row_bytes(WT, p.n_embd);
+    const int gw = blockIdx.x * kStWarps + warp, n_warps = gridDim.x * kStWarps;
+    const int mine = gw < jobs ? (jobs - gw + n_warps - 1) / n_warps : 0;
+    auto rows_of = [&](int jj, const unsigned char *(&row)[2], const unsigned char *(&wend)[2]) {
+        const int t = gw + jj * n_warps;
+        const int slot = t / half, f = t - slot * half;
+        const bool is_q = slot < p.Hq, is_k = !is_q && slot < p.Hq + p.Hkv;
+        const int head = is_q ? slot : (is_k ? slot - p.Hq : slot - p.Hq - p.Hkv);
+        const unsigned char *w = is_q ? p.wq : (is_k ? p.wk : p.wv);
+        row[0] = w + (size_t)(head * p.D + f) * rb;
+        row[1] = row[0] + (size_t)half * rb;
+        wend[0] = wend[1] = w + (size_t)(is_q ? p.Hq : p.Hkv) * p.D * rb;
+    };
+    auto finish = [&](int jj, float (&acc)[2][NB]) {
+        warp_sum2<2, NB>(acc);
+        const int t = gw + jj * n_warps;
+        const int slot = t / half, f = t - slot * half;
+        const bool is_q = slot < p.Hq, is_k = !is_q && slot < p.Hq + p.Hkv;
+        const int head = is_q ? slot : (is_k ? slot - p.Hq : slot - p.Hq - p.Hkv);
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+            if (lane == b && b < nb) {
+                const int bb = b0 + b, row0 = head * p.D + f;
+                const int pos = p.seq_pos ? p.seq_pos[bb] : p.pos0;
+                float x0 = acc[0][b], x1 = acc[1][b];
+                if ((is_q || is_k) && p.cos_tab) {
+                    // the expression of src/kernels.cu:412-413 with sign = +1
+                    const float c = p.cos_tab[(size_t)pos * half + f], s = p.sin_tab[(size_t)pos * half + f];
+                    const float ra = x0 * c - x1 * s, rd = x0 * s + x1 * c;
+                    x0 = ra; x1 = rd;
+                }
+                if (is_q) {
+                    float *o = p.q_out + (size_t)bb * p.Hq * p.D + row0;
+                    o[0] = x0; o[half] = x1;
+                } else {
+                    float *o = is_k ? p.k_out : p.v_out;
+                    if (o) { o[(size_t)bb * p.Hkv * p.D + row0] = x0; o[(size_t)bb * p.Hkv * p.D + row0 + half] = x1; }
+                    const int crow = pos - p.cache_row0;
+                    if (p.k_cache && crow >= 0 && crow < p.max_seq) {
+                        const int64_t base = (p.kv_off ? p.kv_off[bb] : (int64_t)bb * p.seq_stride) + (int64_t)head * p.head_stride +
+                                             (int64_t)crow * p.D + f;
+                        CacheT *dst = reinterpret_cast<CacheT *>(is_k ? p.k_cache : p.v_cache) + base;
+                        store_cache<CacheT>(dst, x0);
+                        store_cache<CacheT>(dst + half, x1);
+                    }
+                }
+            }
+    };
+    slab_prime<WT>(ring, full, g, mine, lane, rows_of);      // weights on their way while x is staged
+    stage_x<WT>(xs, p.x + (size_t)b0 * p.n_embd, p.n_embd, p.n_embd, nb);
+    for (int i = threadIdx.x + nb * ld; i < NB * ld; i += blockDim.x) xs[i] = 0.f;
+    __syncthreads();
+    slab_pipeline<WT, NB>(ring, full, g, xs, ld, mine, lane, abort_flag, rows_of, finish);
+}
+
 // ------------------------------------------------------------------ host side
-template <typename K, typename P> int launch_with_smem(K kernel, dim3 grid, size_t smem, cudaStream_t st, const char *what, const P &params) {
+template <int kWarps = kMvWarps, typename K, typename... P> int launch_with_smem(K kernel, dim3 grid, size_t smem, cudaStream_t st, const char *what, const P &...params) {
     if (smem > 48 * 1024) {
         // opt in once per kernel and device (the attribute is per function, per device)
         static thread_local const void *done[64][32];
@@ -378,7 +674,7 @@ template <typename K, typename P> int launch_with_smem(K kernel, dim3 grid, size
                     if (!done[dev][i]) { done[dev][i] = (const void *)kernel; break; }
         }
     }
-    kernel<<<grid, kMvWarps * 32, smem, st>>>(params);
+    kernel<<<grid, kWarps * 32, smem, st>>>(params...);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
     return NIMLLM_OK;
@@ -388,8 +684,33 @@ int batch_tile(int batch) { return batch >= 8 ? 8 : batch > 2 ? 4 : batch; }    
 
 template <int WT> size_t smem_for(int nb, int cols) { return (size_t)nb * xs_stride<WT>(cols) * sizeof(float); }
 
+// ring geometry of the staged kernels for nb input vectors of `cols` floats; false when shared memory
+// cannot hold the vectors plus two stages per warp
+template <int WT> bool slab_geom(int nb, int cols, SlabGeom &g, size_t &smem) {
+    g.cols = cols;
+    g.segw = cols < seg_weights(WT) ? cols : seg_weights(WT);
+    g.nseg = (cols + g.segw - 1) / g.segw;
+    g.slot_half = (int)((row_bytes(WT, g.segw) + 32 + 127) & ~(size_t)127);
+    const size_t xs_bytes = (smem_for<WT>(nb, cols) + 127) & ~(size_t)127;
+    const size_t per_stage = (size_t)kStWarps * 2 * g.slot_half;
+    if (xs_bytes + 2048 + 2 * per_stage > 227 * 1024) return false;
+    size_t n = (227 * 1024 - xs_bytes - 2048) / per_stage;
+    g.nstage = (int)(n > 8 ? 8 : n);
+    smem = xs_bytes + 2048 + g.nstage * per_stage;
+    return true;
+}
+
+// Which kernel runs (measured at 4096-wide layers, weights larger than L2): with one to four input vectors
+// the direct loads win (16 and more warps per SM hide the latency of the short dependent chains better than
+// the eight ring-owning warps do); with eight vectors the arithmetic per weight byte is large, the weights
+// are better read from shared memory at full rate and one CTA per SM stages x once instead of once per
+// 16 rows: 55.6 -> 39.5 us (Q8_0 q/k/v), 90.8 -> 58.2 us (fp32).  Q8_0 pairs with two and four vectors
+// run out of registers in the direct form (31.2 us vs 18.3 us staged).
+template <int WT> bool use_staged_matvec(int nb) { return nb >= 8; }
+template <int WT> bool use_staged_qkv(int nb) { return nb >= 8 || (WT == W_Q8_0 && nb >= 2); }
+
 template <int WT>
-int launch_matvec_t(const MatvecParams &p, cudaStream_t st) {
+int launch_matvec_direct(const MatvecParams &p, cudaStream_t st) {
     const int nb = batch_tile(p.batch);
     const size_t smem = smem_for<WT>(nb, p.cols);
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "matvec: %d input vectors of %d floats do not fit shared memory", nb, p.cols);
@@ -411,6 +732,26 @@ int launch_matvec_t(const MatvecParams &p, cudaStream_t st) {
     }
 }
 
+template <int WT>
+int launch_matvec_t(const MatvecParams &p, cudaStream_t st) {
+    const int nb = batch_tile(p.batch);
+    if (!use_staged_matvec<WT>(nb)) return launch_matvec_direct<WT>(p, st);
+    SlabGeom g;
+    size_t smem;
+    if (!slab_geom<WT>(nb, p.cols, g, smem))
+        return fail(NIMLLM_ERR_UNSUPPORTED, "matvec: %d input vectors of %d floats do not fit shared memory", nb, p.cols);
+    const int jobs = (p.rows + 1) / 2;
+    int gx = (jobs + kStWarps - 1) / kStWarps;
+    if (gx > sm_count()) gx = sm_count();                      // one CTA per SM, every warp a ring of its own
+    dim3 grid(gx, (p.batch + nb - 1) / nb);
+    switch (nb) {
+        case 1: return launch_with_smem<kStWarps>(matvec_staged_kernel<WT, 1>, grid, smem, st, "matvec", p, g);
+        case 2: return launch_with_smem<kStWarps>(matvec_staged_kernel<WT, 2>, grid, smem, st, "matvec", p, g);
+        case 4: return launch_with_smem<kStWarps>(matvec_staged_kernel<WT, 4>, grid, smem, st, "matvec", p, g);
+        default: return launch_with_smem<kStWarps>(matvec_staged_kernel<WT, 8>, grid, smem, st, "matvec", p, g);
+    }
+}
+
 int launch_matvec(int wt, const MatvecParams &p, cudaStream_t st) {
     switch (wt) {
         case W_F32: return launch_matvec_t<W_F32>(p, st);
@@ -421,7 +762,7 @@ int launch_matvec(int wt, const MatvecParams &p, cudaStream_t st) {
 }
 
 template <int WT, typename CacheT>
-int launch_qkv_t(const QkvParams &p, cudaStream_t st) {
+int launch_qkv_direct(const QkvParams &p, cudaStream_t st) {
     const int nb = batch_tile(p.batch);
     const size_t smem = smem_for<WT>(nb, p.n_embd);
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "qkv_rope_append: %d input vectors of %d floats do not fit shared memory", nb, p.n_embd);
@@ -436,6 +777,26 @@ int launch_qkv_t(const QkvParams &p, cudaStream_t st) {
         case 2: return launch_with_smem(qkv_rope_append_kernel<WT, 2, CacheT>, grid, smem, st, "qkv_rope_append", p);
         case 4: return launch_with_smem(qkv_rope_append_kernel<WT, 4, CacheT>, grid, smem, st, "qkv_rope_append", p);
         default: return launch_with_smem(qkv_rope_append_kernel<WT, 8, CacheT>, grid, smem, st, "qkv_rope_append", p);
+    }
+}
+
+template <int WT, typename CacheT>
+int launch_qkv_t(const QkvParams &p, cudaStream_t st) {
+    const int nb = batch_tile(p.batch);
+    if (!use_staged_qkv<WT>(nb)) return launch_qkv_direct<WT, CacheT>(p, st);
+    SlabGeom g;
+    size_t smem;
+    if (!slab_geom<WT>(nb, p.n_embd, g, smem))
+        return fail(NIMLLM_ERR_UNSUPPORTED, "qkv_rope_append: %d input vectors of %d floats do not fit shared memory", nb, p.n_embd);
+    const int jobs = (p.Hq + 2 * p.Hkv) * (p.D / 2);
+    int gx = (jobs + kStWarps - 1) / kStWarps;
+    if (gx > sm_count()) gx = sm_count();
+    dim3 grid(gx, (p.batch + nb - 1) / nb);
+    switch (nb) {
+        case 1: return launch_with_smem<kStWarps>(qkv_rope_append_staged_kernel<WT, 1, CacheT>, grid, smem, st, "qkv_rope_append", p, g);
+        case 2: return launch_with_smem<kStWarps>(qkv_rope_append_staged_kernel<WT, 2, CacheT>, grid, smem, st, "qkv_rope_append", p, g);
+        case 4: return launch_with_smem<kStWarps>(qkv_rope_append_staged_kernel<WT, 4, CacheT>, grid, smem, st, "qkv_rope_append", p, g);
+        default: return launch_with_smem<kStWarps>(qkv_rope_append_staged_kernel<WT, 8, CacheT>, grid, smem, st, "qkv_rope_append", p, g);
     }
 }
 
@@ -508,6 +869,17 @@ int nimllm_qkv_rope_append(const float *x_norm, const void *wq, const void *wk, 
     p.batch = batch; p.n_embd = n_embd; p.Hq = n_head; p.Hkv = n_kv_head; p.D = head_dim;
     if (k_cache && cache_dtype == NIMLLM_BF16) return launch_qkv<__nv_bfloat16>(w_type, p, (cudaStream_t)stream);
     return launch_qkv<float>(w_type, p, (cudaStream_t)stream);
+}
+
+int nimllm_matvec_status(int reset) {
+    int st = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&st, g_matvec_status, sizeof(int));
+    if (e == cudaSuccess && reset && st != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_matvec_status, &zero, sizeof(int));
+    }
+    if (e != cudaSuccess) return -fail(NIMLLM_ERR_CUDA, "matvec_status: %s", cudaGetErrorString(e));
+    return st;
 }
 
 /* src/kernels.cu:996-1003 and :1053-1059: y[rows] = A[rows, cols] x[cols], legacy default stream, void */

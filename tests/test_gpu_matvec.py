@@ -85,6 +85,23 @@ def test_matvec_batched_with_residual(kind, B):
     assert_close(host(y), ref, TOL_F32, f"{kind} matvec + residual, batch {B}")
 
 
+@pytest.mark.parametrize("rows,cols", SHAPES)
+@pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
+def test_staged_kernels_on_ragged_shapes(rows, cols, kind):
+    """Batches of eight and more go through the kernels that stage weights in shared memory: row
+    segments that start off a 16-byte boundary, matrices whose last bytes lie past the last 16-byte
+    boundary (7 x 32 Q4_0 = 126 bytes), odd block counts per row, an odd number of rows, a second
+    partial batch tile."""
+    blocks, wd, wdev = _weights(320 + rows, rows, cols, kind)
+    B = 11
+    x = normal(321, 1, (B, cols))
+    y = A.matvec(wdev, dev(x), rows, w_type=W_TYPE[kind])
+    torch.cuda.synchronize()
+    ref = (x.astype(np.float64) @ wd.astype(np.float64).T).astype(np.float32)
+    assert_close(host(y), ref, TOL_F32, f"{kind} staged matvec {rows}x{cols}")
+    assert A.matvec_status() == 0
+
+
 @pytest.mark.parametrize("kind", ["f32", "bf16", "q8_0", "q4_0"])
 @pytest.mark.parametrize("Hq,Hkv,D,n_embd", [(9, 3, 64, 576), (32, 8, 128, 4096), (4, 4, 64, 256)])
 @pytest.mark.parametrize("B,cache_dtype", [(1, torch.float32), (5, torch.bfloat16), (8, torch.float32), (10, torch.bfloat16)])
