@@ -380,8 +380,9 @@ int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float 
     const size_t need = nimllm_attn_prefill_bwd_workspace_bytes(batch, seq_len, n_head, head_dim);
     if (!workspace || workspace_bytes < need)
         return fail(NIMLLM_ERR_WORKSPACE, "attn_prefill_bwd: workspace %zu bytes, need %zu", workspace_bytes, need);
-    if (((uintptr_t)q_rot | (uintptr_t)k_rot | (uintptr_t)v | (uintptr_t)dout) & 15)
-        return fail(NIMLLM_ERR_ARG, "attn_prefill_bwd: q, k, v, dout must be 16-byte aligned");
+    if (((uintptr_t)q_rot | (uintptr_t)k_rot | (uintptr_t)v | (uintptr_t)out | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk |
+         (uintptr_t)dv | (uintptr_t)workspace) & 15)
+        return fail(NIMLLM_ERR_ARG, "attn_prefill_bwd: q, k, v, out, dout, dq, dk, dv and the workspace must be 16-byte aligned");
     BwdParams p;
     p.q = q_rot; p.k = k_rot; p.v = v; p.out = out; p.dout = dout; p.lse = lse;
     p.cos_tab = rope_cos; p.sin_tab = rope_sin; p.delta = (float *)workspace;
