@@ -592,6 +592,79 @@ def run_prefill(args, dist, with_e2e=True, with_cpu=True):
     return line
 
 
+def run_projections(args, dist):
+    """The decode step's projections either side of attention, one new token of one sequence (the
+    reference's chat path, src/model.nim:775-815,843-849) through every layer of a model shaped like
+    Llama-3-8B's attention (32 layers, 32 q / 8 kv heads, D = 128, n_embd 4096): per layer one fused
+    q/k/v projection + RoPE + cache append and one output projection + residual.  The layers' weights
+    (1.4 GB as Q8_0) are far larger than L2, so every launch streams its weights from HBM.  Every
+    rank runs the same model (replicas)."""
+    import torch
+    from nimllm_b200 import _lib, attention as A
+    layers, Hq, Hkv, D, E, cap = 32, 32, 8, 128, 4096, 64
+    kind = args.wtype
+    per_weight = {"f32": 4.0, "bf16": 2.0, "q8_0": 34 / 32, "q4_0": 18 / 32}[kind]
+    wt = {"f32": _lib.W_F32, "bf16": _lib.W_BF16, "q8_0": _lib.W_Q8_0, "q4_0": _lib.W_Q4_0}[kind]
+    gen = torch.Generator(device="cuda").manual_seed(SEEDS["c3"] + 77 + 1000 * dist.rank)
+
+    def weights(rows, cols):
+        if kind == "f32":
+            return torch.randn(rows, cols, generator=gen, device="cuda") * 0.02
+        if kind == "bf16":
+            return (torch.randn(rows, cols, generator=gen, device="cuda") * 0.02).bfloat16()
+        bs = 34 if kind == "q8_0" else 18
+        t = torch.randint(0, 256, (rows * cols // 32, bs), generator=gen, dtype=torch.uint8, device="cuda")
+        t[:, 1] = 0x20                 # high byte of the fp16 block scale: small, positive, finite
+        return t.reshape(-1)
+
+    W = [(weights(Hq * D, E), weights(Hkv * D, E), weights(Hkv * D, E), weights(E, Hq * D)) for _ in range(layers)]
+    x = torch.randn(1, E, generator=gen, device="cuda")
+    kc = torch.zeros(layers, 1, Hkv, cap, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    cos, sin = A.rope_tables(cap, D, 500000.0)
+    box = {}
+
+    def step():
+        h = x
+        for l, (wq, wk, wv, wo) in enumerate(W):
+            q = A.qkv_rope_append(h, wq, wk, wv, cos, sin, n_head=Hq, n_kv_head=Hkv, head_dim=D, w_type=wt, pos0=3,
+                                  k_cache=kc[l], v_cache=vc[l], seq_stride=Hkv * cap * D, head_stride=cap * D, max_seq=cap)
+            h = A.wo_residual(q, wo, h, w_type=wt)      # (q stands in for the attention output: same shape)
+        box["h"] = h
+
+    # replayed as one CUDA graph, the way a whole-token step is replayed
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    sampler = ClockSampler(dist.local)
+    with sampler:
+        ms = timed_steps(torch, graph.replay, args.steps, args.warmup, None, dist)
+    t_max = dist.max(sum(ms) / 1e3)
+    weights_per_layer = (Hq + 2 * Hkv) * D * E + E * Hq * D
+    bytes_step = layers * weights_per_layer * per_weight
+    pk = peaks()
+    achieved = bytes_step / (sum(ms) / len(ms) / 1e3) / 1e9
+    return {
+        "metric": "decode_projection_weight_gbps", "value": round(bytes_step * dist.world * args.steps / t_max / 1e9, 1),
+        "unit": "GB/s", "n_gpus": dist.world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(t_max / args.steps * 1e3, 4), "us_per_layer": round(t_max / args.steps / layers * 1e6, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind, "data": "synthetic",
+        "config": {"workload": f"decode projections, 1 token of 1 sequence: {layers} layers x (q/k/v projection + RoPE + append, "
+                               f"output projection + residual), {Hq}q/{Hkv}kv heads, D={D}, n_embd {E}, {kind} weights",
+                   "parallelism": f"{dist.world} replica(s)", "l2": f"{bytes_step / 1e6:.0f} MB of weights per step, larger than L2; no flush kernel",
+                   "launch": "one CUDA graph of 64 kernel nodes per step"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"],
+                     "algorithmic_bytes_per_step": bytes_step,
+                     "kernel": "qkv_rope_append_kernel + matvec_kernel per layer; weight bytes / CUDA-event time of the whole step"},
+        "gpu_launches": 2 * layers * args.steps,
+        "clocks": sampler.summary(),
+    }
+
+
 def cpu_baseline_prefill(q, k, v, Hq, Hkv, D, scale):
     """The CPU restatement of forward()'s per-head attention loop (oracle_attn_forward: fp32,
     S x S scores per head, OpenMP over heads) on a sample of the workload's (batch, head) pairs."""
@@ -714,7 +787,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "c3", "c3p", "c5", "c4"])
+    ap.add_argument("--workload", default="all", choices=["all", "c3", "c3p", "c5", "c4", "proj"])
+    ap.add_argument("--wtype", default="q8_0", choices=["f32", "bf16", "q8_0", "q4_0"], help="--workload proj: weight format")
     ap.add_argument("--sustain", type=float, default=2.0, help="seconds of the back-to-back sustained loop per workload (0: skip)")
     ap.add_argument("--chunk-rows", type=int, default=0)
     ap.add_argument("--eager", action="store_true", help="decode workloads: launch the step's kernels eagerly instead of replaying a graph")
@@ -756,6 +830,8 @@ def main():
         line = run_decode(args, dist, args.workload)
     elif args.workload == "c4":
         line = run_prefill(args, dist)
+    elif args.workload == "proj":
+        line = run_projections(args, dist)
     else:
         # headline: c3 exactly as `--workload c3` prints it; the other configurations of the same
         # run ride along under "also" (end-to-end legs only on one GPU; the CPU baseline only for
@@ -764,7 +840,8 @@ def main():
         also = {}
         for key, fn in (("c4", lambda: run_prefill(args, dist, with_e2e=solo, with_cpu=False) if 8 % dist.world == 0 else None),
                         ("c5", lambda: run_decode(args, dist, "c5", with_e2e=solo, with_cpu=False)),
-                        ("c3_partitioned", lambda: run_decode(args, dist, "c3p", with_e2e=False, with_cpu=False))):
+                        ("c3_partitioned", lambda: run_decode(args, dist, "c3p", with_e2e=False, with_cpu=False)),
+                        ("projections", lambda: run_projections(args, dist) if solo else None)):
             torch.cuda.empty_cache()
             try:
                 rec = fn()

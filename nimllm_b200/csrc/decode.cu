@@ -510,8 +510,12 @@ __global__ void __launch_bounds__(NW * 32, MINB) decode_mma_balanced_kernel(Deco
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n_uniform = (p.max_len + U - 1) / U;
-    // the merge kernel that follows is a programmatic dependent: its CTAs may take their places
-    // now and wait there for this grid to finish, instead of being launched after it
+    // Launched as a programmatic dependent of whatever precedes it in the stream: when that kernel
+    // lets its dependents go early (this library's merge kernels do), the CTAs of this grid are
+    // already in place when it ends.  Nothing is read or written before this wait.
+    grid_dependency_wait();
+    // the merge kernel that follows is a programmatic dependent in turn: its CTAs may take their
+    // places now and wait there for this grid to finish, instead of being launched after it
     launch_dependents();
 
     if (p.seq_len) {
@@ -819,6 +823,7 @@ __device__ __forceinline__ void combine_row_warp(const BalCombineParams &c, int 
     if (lane == 0) sink.stats(M, wsum);
 }
 __global__ void __launch_bounds__(128) combine_balanced_warp_kernel(BalCombineParams c) {
+    launch_dependents();                 // the next kernel of the stream may place its CTAs (it waits for this grid)
     grid_dependency_wait();              // the decode kernel's records and prefix array are complete
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const unsigned int epoch = c.do_push ? peer_push_epoch(c.push) : 0u;
@@ -891,6 +896,7 @@ __device__ __forceinline__ void combine_row_cta(const BalCombineParams &c, int r
 __global__ void __launch_bounds__(128) combine_balanced_kernel(BalCombineParams c) {
     __shared__ float s_acc[4][256];
     __shared__ float s_w[4];
+    launch_dependents();                 // the next kernel of the stream may place its CTAs (it waits for this grid)
     grid_dependency_wait();              // the decode kernel's records and prefix array are complete
     const unsigned int epoch = c.do_push ? peer_push_epoch(c.push) : 0u;
     combine_row_cta(c, blockIdx.x, epoch, s_acc, s_w);
@@ -1058,14 +1064,21 @@ int launch_balanced(DecodeParams &p, const int32_t *seq_len, void *out, int out_
     int *cum = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(workspace) +
                                        bal_record_bytes(n_head, n_kv_head, head_dim));
     const bool paged = p.page_table != nullptr;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(bs.grid); cfg.blockDim = dim3(bs.nw * 32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e;
     if (head_dim == 64) {
-        if (paged) decode_mma_balanced_kernel<64, 1, 2, 8, true><<<bs.grid, 256, 0, st>>>(p, cum);
-        else decode_mma_balanced_kernel<64, 1, 2, 8, false><<<bs.grid, 256, 0, st>>>(p, cum);
+        if (paged) e = cudaLaunchKernelEx(&cfg, decode_mma_balanced_kernel<64, 1, 2, 8, true>, p, cum);
+        else e = cudaLaunchKernelEx(&cfg, decode_mma_balanced_kernel<64, 1, 2, 8, false>, p, cum);
     } else {
-        if (paged) decode_mma_balanced_kernel<128, 2, 1, 4, true><<<bs.grid, 128, 0, st>>>(p, cum);
-        else decode_mma_balanced_kernel<128, 2, 1, 4, false><<<bs.grid, 128, 0, st>>>(p, cum);
+        if (paged) e = cudaLaunchKernelEx(&cfg, decode_mma_balanced_kernel<128, 2, 1, 4, true>, p, cum);
+        else e = cudaLaunchKernelEx(&cfg, decode_mma_balanced_kernel<128, 2, 1, 4, false>, p, cum);
     }
-    NIMLLM_CHECK_LAUNCH("attn_decode balanced");
+    if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_decode balanced: %s", cudaGetErrorString(e));
     BalCombineParams c;
     c.recs = p.ws; c.cum = cum; c.seq_len = seq_len; c.out = out; c.partials_out = partials_out;
     c.out_dtype = out_dtype; c.B = batch; c.Hq = n_head; c.Hkv = n_kv_head; c.G = p.G; c.D = head_dim;
@@ -1075,13 +1088,7 @@ int launch_balanced(DecodeParams &p, const int32_t *seq_len, void *out, int out_
     // The merge launch is a programmatic dependent of the decode kernel (its CTAs are placed while
     // the decode still runs and wait for it on the device).  Few pieces per pair (a large batch):
     // one warp per row; many pieces: a CTA per row.
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = 0; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaError_t e;
+    cfg.blockDim = dim3(128);
     if ((int64_t)c.wk < 4ll * batch * n_kv_head) {
         cfg.gridDim = dim3((batch * n_head + 3) / 4);
         e = cudaLaunchKernelEx(&cfg, combine_balanced_warp_kernel, c);
