@@ -46,7 +46,8 @@ SHAPE_OVERRIDE = None   # set by --shape (profiling only); the defaults are the 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu
 # capture of that kernel on this workload (a constant: re-capture after changing the kernel)
 NCU_TRAFFIC_BYTES = {"c3": 462600000 + 900000, "c3p": 462600000 + 900000, "c5": 4295500000 + 1900000,
-                     "c4": 1903500000 + 231800000}
+                     "c4": 1903500000 + 231800000,
+                     "proj_q8_0": 32 * (26796252 + 17897384)}
 WORKLOAD_TEXT = {
     "c3": "C3 batched GQA decode: 256 ragged sequences per GPU, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
     "c3p": "C3 batched GQA decode: one batch of 256 ragged sequences partitioned over the GPUs, L~U[512,4096], 9q/3kv heads, D=64, bf16 KV",
@@ -657,8 +658,8 @@ def run_projections(args, dist):
                    "parallelism": f"{dist.world} replica(s)", "l2": f"{bytes_step / 1e6:.0f} MB of weights per step, larger than L2; no flush kernel",
                    "launch": "one CUDA graph of 64 kernel nodes per step"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm"], 4), "traffic": None, "peak_source": pk["source"],
-                     "algorithmic_bytes_per_step": bytes_step,
+                     "frac": round(achieved / pk["hbm"], 4), "traffic": NCU_TRAFFIC_BYTES.get("proj_" + kind),
+                     "peak_source": pk["source"], "algorithmic_bytes_per_step": bytes_step,
                      "kernel": "qkv_rope_append_kernel + matvec_kernel per layer; weight bytes / CUDA-event time of the whole step"},
         "gpu_launches": 2 * layers * args.steps,
         "clocks": sampler.summary(),

@@ -18,9 +18,11 @@
 // up to kMaxBatch input vectors with it, so a weight byte is fetched once per launch tile.
 // Lanes stride over the row in units of 16 bytes (fp32 / bf16) or of block pairs read as
 // aligned 32-bit words (Q4_0: 9 words, Q8_0: 17 words per 64 weights; single blocks through
-// 16-bit loads when a row holds an odd number of blocks).  The input vectors sit in shared
-// memory, padded by one float per 64 for the block formats so that lanes reading different
-// block pairs hit different banks.  A warp takes several rows per pass (their loads are in flight
+// 16-bit loads when a row holds an odd number of blocks).  Block rows of a multiple of 16 bytes
+// (cols a multiple of 256) are fetched 16 bytes per lane and passed through a per-warp buffer in
+// shared memory instead (rows_dot_wide).  The input vectors sit in shared memory, padded by two
+// floats per 64 for the block formats so that lanes reading different block pairs hit different
+// banks; a block's even and odd weights are accumulated as packed fp32 pairs (fma.rn.f32x2).  A warp takes several rows per pass (their loads are in flight
 // together, and every input value read from shared memory serves all of them).
 //
 // Two forms of every kernel: the weights loaded straight into registers (few input vectors), or
@@ -46,10 +48,10 @@ __host__ __device__ inline size_t row_bytes(int wt, int cols) {
     return wt == W_F32 ? (size_t)cols * 4 : wt == W_BF16 ? (size_t)cols * 2 : wt == W_Q8_0 ? (size_t)(cols / 32) * 34
                                                                                              : (size_t)(cols / 32) * 18;
 }
-// index of x[j] in shared memory: one pad float per 64 for the block formats, so that lanes working
-// on consecutive block pairs (65 floats apart) read different banks
-template <int WT> __device__ __forceinline__ int xs_index(int j) { return (WT >= W_Q8_0) ? j + (j >> 6) : j; }
-template <int WT> __host__ __device__ inline int xs_stride(int cols) { return (WT >= W_Q8_0) ? cols + cols / 64 + 4 : cols; }
+// index of x[j] in shared memory: two pad floats per 64 for the block formats, so that lanes working
+// on consecutive block pairs (66 floats apart) read different banks with their 8-byte loads
+template <int WT> __device__ __forceinline__ int xs_index(int j) { return (WT >= W_Q8_0) ? j + 2 * (j >> 6) : j; }
+template <int WT> __host__ __device__ inline int xs_stride(int cols) { return (WT >= W_Q8_0) ? cols + 2 * (cols / 64) + 4 : cols; }
 
 // 4- and 2-byte loads of block data: neighbouring lanes and the loads of one lane share 32-byte
 // sectors, so these allocate in L1 (every sector then comes out of L2 once per SM, not once per load)
@@ -141,6 +143,68 @@ template <int R, int NB> __device__ __forceinline__ void add_block(const float (
         for (int b = 0; b < NB; b++) { acc[r][b] = fmaf(d[r], part[r][b], acc[r][b]); part[r][b] = 0.f; }
 }
 
+// Packed fp32 arithmetic (two IEEE fp32 operations per instruction, each rounded like the scalar form).
+__device__ __forceinline__ uint64_t pack2(float a, float b) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ float sum2(uint64_t v) { float lo, hi; asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); return lo + hi; }
+// the quantised values of one 32-bit word as pairs of consecutive weights (same byte trick as dequant_word)
+template <int WT> __device__ __forceinline__ void dequant_word2(uint32_t q, uint64_t *out) {
+    if (WT == W_Q4_0) {
+        const uint32_t lo = q & 0x0F0F0F0Fu, hi = (q >> 4) & 0x0F0F0F0Fu;
+        const uint64_t k2 = pack2(-8388616.f, -8388616.f);               // nibble - 8
+#pragma unroll
+        for (int i = 0; i < 4; i++) out[i] = add2(pack2(byte_as_float(lo, i), byte_as_float(hi, i)), k2);
+    } else {
+        const uint32_t u = q ^ 0x80808080u;                              // int8 + 128 as unsigned bytes
+        const uint64_t k2 = pack2(-8388736.f, -8388736.f);
+#pragma unroll
+        for (int i = 0; i < 2; i++) out[i] = add2(pack2(byte_as_float(u, 2 * i), byte_as_float(u, 2 * i + 1)), k2);
+    }
+}
+// One block pair (64 weights) of R rows, read as aligned 32-bit words {d0 | q0[0..1]} q0.. {q0 tail | d1} q1..;
+// `base` = index of the pair's first input value in the padded shared-memory layout (even: the input
+// values are read two at a time).  Even and odd weights of a block are summed separately (packed fp32).
+template <int WT, int NB, int R, bool SM>
+__device__ __forceinline__ void pair_dot(const unsigned char *const (&pp)[R], const float *xs, int xs_ld, int base, float (&acc)[R][NB]) {
+    constexpr int QW = WT == W_Q4_0 ? 4 : 8;             // 32-bit words of quantised values per block
+    constexpr int N = 32 / QW;                           // weights per word
+    uint32_t w[R][2 * QW + 1];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int i = 0; i < 2 * QW + 1; i++) w[r][i] = ld_u32<SM>(pp[r] + 4 * i);
+#pragma unroll
+    for (int blk = 0; blk < 2; blk++) {
+        uint64_t part[R][NB];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int b = 0; b < NB; b++) part[r][b] = 0ull;              // (+0, +0)
+#pragma unroll
+        for (int i = 0; i < QW; i++) {
+            uint64_t wp[R][N / 2];
+#pragma unroll
+            for (int r = 0; r < R; r++)
+                dequant_word2<WT>(blk == 0 ? (w[r][i] >> 16) | (w[r][i + 1] << 16) : w[r][QW + 1 + i], wp[r]);
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+#pragma unroll
+                for (int h = 0; h < N / 2; h++) {
+                    const uint64_t xp = *reinterpret_cast<const uint64_t *>(xs + b * xs_ld + base + blk * 32 + i * N + 2 * h);
+#pragma unroll
+                    for (int r = 0; r < R; r++) part[r][b] = fma2(wp[r][h], xp, part[r][b]);
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const float d = half_bits_to_float(blk == 0 ? w[r][0] : w[r][QW] >> 16);
+#pragma unroll
+            for (int b = 0; b < NB; b++) acc[r][b] = fmaf(d, sum2(part[r][b]), acc[r][b]);
+        }
+    }
+}
+
 // Partial dot products of R weight rows with NB input vectors: this lane's share (lanes stride over
 // the row, the loads of all R rows are in flight together); the caller adds the lanes up.
 template <int WT, int NB, int R, bool SM = false>
@@ -183,39 +247,11 @@ __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], i
 #pragma unroll
         for (int r = 0; r < R; r++) aligned = aligned && ((uintptr_t)row[r] & 3) == 0;
         if (aligned) {
-            // block pairs as aligned words: {d0 | q0[0..1]} q0.. {q0 tail | d1} q1..
             for (int pr = lane; pr < (bpr >> 1); pr += 32) {
-                uint32_t w[R][2 * QW + 1];
+                const unsigned char *pp[R];
 #pragma unroll
-                for (int r = 0; r < R; r++)
-#pragma unroll
-                    for (int i = 0; i < 2 * QW + 1; i++) w[r][i] = ld_u32<SM>(row[r] + (size_t)pr * (2 * BS) + 4 * i);
-                const int base = pr * 65;                     // 64 weights + 1 pad float per pair
-                float part[R][NB], d[R];
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    d[r] = half_bits_to_float(w[r][0]);
-#pragma unroll
-                    for (int b = 0; b < NB; b++) part[r][b] = 0.f;
-                }
-#pragma unroll
-                for (int i = 0; i < QW; i++) {
-                    float wv[R][N];
-#pragma unroll
-                    for (int r = 0; r < R; r++) dequant_word<WT>((w[r][i] >> 16) | (w[r][i + 1] << 16), wv[r]);
-                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + i * N, part);
-                }
-                add_block<R, NB>(d, part, acc);
-#pragma unroll
-                for (int r = 0; r < R; r++) d[r] = half_bits_to_float(w[r][QW] >> 16);
-#pragma unroll
-                for (int i = 0; i < QW; i++) {
-                    float wv[R][N];
-#pragma unroll
-                    for (int r = 0; r < R; r++) dequant_word<WT>(w[r][QW + 1 + i], wv[r]);
-                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, base + 32 + i * N, part);
-                }
-                add_block<R, NB>(d, part, acc);
+                for (int r = 0; r < R; r++) pp[r] = row[r] + (size_t)pr * (2 * BS);
+                pair_dot<WT, NB, R, SM>(pp, xs, xs_ld, pr * 66, acc);      // 64 weights + 2 pad floats per pair
             }
         } else {
             // rows with an odd number of blocks: single blocks through 16-bit loads
@@ -235,10 +271,64 @@ __device__ __forceinline__ void rows_dot(const unsigned char *const (&row)[R], i
                         const unsigned char *p = row[r] + (size_t)bk * BS;
                         dequant_word<WT>(ld_u16<SM>(p + 2 + 4 * i) | (ld_u16<SM>(p + 4 + 4 * i) << 16), wv[r]);
                     }
-                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, bk * 32 + (bk >> 1) + i * N, part);
+                    fma_chunk<R, NB, N, false>(wv, xs, xs_ld, bk * 32 + 2 * (bk >> 1) + i * N, part);
                 }
                 add_block<R, NB>(d, part, acc);
             }
+        }
+    }
+}
+
+// Block-format rows whose length in bytes is a multiple of 16 (cols a multiple of 256): the warp fetches
+// a segment of 32 block pairs of each row with 16-byte loads, lanes on consecutive 16-byte pieces (every
+// 32-byte sector is asked for once, not once per 32-bit word of a pair), passes it through a buffer of
+// its own in shared memory and reads its pair from there (lanes 68 or 36 bytes apart: odd word strides,
+// no bank conflicts).  The next segment's loads are in flight while the current one is worked on, and
+// the first segment can be fetched before the input vectors are staged.
+template <int WT> struct Wide {
+    static constexpr int BS = WT == W_Q4_0 ? 18 : 34;
+    static constexpr int kSegBytes = 32 * 2 * BS;                    // 2176 or 1152
+    static constexpr int kPieces = (kSegBytes / 16 + 31) / 32;       // 16-byte pieces per lane: 5 or 3
+    static constexpr int kBufBytes = kSegBytes + 16;                 // per row and warp
+};
+template <int WT, int R>
+__device__ __forceinline__ void wide_fetch(uint4 (&pre)[R][Wide<WT>::kPieces], const unsigned char *const (&row)[R], int seg, int npairs,
+                                           int lane) {
+    const int pairs = min(32, npairs - seg * 32);
+    const int pieces = (pairs * 2 * Wide<WT>::BS + 15) >> 4;         // the row ends on a 16-byte boundary: never past it
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int k = 0; k < Wide<WT>::kPieces; k++) {
+            const int c = lane + 32 * k;
+            if (c < pieces) pre[r][k] = ldg_stream(row[r] + (size_t)seg * Wide<WT>::kSegBytes + 16 * c);
+        }
+}
+template <int WT, int NB, int R>
+__device__ __forceinline__ void rows_dot_wide(const unsigned char *const (&row)[R], int cols, const float *xs, int xs_ld, int lane,
+                                              float (&acc)[R][NB], unsigned char *wbuf, uint4 (&pre)[R][Wide<WT>::kPieces], bool fetched) {
+    using Wd = Wide<WT>;
+    const int npairs = cols >> 6;
+    const int nseg = (npairs + 31) >> 5;
+    if (!fetched) wide_fetch<WT, R>(pre, row, 0, npairs, lane);
+    for (int seg = 0; seg < nseg; seg++) {
+        const int pairs = min(32, npairs - seg * 32);
+        const int pieces = (pairs * 2 * Wd::BS + 15) >> 4;
+        __syncwarp();                                               // the buffer's previous contents have been used
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int k = 0; k < Wd::kPieces; k++) {
+                const int c = lane + 32 * k;
+                if (c < pieces) *reinterpret_cast<uint4 *>(wbuf + r * Wd::kBufBytes + 16 * c) = pre[r][k];
+            }
+        __syncwarp();
+        if (seg + 1 < nseg) wide_fetch<WT, R>(pre, row, seg + 1, npairs, lane);
+        if (lane < pairs) {
+            const unsigned char *pp[R];
+#pragma unroll
+            for (int r = 0; r < R; r++) pp[r] = wbuf + r * Wd::kBufBytes + lane * (2 * Wd::BS);
+            pair_dot<WT, NB, R, true>(pp, xs, xs_ld, (seg * 32 + lane) * 66, acc);
         }
     }
 }
@@ -433,21 +523,36 @@ struct MatvecParams {
     int rows, cols, x_ld, y_ld, batch;
 };
 
-// Three resident CTAs per SM are asked for, not the eight that fit: with only "256 threads" as the bound
-// the compiler holds the kernel to 32 - 40 registers to keep full occupancy and then cannot keep a
-// pass's loads in flight together (fp32 q/k/v at 4096-wide layers: 23.5 -> 18.6 us with this bound).
+// Three resident CTAs per SM are asked for (two with four and more input vectors), not the eight that fit:
+// with only "256 threads" as the bound the compiler holds the kernel to 32 - 40 registers to keep full
+// occupancy and then cannot keep a pass's loads in flight together (fp32 q/k/v at 4096-wide layers:
+// 23.5 -> 18.6 us with this bound).  Two CTAs per SM were measured for the block formats too: the
+// q/k/v grid of a 4096-wide layer (384 CTAs) then no longer fits one wave and the call gets slower.
 template <int WT, int NB, int R>                             // R rows per warp pass
-__global__ void __launch_bounds__(kMvWarps * 32, 3) matvec_kernel(MatvecParams p) {
+__global__ void __launch_bounds__(kMvWarps * 32, (NB >= 4 ? 2 : 3)) matvec_kernel(MatvecParams p) {
     extern __shared__ __align__(16) float xs[];
     const int b0 = blockIdx.y * NB;
     const int nb = min(NB, p.batch - b0);
     const int ld = xs_stride<WT>(p.cols);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t rb = row_bytes(WT, p.cols);
+    constexpr bool kBlocks = WT >= W_Q8_0;
+    constexpr int WTB = kBlocks ? WT : W_Q8_0;               // (the wide path is only instantiated for block formats)
+    const bool wide = kBlocks && R == 2 && (rb & 15) == 0;
+    unsigned char *wbuf = reinterpret_cast<unsigned char *>(xs) + (((size_t)NB * ld * 4 + 15) & ~(size_t)15) +
+                          (size_t)warp * R * Wide<WTB>::kBufBytes;
+    uint4 pre[R][Wide<WTB>::kPieces];
+    const int first_row = (blockIdx.x * kMvWarps + warp) * R;
+    if (kBlocks && wide && first_row < p.rows) {             // the first weights are on their way while x is staged
+        const unsigned char *rows[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) rows[r] = p.w + (size_t)min(first_row + r, p.rows - 1) * rb;
+        wide_fetch<WTB, R>(pre, rows, 0, p.cols >> 6, lane);
+    }
     stage_x<WT>(xs, p.x + (size_t)b0 * p.x_ld, p.cols, p.x_ld, nb);
     for (int i = threadIdx.x + nb * ld; i < NB * ld; i += blockDim.x) xs[i] = 0.f;     // unused vectors read as zeros
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const size_t rb = row_bytes(WT, p.cols);
-    for (int row0 = (blockIdx.x * kMvWarps + warp) * R; row0 < p.rows; row0 += gridDim.x * kMvWarps * R) {
+    for (int row0 = first_row; row0 < p.rows; row0 += gridDim.x * kMvWarps * R) {
         float acc[R][NB];
         const unsigned char *rows[R];
 #pragma unroll
@@ -456,7 +561,8 @@ __global__ void __launch_bounds__(kMvWarps * 32, 3) matvec_kernel(MatvecParams p
 #pragma unroll
             for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
         }
-        rows_dot<WT, NB, R>(rows, p.cols, xs, ld, lane, acc);
+        if (kBlocks && wide) rows_dot_wide<WTB, NB, R>(rows, p.cols, xs, ld, lane, acc, wbuf, pre, row0 == first_row);
+        else rows_dot<WT, NB, R>(rows, p.cols, xs, ld, lane, acc);
         warp_sum2<R, NB>(acc);
 #pragma unroll
         for (int r = 0; r < R; r++)
@@ -530,34 +636,53 @@ template <> __device__ __forceinline__ void store_cache<__nv_bfloat16>(__nv_bflo
 // One warp task = RP neighbouring rotation pairs (f, f + D/2) of one head of q, k or v: 2 RP weight
 // rows whose loads are in flight together (the block formats have short rows: two pairs per task).
 template <int WT, int NB, typename CacheT>
-__global__ void __launch_bounds__(kMvWarps * 32, 3) qkv_rope_append_kernel(QkvParams p) {
+__global__ void __launch_bounds__(kMvWarps * 32, (NB >= 4 ? 2 : 3)) qkv_rope_append_kernel(QkvParams p) {
     constexpr int RP = 1;                                 // (two pairs per task were measured: no gain for the block formats)
     extern __shared__ __align__(16) float xs[];
     const int b0 = blockIdx.y * NB;
     const int nb = min(NB, p.batch - b0);
     const int ld = xs_stride<WT>(p.n_embd);
-    stage_x<WT>(xs, p.x + (size_t)b0 * p.n_embd, p.n_embd, p.n_embd, nb);
-    for (int i = threadIdx.x + nb * ld; i < NB * ld; i += blockDim.x) xs[i] = 0.f;
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = p.D / 2;
     const int fpt = half / RP;                            // tasks per head
     const int tasks = (p.Hq + 2 * p.Hkv) * fpt;
     const size_t rb = row_bytes(WT, p.n_embd);
-    for (int t = blockIdx.x * kMvWarps + warp; t < tasks; t += gridDim.x * kMvWarps) {
+    constexpr bool kBlocks = WT >= W_Q8_0;
+    constexpr int WTB = kBlocks ? WT : W_Q8_0;            // (the wide path is only instantiated for block formats)
+    const bool wide = kBlocks && (rb & 15) == 0;
+    unsigned char *wbuf = reinterpret_cast<unsigned char *>(xs) + (((size_t)NB * ld * 4 + 15) & ~(size_t)15) +
+                          (size_t)warp * 2 * RP * Wide<WTB>::kBufBytes;
+    uint4 pre[2 * RP][Wide<WTB>::kPieces];
+    auto rows_of = [&](int t, const unsigned char *(&rows)[2 * RP]) {
         const int slot = t / fpt, f0 = (t - slot * fpt) * RP;
         const bool is_q = slot < p.Hq, is_k = !is_q && slot < p.Hq + p.Hkv;
         const int head = is_q ? slot : (is_k ? slot - p.Hq : slot - p.Hq - p.Hkv);
         const unsigned char *w = is_q ? p.wq : (is_k ? p.wk : p.wv);
+#pragma unroll
+        for (int r = 0; r < 2 * RP; r++) rows[r] = w + (size_t)(head * p.D + f0 + (r >> 1) + (r & 1) * half) * rb;      // pair r/2: rows f, f + D/2
+    };
+    const int first_task = blockIdx.x * kMvWarps + warp;
+    if (kBlocks && wide && first_task < tasks) {          // the first weights are on their way while x is staged
+        const unsigned char *rows[2 * RP];
+        rows_of(first_task, rows);
+        wide_fetch<WTB, 2 * RP>(pre, rows, 0, p.n_embd >> 6, lane);
+    }
+    stage_x<WT>(xs, p.x + (size_t)b0 * p.n_embd, p.n_embd, p.n_embd, nb);
+    for (int i = threadIdx.x + nb * ld; i < NB * ld; i += blockDim.x) xs[i] = 0.f;
+    __syncthreads();
+    for (int t = first_task; t < tasks; t += gridDim.x * kMvWarps) {
+        const int slot = t / fpt, f0 = (t - slot * fpt) * RP;
+        const bool is_q = slot < p.Hq, is_k = !is_q && slot < p.Hq + p.Hkv;
+        const int head = is_q ? slot : (is_k ? slot - p.Hq : slot - p.Hq - p.Hkv);
         float acc[2 * RP][NB];
         const unsigned char *rows[2 * RP];
+        rows_of(t, rows);
 #pragma unroll
-        for (int r = 0; r < 2 * RP; r++) {
-            rows[r] = w + (size_t)(head * p.D + f0 + (r >> 1) + (r & 1) * half) * rb;      // pair r/2: rows f, f + D/2
+        for (int r = 0; r < 2 * RP; r++)
 #pragma unroll
             for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
-        }
-        rows_dot<WT, NB, 2 * RP>(rows, p.n_embd, xs, ld, lane, acc);
+        if (kBlocks && wide) rows_dot_wide<WTB, NB, 2 * RP>(rows, p.n_embd, xs, ld, lane, acc, wbuf, pre, t == first_task);
+        else rows_dot<WT, NB, 2 * RP>(rows, p.n_embd, xs, ld, lane, acc);
         warp_sum2<2 * RP, NB>(acc);
 #pragma unroll
         for (int pr = 0; pr < RP; pr++)
@@ -686,6 +811,12 @@ template <int kWarps = kMvWarps, typename K, typename... P> int launch_with_smem
 int batch_tile(int batch) { return batch >= 8 ? 8 : batch > 2 ? 4 : batch; }      // 1, 2, 4 or 8 vectors per weight fetch
 
 template <int WT> size_t smem_for(int nb, int cols) { return (size_t)nb * xs_stride<WT>(cols) * sizeof(float); }
+// the direct kernels' shared memory: x, and for the block formats two row buffers per warp
+template <int WT> size_t smem_direct(int nb, int cols) {
+    size_t b = (smem_for<WT>(nb, cols) + 15) & ~(size_t)15;
+    if (WT >= W_Q8_0) b += (size_t)kMvWarps * 2 * Wide<(WT >= W_Q8_0 ? WT : W_Q8_0)>::kBufBytes;
+    return b;
+}
 
 // ring geometry of the staged kernels for nb input vectors of `cols` floats; false when shared memory
 // cannot hold the vectors plus two stages per warp
@@ -715,10 +846,11 @@ template <int WT> bool use_staged_qkv(int nb) { return nb >= 8 || (WT == W_Q8_0 
 template <int WT>
 int launch_matvec_direct(const MatvecParams &p, cudaStream_t st) {
     const int nb = batch_tile(p.batch);
-    const size_t smem = smem_for<WT>(nb, p.cols);
+    const size_t smem = smem_direct<WT>(nb, p.cols);
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "matvec: %d input vectors of %d floats do not fit shared memory", nb, p.cols);
-    // four rows per warp pass when that still leaves two CTAs of work per SM, else two
-    const bool r4 = nb < 8 && p.rows >= (WT >= W_Q8_0 ? 1 : 2) * sm_count() * kMvWarps * 2;
+    // fp32 / bf16: four rows per warp pass when that still leaves two CTAs of work per SM, else two;
+    // the block formats always take two (their rows pass through two buffers per warp)
+    const bool r4 = WT < W_Q8_0 && nb < 8 && p.rows >= 2 * sm_count() * kMvWarps * 2;
     const int rows_per_cta = kMvWarps * (r4 ? 4 : 2);
     int gx = (p.rows + rows_per_cta - 1) / rows_per_cta;
     const int cap = sm_count() * 8;
@@ -767,7 +899,7 @@ int launch_matvec(int wt, const MatvecParams &p, cudaStream_t st) {
 template <int WT, typename CacheT>
 int launch_qkv_direct(const QkvParams &p, cudaStream_t st) {
     const int nb = batch_tile(p.batch);
-    const size_t smem = smem_for<WT>(nb, p.n_embd);
+    const size_t smem = smem_direct<WT>(nb, p.n_embd);
     if (smem > 227 * 1024) return fail(NIMLLM_ERR_UNSUPPORTED, "qkv_rope_append: %d input vectors of %d floats do not fit shared memory", nb, p.n_embd);
     const int rp = 1;
     const int tasks = (p.Hq + 2 * p.Hkv) * (p.D / 2 / rp);
