@@ -110,6 +110,9 @@ int nimllm_rope_append(void *q, int n_head, void *k_new, const void *v_new, int 
  *            KV-sequence shard hands to nimllm_attn_combine
  *   chunk_rows  KV rows per split; 0 = choose
  *   workspace   nimllm_attn_decode_workspace_bytes(...) bytes, 256-byte aligned
+ *   Cache rows are read 16 bytes at a time: k_cache / v_cache, seq_stride, head_stride and every
+ *   kv_off[b] must be multiples of 16 bytes (8 bf16 or 4 fp32 elements); the host-visible ones are
+ *   checked (NIMLLM_ERR_ARG), the device array kv_off cannot be.
  */
 size_t nimllm_attn_decode_workspace_bytes(int batch, int n_head, int n_kv_head, int head_dim,
                                           int max_len, int chunk_rows);

@@ -1182,6 +1182,11 @@ int nimllm_attn_decode(const void *q, int q_dtype, const void *k_cache, const vo
     if (batch > 65535) return fail(NIMLLM_ERR_UNSUPPORTED, "attn_decode: batch %d > 65535", batch);
     if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
         return fail(NIMLLM_ERR_ARG, "attn_decode: cache pointers must be 16-byte aligned");
+    {   // rows are read 16 bytes at a time: every (sequence, KV head) block must start on such a boundary
+        const int64_t per16 = cache_dtype == NIMLLM_BF16 ? 8 : 4;
+        if (head_stride % per16 != 0 || (!kv_off && seq_stride % per16 != 0))
+            return fail(NIMLLM_ERR_ARG, "attn_decode: seq_stride and head_stride must be multiples of 16 bytes");
+    }
     const bool mma_ok = cache_dtype == NIMLLM_BF16 && n_head / n_kv_head <= 8;
     // The balanced kernel is the default for a bf16 cache when the caller leaves the chunking to
     // the library and the workspace holds its records; an explicit chunk_rows keeps the chunk grid.
@@ -1312,6 +1317,8 @@ int nimllm_attn_decode_push(nimllm_peer_exchange *x, const void *q, int q_dtype,
         return fail(NIMLLM_ERR_WORKSPACE, "attn_decode_push: workspace %zu bytes, need %zu", workspace_bytes, need);
     if ((((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) || ((uintptr_t)workspace & 255))
         return fail(NIMLLM_ERR_ARG, "attn_decode_push: caches 16-byte, workspace 256-byte aligned");
+    if (head_stride % 8 != 0 || (!kv_off && seq_stride % 8 != 0))
+        return fail(NIMLLM_ERR_ARG, "attn_decode_push: seq_stride and head_stride must be multiples of 16 bytes");
     const size_t bal = bal_workspace_bytes(batch, n_head, n_kv_head, head_dim, max_len, true);
     float *rows_done = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + (bal + 255) / 256 * 256);
     DecodeParams p;

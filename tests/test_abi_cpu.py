@@ -52,6 +52,10 @@ def test_validation_errors_have_status_and_message():
     rc = L.nimllm_attn_decode(one, 0, one, one, 0, None, 0, 0, None, 4096, one, 0, None, 1, 4, 2, 64, 0.125, 128,
                               None, 0, None)
     assert rc == 3 and b"workspace" in L.nimllm_attn_last_error()
+    # a bf16 cache whose KV heads start 6 elements apart: 16-byte loads would be misaligned
+    rc = L.nimllm_attn_decode(one, 0, one, one, 1, None, 4096, 6, None, 16, one, 0, None, 1, 4, 2, 64, 0.125, 0, None,
+                              0, None)
+    assert rc == 1 and b"multiples of 16 bytes" in L.nimllm_attn_last_error()
     rc = L.nimllm_attn_prefill(None, None, None, 0, None, None, 0, None, 1, 8, 4, 2, 64, 0.125, 1, None, None, 0,
                                None, 0, 0, 0, None, None, 0, None)
     assert rc == 1
