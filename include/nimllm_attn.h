@@ -9,6 +9,11 @@
  * `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream
  * the reference launches everything on (src/gpu.nim:166-175).
  *
+ * Stream order: every entry point behaves as a plain stream-ordered launch.  Internally the decode and
+ * projection kernels are launched with programmatic stream serialization and wait on the device for the
+ * kernel before them before they read an input or write an output, so that back-to-back calls of this
+ * library overlap their launch latencies; nothing is required of the caller.
+ *
  * Tensor layouts are the reference's: activations are row-major [tokens, heads*D]
  * with heads as column blocks of width D (src/model.nim:487-497); a KV head of
  * the cache is a dense row-major [rows, D] block with K stored AFTER RoPE and V
