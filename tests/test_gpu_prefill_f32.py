@@ -127,3 +127,22 @@ def test_batched_prefill_with_position_offset():
     for b in range(B):
         ref, _, _ = O.attn_forward(q[b], k[b], v[b], ocos[pos0:], osin[pos0:], Hq, Hkv, D)
         assert_close(out[b], ref, TOL_F32, f"batch {b}")
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D", [(6, 200, 16, 4, 64), (5, 130, 24, 8, 128), (8, 100, 20, 5, 32), (3, 449, 9, 3, 64)])
+def test_register_tiled_kernel_on_launches_that_fill_the_gpu(B, S, Hq, Hkv, D):
+    """Launches of at least one 64-row query tile per two SMs run the register-tiled fp32 kernel: ragged last
+    tiles, a diagonal inside every tile, all three head sizes, batch > 1; output and log-sum-exp."""
+    q = normal(400 + S, 0, (B, S, Hq * D)); k = normal(400 + S, 1, (B, S, Hkv * D)); v = normal(400 + S, 2, (B, S, Hkv * D))
+    cos, sin = A.rope_tables(S, D, 10000.0)
+    lse = torch.zeros(B, Hq, S, device="cuda")
+    out = host(A.attn_forward(dev(q), dev(k), dev(v), cos, sin, n_head=Hq, n_kv_head=Hkv, head_dim=D, lse=lse))
+    ocos, osin = O.rope_tables(S, D, 10000.0)
+    lse_h = host(lse)
+    for b in range(B):
+        ref, q_rot, k_rot = O.attn_forward(q[b], k[b], v[b], ocos, osin, Hq, Hkv, D)
+        assert_close(out[b], ref, TOL_F32, f"tiled prefill fp32, batch {b}")
+        for h, i in ((0, 0), (Hq - 1, S - 1), (Hq // 2, 63), (1, 64)):
+            kvh = h // (Hq // Hkv)
+            sc = (q_rot[i, h * D:(h + 1) * D].astype(np.float64) @ k_rot[:i + 1, kvh * D:(kvh + 1) * D].astype(np.float64).T) / np.sqrt(D)
+            assert abs(lse_h[b, h, i] - np.log(np.exp(sc - sc.max()).sum()) - sc.max()) < 1e-4
