@@ -95,6 +95,31 @@ int attnForwardCached(const ModelShape &m, KvCache &kv, int li, GpuBuf q, GpuBuf
                               m.headDim, scale, 0, ws, wsBytes, nullptr);
 }
 
+int attnStepCached(const ModelShape &m, KvCache &kv, int li, const AttnWeights &w, GpuBuf xNorm, GpuBuf xResid,
+                   GpuBuf xOut, GpuBuf ropeCos, GpuBuf ropeSin, Arena &arena) {
+    if (kv.pos + 1 > m.blockSize) return NIMLLM_ERR_ARG;             // src/chat.nim:96,103 guard
+    const float scale = 1.0f / std::sqrt((float)m.headDim);          // src/model.nim:762
+    const int64_t seqStride = (int64_t)m.nKvHead * m.blockSize * m.headDim;
+    const int64_t headStride = (int64_t)m.blockSize * m.headDim;
+    GpuBuf q = arena.trackedCreate((size_t)m.nEmbd()), attn = arena.trackedCreate((size_t)m.nEmbd());
+    // src/model.nim:775-815: three mat-vecs, two ropeFwd, 2 * nKvHead copies -> one launch
+    int rc = nimllm_qkv_rope_append((const float *)xNorm.data, w.wq, w.wk, w.wv, w.wType, (float *)q.data, nullptr, nullptr,
+                                    (const float *)ropeCos.data, (const float *)ropeSin.data, nullptr, kv.pos, kv.k[li].data,
+                                    kv.v[li].data, NIMLLM_F32, nullptr, seqStride, headStride, 0, m.blockSize, 1, m.nEmbd(),
+                                    m.nHead, m.nKvHead, m.headDim, nullptr);
+    if (rc) return rc;
+    const int S = kv.pos + 1;                                        // src/model.nim:754
+    size_t wsBytes = nimllm_attn_decode_workspace_bytes(1, m.nHead, m.nKvHead, m.headDim, S, 0);
+    void *ws = wsBytes ? arena.bytes(wsBytes) : nullptr;
+    rc = nimllm_attn_decode(q.data, NIMLLM_F32, kv.k[li].data, kv.v[li].data, NIMLLM_F32, nullptr, seqStride, headStride,
+                            nullptr, S, attn.data, NIMLLM_F32, nullptr, 1, m.nHead, m.nKvHead, m.headDim, scale, 0, ws,
+                            wsBytes, nullptr);
+    if (rc) return rc;
+    // src/model.nim:843-849: wo mat-vec + gpu_add -> one launch
+    return nimllm_wo_residual((const float *)attn.data, w.wo, w.wType, (const float *)xResid.data, (float *)xOut.data, 1,
+                              m.nEmbd(), m.nEmbd(), nullptr);
+}
+
 int prefillStatus(bool reset) { return nimllm_attn_prefill_status(reset ? 1 : 0); }
 
 std::string lastError() { return nimllm_attn_last_error(); }
@@ -165,6 +190,19 @@ int nimllm_host_attn_forward_cached(void *h, int li, void *q, void *kNew, void *
         return attnForwardCached(m, s->kv, li, GpuBuf{q, (size_t)m.nEmbd()}, GpuBuf{kNew, (size_t)m.nKvDim()},
                                  GpuBuf{vNew, (size_t)m.nKvDim()}, s->ropeCos, s->ropeSin,
                                  GpuBuf{attnOut, (size_t)m.nEmbd()}, *s->arena);
+    } catch (...) {
+        return NIMLLM_ERR_WORKSPACE;
+    }
+}
+
+int nimllm_host_attn_step_cached(void *h, int li, const void *wq, const void *wk, const void *wv, const void *wo, int wType,
+                                 void *xNorm, void *xResid, void *xOut) {
+    HostSession *s = (HostSession *)h;
+    const ModelShape &m = s->shape;
+    try {
+        return attnStepCached(m, s->kv, li, AttnWeights{wq, wk, wv, wo, wType}, GpuBuf{xNorm, (size_t)m.nEmbd()},
+                              GpuBuf{xResid, (size_t)m.nEmbd()}, GpuBuf{xOut, (size_t)m.nEmbd()}, s->ropeCos, s->ropeSin,
+                              *s->arena);
     } catch (...) {
         return NIMLLM_ERR_WORKSPACE;
     }

@@ -72,6 +72,20 @@ int attnForward(const ModelShape &m, GpuBuf q, GpuBuf k, GpuBuf v, GpuBuf ropeCo
 int attnForwardCached(const ModelShape &m, KvCache &kv, int li, GpuBuf q, GpuBuf kNew, GpuBuf vNew,
                       GpuBuf ropeCos, GpuBuf ropeSin, GpuBuf attnOut, Arena &arena);
 
+// The attention weights of one layer as the reference holds them (src/model.nim:36-47): row-major
+// [out, in] matrices, fp32 or -- the GGUF path, src/model.nim:445-450 -- Q8_0 / Q4_0 blocks.
+struct AttnWeights {
+    const void *wq, *wk, *wv, *wo;
+    int wType;               // NIMLLM_W_F32, _BF16, _Q8_0, _Q4_0
+};
+
+// forwardCached()'s whole attention part for ONE new token of layer li (src/model.nim:775-849) in three
+// launches + one merge: q/k/v projection of xNorm with RoPE and the cache append fused in, attention over
+// rows 0..kv.pos, output projection with the residual added: xOut = xResid + wo * attn.  Scratch for q and
+// the attention output comes from the arena.  The caller advances kv.pos after the last layer.
+int attnStepCached(const ModelShape &m, KvCache &kv, int li, const AttnWeights &w, GpuBuf xNorm, GpuBuf xResid,
+                   GpuBuf xOut, GpuBuf ropeCos, GpuBuf ropeSin, Arena &arena);
+
 // Sticky status of the bf16 tensor-core prefill on the current device (0 ok, 1 a launch gave up on a
 // bounded wait and left incomplete results); synchronises the device.  Call it where the host waits
 // for results anyway -- after a forward pass, before sampling (src/chat.nim:97-101).
