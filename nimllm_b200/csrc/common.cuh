@@ -104,9 +104,11 @@ __device__ __forceinline__ float *peer_push_slot(const PeerPush &px, int r, unsi
 // called by every thread of every CTA after its stores: the last CTA to get here advances the
 // counter and raises this rank's flag on every peer (plain stores + system-scope release)
 __device__ __forceinline__ void peer_push_publish(const PeerPush &px, unsigned int epoch) {
-    __threadfence_system();
+    // the CTA's stores happen-before thread 0 through the barrier; its system-scope fence then orders all of
+    // them (fences are cumulative) before the counter and, in the last CTA, before the flags
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         unsigned int *ctl = peer_ctl(px, px.rank) + kPeerMaxWorld;
         if (atomicAdd(&ctl[0], 1u) == gridDim.x - 1) {
             ctl[0] = 0u;
