@@ -866,17 +866,15 @@ def main():
         # headline: c3 exactly as `--workload c3` prints it; the other configurations of the same
         # run ride along under "also" (end-to-end legs only on one GPU; the CPU baseline only for
         # the headline)
-        line = run_decode(args, dist, "c3")
         also = {}
         # the prefill sub-record times at most 20 steps (40 ms: the burst regime its roofline is quoted against);
-        # what two seconds of back-to-back steps run at under the power cap is in its "sustained" object
+        # what two seconds of back-to-back steps run at under the power cap is in its "sustained" object.  It
+        # runs first, on a GPU that the other workloads' two-second loops have not heated yet.
         import copy
         c4_args = copy.copy(args)
         c4_args.steps = min(args.steps, 20)
-        for key, fn in (("c4", lambda: run_prefill(c4_args, dist, with_e2e=solo, with_cpu=False) if 8 % dist.world == 0 else None),
-                        ("c5", lambda: run_decode(args, dist, "c5", with_e2e=solo, with_cpu=False)),
-                        ("c3_partitioned", lambda: run_decode(args, dist, "c3p", with_e2e=False, with_cpu=False)),
-                        ("projections", lambda: run_projections(args, dist) if solo else None)):
+
+        def sub(key, fn):
             torch.cuda.empty_cache()
             try:
                 rec = fn()
@@ -885,6 +883,13 @@ def main():
                 log(f"also.{key} failed: {rec['error']}")
             if rec is not None:
                 also[key] = rec
+
+        sub("c4", lambda: run_prefill(c4_args, dist, with_e2e=solo, with_cpu=False) if 8 % dist.world == 0 else None)
+        torch.cuda.empty_cache()
+        line = run_decode(args, dist, "c3")
+        sub("c5", lambda: run_decode(args, dist, "c5", with_e2e=solo, with_cpu=False))
+        sub("c3_partitioned", lambda: run_decode(args, dist, "c3p", with_e2e=False, with_cpu=False))
+        sub("projections", lambda: run_projections(args, dist) if solo else None)
         line["also"] = also
     if dist.rank == 0:
         print(json.dumps(line), file=real_stdout, flush=True)
