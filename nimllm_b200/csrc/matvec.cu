@@ -527,9 +527,10 @@ struct MatvecParams {
 // with only "256 threads" as the bound the compiler holds the kernel to 32 - 40 registers to keep full
 // occupancy and then cannot keep a pass's loads in flight together (fp32 q/k/v at 4096-wide layers:
 // 23.5 -> 18.6 us with this bound).  Two CTAs per SM were measured for the block formats too: the
-// q/k/v grid of a 4096-wide layer (384 CTAs) then no longer fits one wave and the call gets slower.
+// q/k/v grid of a 4096-wide layer (384 CTAs) then no longer fits one wave and the call gets slower.  bf16 with
+// four input vectors keeps three as well (76 registers suffice; 23.6 against 33.1 us with two).
 template <int WT, int NB, int R>                             // R rows per warp pass
-__global__ void __launch_bounds__(kMvWarps * 32, (NB >= 4 ? 2 : 3)) matvec_kernel(MatvecParams p) {
+__global__ void __launch_bounds__(kMvWarps * 32, ((NB >= 4 && WT != W_BF16) ? 2 : 3)) matvec_kernel(MatvecParams p) {
     extern __shared__ __align__(16) float xs[];
     const int b0 = blockIdx.y * NB;
     const int nb = min(NB, p.batch - b0);
@@ -649,7 +650,7 @@ template <> __device__ __forceinline__ void store_cache<__nv_bfloat16>(__nv_bflo
 // One warp task = RP neighbouring rotation pairs (f, f + D/2) of one head of q, k or v: 2 RP weight
 // rows whose loads are in flight together (the block formats have short rows: two pairs per task).
 template <int WT, int NB, typename CacheT>
-__global__ void __launch_bounds__(kMvWarps * 32, (NB >= 4 ? 2 : 3)) qkv_rope_append_kernel(QkvParams p) {
+__global__ void __launch_bounds__(kMvWarps * 32, ((NB >= 4 && WT != W_BF16) ? 2 : 3)) qkv_rope_append_kernel(QkvParams p) {
     constexpr int RP = 1;                                 // (two pairs per task were measured: no gain for the block formats)
     extern __shared__ __align__(16) float xs[];
     const int b0 = blockIdx.y * NB;
