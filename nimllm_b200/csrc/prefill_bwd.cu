@@ -16,7 +16,9 @@
 // so the sums over heads and rows happen in a fixed order in registers, no atomics, results are
 // deterministic; dq with one CTA per (32 query rows, query head) walking the KV tiles.
 // fp32 FMA on the CUDA cores: this is the <= 1e-4 parity path of the training configuration
-// (S = 128..2048, D = 64), not a tensor-core kernel.
+// (S = 128..2048, D = 64), not a tensor-core kernel.  The dk/dv and dq kernels exist twice: on
+// 32 x 32 tiles (every head size, small launches) and on 64 x 64 register-blocked tiles (head size 64,
+// launches that fill the GPU).
 #include "common.cuh"
 
 namespace nimllm {
@@ -320,6 +322,245 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(BwdParams p) {
     }
 }
 
+// ---------------------------------------------------------------------- register-tiled forms (head_dim 64)
+// The same arithmetic on 64 x 64 tiles for launches that fill the GPU: thread (rg, cg) of a 16 x 8 thread
+// grid owns a 4 x 8 block of the score tile (rows rg + 16 i, columns cg + 8 j) and 4 rows x 8 columns
+// (cg * 4 + 32 u + e) of the accumulated gradient, so a 16-byte shared-memory read feeds about ten
+// multiply-adds instead of three and a half.  The rotation partner f + 32 of column f is held by the same
+// thread.  Tiles are [64][68] floats: the strides rg * 68 and cg * 68 put the 16-byte reads of a
+// quarter-warp on different banks.
+constexpr int kTT = 64;            // tile edge of the tiled kernels
+constexpr int kTL = 64 + 4;        // row pitch of their [64][64] tiles
+
+__device__ __forceinline__ void load_tile64(float *dst, const float *src, int64_t seq_base, int row0, int S, int width, int col0) {
+    for (int i = threadIdx.x; i < kTT * 16; i += 128) {
+        const int r = i >> 4, c = (i & 15) * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < S) x = *reinterpret_cast<const float4 *>(src + (seq_base + row0 + r) * width + col0 + c);
+        *reinterpret_cast<float4 *>(dst + r * kTL + c) = x;
+    }
+}
+// acc[i][j] += A[rg + 16 i] . B[cg + 8 j] over the 64 columns of two [64][68] tiles
+__device__ __forceinline__ void tile_dots(const float *A, const float *B, int rg, int cg, float (&acc)[4][8]) {
+#pragma unroll 2
+    for (int d = 0; d < 64; d += 4) {
+        float4 af[4], bf[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) af[i] = *reinterpret_cast<const float4 *>(A + (rg + 16 * i) * kTL + d);
+#pragma unroll
+        for (int j = 0; j < 8; j++) bf[j] = *reinterpret_cast<const float4 *>(B + (cg + 8 * j) * kTL + d);
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                acc[i][j] = fmaf(af[i].x, bf[j].x, fmaf(af[i].y, bf[j].y, fmaf(af[i].z, bf[j].z, fmaf(af[i].w, bf[j].w, acc[i][j]))));
+    }
+}
+// g[i][4u + e] += sum_j W[rg + 16 i][j] * X[j][cg * 4 + 32 u + e]: the weights of a row are written and read by
+// the same eight lanes
+__device__ __forceinline__ void tile_accumulate(const float *W, const float *X, int rg, int cg, float (&g)[4][8]) {
+#pragma unroll 2
+    for (int j = 0; j < 64; j += 4) {
+        float4 wf[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) wf[i] = *reinterpret_cast<const float4 *>(W + (rg + 16 * i) * kTL + j);
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+            const float4 x0 = *reinterpret_cast<const float4 *>(X + (j + jj) * kTL + cg * 4);
+            const float4 x1 = *reinterpret_cast<const float4 *>(X + (j + jj) * kTL + cg * 4 + 32);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float w = jj == 0 ? wf[i].x : jj == 1 ? wf[i].y : jj == 2 ? wf[i].z : wf[i].w;
+                g[i][0] = fmaf(w, x0.x, g[i][0]); g[i][1] = fmaf(w, x0.y, g[i][1]); g[i][2] = fmaf(w, x0.z, g[i][2]); g[i][3] = fmaf(w, x0.w, g[i][3]);
+                g[i][4] = fmaf(w, x1.x, g[i][4]); g[i][5] = fmaf(w, x1.y, g[i][5]); g[i][6] = fmaf(w, x1.z, g[i][6]); g[i][7] = fmaf(w, x1.w, g[i][7]);
+            }
+        }
+    }
+}
+// scale, undo the rotation (columns f = cg * 4 + e and f + 32 are g[e] and g[4 + e]; k_rope with sign = -1,
+// src/kernels.cu:399-413) and store one row of a gradient
+__device__ __forceinline__ void finish_row64(float (&g)[8], float scale, const float *cos_tab, const float *sin_tab, int pos, int cg, float *dst) {
+#pragma unroll
+    for (int c = 0; c < 8; c++) g[c] *= scale;
+    if (cos_tab) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int f = cg * 4 + e;
+            const float c = cos_tab[(int64_t)pos * 32 + f], s = -sin_tab[(int64_t)pos * 32 + f];
+            const float x0 = g[e], x1 = g[4 + e];
+            g[e] = x0 * c - x1 * s;
+            g[4 + e] = x0 * s + x1 * c;
+        }
+    }
+    *reinterpret_cast<float4 *>(dst + cg * 4) = make_float4(g[0], g[1], g[2], g[3]);
+    *reinterpret_cast<float4 *>(dst + cg * 4 + 32) = make_float4(g[4], g[5], g[6], g[7]);
+}
+
+// dq of 64 query rows of one query head: walk the KV tiles up to the diagonal
+__global__ void __launch_bounds__(128) bwd_dq_tiled_kernel(BwdParams p) {
+    constexpr int D = 64;
+    extern __shared__ __align__(16) float smem[];
+    float *Qs = smem, *dOs = Qs + kTT * kTL, *Ks = dOs + kTT * kTL, *Vs = Ks + kTT * kTL, *dSs = Vs + kTT * kTL;
+    float *lse_s = dSs + kTT * kTL, *delta_s = lse_s + kTT;
+    const int it = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;     // longest walks first
+    const int G = p.Hq / p.Hkv, E = p.Hq * D, Ekv = p.Hkv * D, kvh = h / G;
+    const int q0 = it * kTT;
+    const int64_t seq_base = (int64_t)b * p.S;
+    const int rg = threadIdx.x >> 3, cg = threadIdx.x & 7;
+    load_tile64(Qs, p.q, seq_base, q0, p.S, E, h * D);
+    load_tile64(dOs, p.dout, seq_base, q0, p.S, E, h * D);
+    if (threadIdx.x < kTT) {
+        const int qi = q0 + threadIdx.x;
+        lse_s[threadIdx.x] = qi < p.S ? p.lse[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+        delta_s[threadIdx.x] = qi < p.S ? p.delta[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+    }
+    float dq[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < 8; c++) dq[i][c] = 0.f;
+    for (int jt = 0; jt <= it; jt++) {
+        const int k0 = jt * kTT;
+        __syncthreads();                                         // the previous tile's K and V have been used
+        load_tile64(Ks, p.k, seq_base, k0, p.S, Ekv, kvh * D);
+        load_tile64(Vs, p.v, seq_base, k0, p.S, Ekv, kvh * D);
+        __syncthreads();
+        float s[4][8], dp[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) { s[i][j] = 0.f; dp[i][j] = 0.f; }
+        tile_dots(Qs, Ks, rg, cg, s);
+        tile_dots(dOs, Vs, rg, cg, dp);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = rg + 16 * i, qi = q0 + r;
+            const float l = lse_s[r], dl = delta_s[r];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int kj = k0 + cg + 8 * j;
+                const bool live = qi < p.S && kj <= qi;
+                const float pv = live ? expf(s[i][j] * p.scale - l) : 0.f;
+                dSs[r * kTL + cg + 8 * j] = pv * (dp[i][j] - dl);
+            }
+        }
+        __syncwarp();
+        tile_accumulate(dSs, Ks, rg, cg, dq);
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int qi = q0 + rg + 16 * i;
+        if (qi < p.S) finish_row64(dq[i], p.scale, p.cos_tab, p.sin_tab, p.pos0 + qi, cg, p.dq + (seq_base + qi) * E + (int64_t)h * D);
+    }
+}
+
+// dk, dv of 64 KV rows: walk the query heads of the group (or the one query head, when partial sums per head are
+// kept) and their query tiles from the diagonal down.  The score tile is formed transposed ([kv][q]) so that a
+// thread's rows are KV rows.
+__global__ void __launch_bounds__(128) bwd_dkdv_tiled_kernel(BwdParams p) {
+    constexpr int D = 64;
+    extern __shared__ __align__(16) float smem[];
+    float *Ks = smem, *Vs = Ks + kTT * kTL, *Qs = Vs + kTT * kTL, *dOs = Qs + kTT * kTL, *Pt = dOs + kTT * kTL, *dSt = Pt + kTT * kTL;
+    float *lse_s = dSt + kTT * kTL, *delta_s = lse_s + kTT;
+    const int jt = blockIdx.x, b = blockIdx.z;
+    const int G = p.Hq / p.Hkv, E = p.Hq * D, Ekv = p.Hkv * D;
+    const bool split = p.dk_part != nullptr;
+    const int kvh = split ? (int)blockIdx.y / G : (int)blockIdx.y;
+    const int h_first = split ? (int)blockIdx.y : kvh * G, n_heads = split ? 1 : G;
+    const int k0 = jt * kTT;
+    const int64_t seq_base = (int64_t)b * p.S;
+    const int n_tiles = (p.S + kTT - 1) / kTT;
+    const int rg = threadIdx.x >> 3, cg = threadIdx.x & 7;
+    load_tile64(Ks, p.k, seq_base, k0, p.S, Ekv, kvh * D);
+    load_tile64(Vs, p.v, seq_base, k0, p.S, Ekv, kvh * D);
+    float dk[4][8], dv[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < 8; c++) { dk[i][c] = 0.f; dv[i][c] = 0.f; }
+    const int per_h = n_tiles - jt, total = n_heads * per_h;
+    for (int n = 0; n < total; n++) {
+        const int h = h_first + n / per_h, q0 = (jt + n % per_h) * kTT;
+        __syncthreads();                                         // the previous pair's tiles have been used
+        load_tile64(Qs, p.q, seq_base, q0, p.S, E, h * D);
+        load_tile64(dOs, p.dout, seq_base, q0, p.S, E, h * D);
+        if (threadIdx.x < kTT) {
+            const int qi = q0 + threadIdx.x;
+            lse_s[threadIdx.x] = qi < p.S ? p.lse[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+            delta_s[threadIdx.x] = qi < p.S ? p.delta[((int64_t)b * p.Hq + h) * p.S + qi] : 0.f;
+        }
+        __syncthreads();
+        float s[4][8], dp[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) { s[i][j] = 0.f; dp[i][j] = 0.f; }
+        tile_dots(Ks, Qs, rg, cg, s);                            // s[i][j] = k[kv row i] . q[query j]
+        tile_dots(Vs, dOs, rg, cg, dp);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = rg + 16 * i, kj = k0 + r;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int c = cg + 8 * j, qi = q0 + c;
+                const bool live = qi < p.S && kj <= qi;
+                const float pv = live ? expf(s[i][j] * p.scale - lse_s[c]) : 0.f;
+                Pt[r * kTL + c] = pv;
+                dSt[r * kTL + c] = pv * (dp[i][j] - delta_s[c]);
+            }
+        }
+        __syncwarp();
+        tile_accumulate(Pt, dOs, rg, cg, dv);
+        tile_accumulate(dSt, Qs, rg, cg, dk);
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int kj = k0 + rg + 16 * i;
+        if (kj >= p.S) continue;
+        if (split) {                                             // raw partial sums of this query head
+            const int64_t off = (((int64_t)(h_first % G) * p.B * p.S) + seq_base + kj) * Ekv + (int64_t)kvh * D;
+            *reinterpret_cast<float4 *>(p.dk_part + off + cg * 4) = make_float4(dk[i][0], dk[i][1], dk[i][2], dk[i][3]);
+            *reinterpret_cast<float4 *>(p.dk_part + off + cg * 4 + 32) = make_float4(dk[i][4], dk[i][5], dk[i][6], dk[i][7]);
+            *reinterpret_cast<float4 *>(p.dv_part + off + cg * 4) = make_float4(dv[i][0], dv[i][1], dv[i][2], dv[i][3]);
+            *reinterpret_cast<float4 *>(p.dv_part + off + cg * 4 + 32) = make_float4(dv[i][4], dv[i][5], dv[i][6], dv[i][7]);
+        } else {
+            const int64_t off = (seq_base + kj) * Ekv + (int64_t)kvh * D;
+            finish_row64(dk[i], p.scale, p.cos_tab, p.sin_tab, p.pos0 + kj, cg, p.dk + off);
+            *reinterpret_cast<float4 *>(p.dv + off + cg * 4) = make_float4(dv[i][0], dv[i][1], dv[i][2], dv[i][3]);
+            *reinterpret_cast<float4 *>(p.dv + off + cg * 4 + 32) = make_float4(dv[i][4], dv[i][5], dv[i][6], dv[i][7]);
+        }
+    }
+}
+
+int launch_bwd_tiled64(const BwdParams &p, cudaStream_t st) {
+    const size_t smem_dq = (size_t)(5 * kTT * kTL + 2 * kTT) * sizeof(float), smem_kv = (size_t)(6 * kTT * kTL + 2 * kTT) * sizeof(float);
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_dq_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
+        if (e != cudaSuccess) return fail(NIMLLM_ERR_CUDA, "attn_prefill_bwd: shared memory opt-in: %s", cudaGetErrorString(e));
+        attr_set[dev] = true;
+    }
+    const int n_tiles = (p.S + kTT - 1) / kTT;
+    const int rows = p.B * p.S * p.Hq;
+    bwd_delta_kernel<<<(rows + 3) / 4, 128, 0, st>>>(p, 64);
+    NIMLLM_CHECK_LAUNCH("attn_prefill_bwd delta");
+    bwd_dkdv_tiled_kernel<<<dim3(n_tiles, p.dk_part ? p.Hq : p.Hkv, p.B), 128, smem_kv, st>>>(p);
+    NIMLLM_CHECK_LAUNCH("attn_prefill_bwd dk dv");
+    if (p.dk_part) {
+        const int64_t n = (int64_t)p.B * p.S * p.Hkv * 32;
+        bwd_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p, 64);
+        NIMLLM_CHECK_LAUNCH("attn_prefill_bwd reduce");
+    }
+    bwd_dq_tiled_kernel<<<dim3(n_tiles, p.Hq, p.B), 128, smem_dq, st>>>(p);
+    NIMLLM_CHECK_LAUNCH("attn_prefill_bwd dq");
+    return NIMLLM_OK;
+}
+
 template <int D>
 int launch_bwd(const BwdParams &p, cudaStream_t st) {
     const size_t smem = (size_t)(4 * kT * ld<D>() + 2 * kT * (kT + 1) + 2 * kT) * sizeof(float);
@@ -399,6 +640,8 @@ int nimllm_attn_prefill_bwd(const float *q_rot, const float *k_rot, const float 
     p.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)head_dim);
     cudaStream_t st = (cudaStream_t)stream;
     if (head_dim == 32) return launch_bwd<32>(p, st);
+    // 64 x 64 tiles once there is about one query tile per two SMs, the 32 x 32 tiles below that
+    if (head_dim == 64 && (int64_t)((seq_len + 63) / 64) * n_head * batch >= sm_count() / 2) return launch_bwd_tiled64(p, st);
     if (head_dim == 64) return launch_bwd<64>(p, st);
     return launch_bwd<128>(p, st);
 }

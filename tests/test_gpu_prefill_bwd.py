@@ -22,7 +22,10 @@ def _forward(q, k, v, cos, sin, Hq, Hkv, D):
 
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,D", [(1, 128, 9, 3, 64), (2, 77, 4, 2, 32), (1, 300, 8, 2, 128), (1, 1, 3, 3, 64),
-                                           (3, 33, 6, 1, 64)])
+                                           (3, 33, 6, 1, 64),
+                                           # launches large enough for the 64 x 64 register-tiled kernels: grouped heads
+                                           # (per-head partial sums) and one query head per KV head, ragged last tiles
+                                           (2, 300, 9, 3, 64), (2, 200, 10, 10, 64), (1, 449, 12, 4, 64)])
 @pytest.mark.parametrize("rope", [True, False])
 def test_backward_matches_oracle(B, S, Hq, Hkv, D, rope):
     q0 = normal(700 + S, 0, (B, S, Hq * D)); k0 = normal(700 + S, 1, (B, S, Hkv * D))
