@@ -340,8 +340,19 @@ __device__ __forceinline__ void load_tile64(float *dst, const float *src, int64_
         *reinterpret_cast<float4 *>(dst + r * kTL + c) = x;
     }
 }
-// acc[i][j] += A[rg + 16 i] . B[cg + 8 j] over the 64 columns of two [64][68] tiles
+// Packed fp32 arithmetic (two IEEE fp32 multiply-adds per instruction): the halves of a float4 read from
+// shared memory are register pairs as they are.
+__device__ __forceinline__ uint64_t pair_of(float a, float b) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+__device__ __forceinline__ void unpair(uint64_t v, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+// acc[i][j] += A[rg + 16 i] . B[cg + 8 j] over the 64 columns of two [64][68] tiles (even and odd columns are
+// summed separately and added at the end)
 __device__ __forceinline__ void tile_dots(const float *A, const float *B, int rg, int cg, float (&acc)[4][8]) {
+    uint64_t acc2[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc2[i][j] = 0ull;
 #pragma unroll 2
     for (int d = 0; d < 64; d += 4) {
         float4 af[4], bf[8];
@@ -350,15 +361,25 @@ __device__ __forceinline__ void tile_dots(const float *A, const float *B, int rg
 #pragma unroll
         for (int j = 0; j < 8; j++) bf[j] = *reinterpret_cast<const float4 *>(B + (cg + 8 * j) * kTL + d);
 #pragma unroll
-        for (int i = 0; i < 4; i++)
+        for (int i = 0; i < 4; i++) {
+            const uint64_t a01 = pair_of(af[i].x, af[i].y), a23 = pair_of(af[i].z, af[i].w);
 #pragma unroll
-            for (int j = 0; j < 8; j++)
-                acc[i][j] = fmaf(af[i].x, bf[j].x, fmaf(af[i].y, bf[j].y, fmaf(af[i].z, bf[j].z, fmaf(af[i].w, bf[j].w, acc[i][j]))));
+            for (int j = 0; j < 8; j++) acc2[i][j] = fma2(a23, pair_of(bf[j].z, bf[j].w), fma2(a01, pair_of(bf[j].x, bf[j].y), acc2[i][j]));
+        }
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) { float e, o; unpair(acc2[i][j], e, o); acc[i][j] += e + o; }
 }
 // g[i][4u + e] += sum_j W[rg + 16 i][j] * X[j][cg * 4 + 32 u + e]: the weights of a row are written and read by
 // the same eight lanes
 __device__ __forceinline__ void tile_accumulate(const float *W, const float *X, int rg, int cg, float (&g)[4][8]) {
+    uint64_t g2[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) g2[i][c] = pair_of(g[i][2 * c], g[i][2 * c + 1]);
 #pragma unroll 2
     for (int j = 0; j < 64; j += 4) {
         float4 wf[4];
@@ -368,14 +389,20 @@ __device__ __forceinline__ void tile_accumulate(const float *W, const float *X, 
         for (int jj = 0; jj < 4; jj++) {
             const float4 x0 = *reinterpret_cast<const float4 *>(X + (j + jj) * kTL + cg * 4);
             const float4 x1 = *reinterpret_cast<const float4 *>(X + (j + jj) * kTL + cg * 4 + 32);
+            const uint64_t x01 = pair_of(x0.x, x0.y), x23 = pair_of(x0.z, x0.w), x45 = pair_of(x1.x, x1.y), x67 = pair_of(x1.z, x1.w);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const float w = jj == 0 ? wf[i].x : jj == 1 ? wf[i].y : jj == 2 ? wf[i].z : wf[i].w;
-                g[i][0] = fmaf(w, x0.x, g[i][0]); g[i][1] = fmaf(w, x0.y, g[i][1]); g[i][2] = fmaf(w, x0.z, g[i][2]); g[i][3] = fmaf(w, x0.w, g[i][3]);
-                g[i][4] = fmaf(w, x1.x, g[i][4]); g[i][5] = fmaf(w, x1.y, g[i][5]); g[i][6] = fmaf(w, x1.z, g[i][6]); g[i][7] = fmaf(w, x1.w, g[i][7]);
+                const uint64_t ww = pair_of(w, w);
+                g2[i][0] = fma2(ww, x01, g2[i][0]); g2[i][1] = fma2(ww, x23, g2[i][1]);
+                g2[i][2] = fma2(ww, x45, g2[i][2]); g2[i][3] = fma2(ww, x67, g2[i][3]);
             }
         }
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) unpair(g2[i][c], g[i][2 * c], g[i][2 * c + 1]);
 }
 // scale, undo the rotation (columns f = cg * 4 + e and f + 32 are g[e] and g[4 + e]; k_rope with sign = -1,
 // src/kernels.cu:399-413) and store one row of a gradient
