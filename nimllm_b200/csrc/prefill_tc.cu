@@ -46,6 +46,11 @@ namespace nimllm {
 namespace {
 
 using namespace tc;
+// packed fp32 arithmetic: two IEEE fp32 operations per instruction, each rounded like its scalar form
+__device__ __forceinline__ uint64_t pair2(float a, float b) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void unpair2(uint64_t v, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2_f32(uint64_t a, uint64_t b, uint64_t c) { uint64_t r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+__device__ __forceinline__ uint64_t add2_f32(uint64_t a, uint64_t b) { uint64_t r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
 
 // Sticky per-device status of the bf16 prefill: becomes 1 when a bounded wait inside a launch gave
 // up (the outputs of that launch are then incomplete) and stays 1 until the host clears it through
@@ -426,7 +431,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
             // P = exp2(S*c - m_ref) as bf16 pairs, for the tile's own P columns
             const float neg_m = -m_ref;
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            uint64_t sum01 = 0ull, sum23 = 0ull;
+            const uint64_t c2 = pair2(c, c), nm2 = pair2(neg_m, neg_m);
             uint32_t pk[64];
             bool p_free = (j == 0);
 #pragma unroll
@@ -434,17 +440,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 // half-way: has the PV of the tile before finished with the P columns?  (asked here,
                 // so that the answer is back when the stores below need it)
                 if (i == 64 && j > 0) p_free = mbar_test(&sm.pv_done[w], (j - 1) & 1);
+                // scale-and-shift and the row sum as packed fp32 operations (two per instruction)
                 float x[4], e[4];
+                unpair2(fma2_f32(pair2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nm2), x[0], x[1]);
+                unpair2(fma2_f32(pair2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), c2, nm2), x[2], x[3]);
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    x[u] = fmaf(__uint_as_float(v[i + u]), c, neg_m);
-                    e[u] = ex2(x[u]);
-                }
-                sum0 += e[0]; sum1 += e[1]; sum2 += e[2]; sum3 += e[3];
+                for (int u = 0; u < 4; u++) e[u] = ex2(x[u]);
+                sum01 = add2_f32(sum01, pair2(e[0], e[1]));
+                sum23 = add2_f32(sum23, pair2(e[2], e[3]));
                 pk[i >> 1] = pack_bf16(e[0], e[1]);
                 pk[(i >> 1) + 1] = pack_bf16(e[2], e[3]);
             }
-            l += (sum0 + sum1) + (sum2 + sum3);
+            {
+                float sum0, sum1, sum2, sum3;
+                unpair2(sum01, sum0, sum1); unpair2(sum23, sum2, sum3);
+                l += (sum0 + sum1) + (sum2 + sum3);
+            }
             // P_w(j-1) must have been consumed (its PV was issued when the previous softmax ended)
             if (j > 0) {
                 if (!__all_sync(0xffffffffu, p_free) &&
